@@ -1,0 +1,221 @@
+"""The cache manager: pages of keys and values with a block table per request, one page
+pool per group of cache slots with the same need, and a state slot per request.
+
+Cache slots (one per run-order entry that writes a cache) are grouped by what their mixer
+keeps: (kv heads, head size, window).  A group has its own pool and its own block table
+per request; all slots of a group share the table (page id p means page p of every slot's
+storage in that group).  A group with a window gives pages back as soon as every position
+on them is further back than any later query can look.
+
+Accounting per request, in tokens:
+  extend(id, n)   make room for positions [0, n): takes pages, may raise OutOfPages
+  commit(id, n)   the step ran: n tokens are in the cache; pages a window has passed are freed
+  release(id)     the request ended (or is preempted): everything goes back
+After the reference's BlockManager (atom/model_engine/block_manager.py: can_allocate :371,
+allocate :447, can_append :1109, may_append :1117, deallocate :1083), reshaped so that a
+step may hold prompt portions and decoded tokens together.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Tuple
+
+from ..parts.spec import CacheNeed
+from .page_pool import OutOfPages, PagePool
+from .state_slots import StateSlots
+
+NO_PAGE = -1
+
+
+@dataclass
+class CacheGroup:
+    index: int
+    key: Tuple
+    window: Optional[int]
+    num_kv_heads: int
+    head_dim: int
+    slots: List[int]                 # cache slots (run-order cache ids) stored in this group
+    pool: PagePool = None            # type: ignore
+
+
+@dataclass
+class RequestCache:
+    state_slot: int
+    committed: int = 0               # tokens whose keys/values are in the cache
+    reserved: int = 0                # positions [0, reserved) have pages (where still needed)
+    tables: Dict[int, List[int]] = field(default_factory=dict)   # group -> page id per logical page
+
+
+class CacheManager:
+    def __init__(self, needs: Dict[int, CacheNeed], page_size: int, num_pages, max_requests: int):
+        """needs: cache slot -> CacheNeed.  num_pages: int (every group) or {group key: int}."""
+        if page_size <= 0:
+            raise ValueError("page_size must be positive")
+        self.page_size = page_size
+        self.groups: List[CacheGroup] = []
+        self.slot_group: Dict[int, int] = {}
+        self.state_needs: Dict[int, CacheNeed] = {}
+        by_key: Dict[Tuple, CacheGroup] = {}
+        for slot in sorted(needs):
+            need = needs[slot]
+            if need.kind == "state":
+                self.state_needs[slot] = need
+                continue
+            if need.kind != "pages":
+                raise ValueError(f"cache slot {slot}: unknown cache need kind '{need.kind}'")
+            if need.window is not None and need.window <= 0:
+                raise ValueError(f"cache slot {slot}: window must be positive")
+            k = need.group_key()
+            g = by_key.get(k)
+            if g is None:
+                g = CacheGroup(len(self.groups), k, need.window, need.num_kv_heads, need.head_dim, [])
+                n = num_pages[k] if isinstance(num_pages, dict) else num_pages
+                g.pool = PagePool(n)
+                by_key[k] = g
+                self.groups.append(g)
+            g.slots.append(slot)
+            self.slot_group[slot] = g.index
+        self.state_slots = StateSlots(max_requests)
+        self.requests: Dict[Hashable, RequestCache] = {}
+
+    # ------------------------------------------------------------------ queries
+
+    def _first_needed_page(self, g: CacheGroup, committed: int) -> int:
+        """Logical page below which no later query of the request can look."""
+        if g.window is None:
+            return 0
+        first_pos = committed - g.window + 1   # oldest key the next query (at `committed`) sees
+        return max(0, first_pos) // self.page_size
+
+    def pages_to_extend(self, rid: Optional[Hashable], n_tokens: int) -> Dict[int, int]:
+        """Pages each group must give so that positions [0, n_tokens) of the request are held."""
+        rc = self.requests.get(rid) if rid is not None else None
+        out = {}
+        n_logical = -(-n_tokens // self.page_size)
+        for g in self.groups:
+            if rc is None:
+                out[g.index] = n_logical - self._first_needed_page(g, 0)
+            else:
+                have = len(rc.tables[g.index])
+                out[g.index] = max(0, n_logical - have)
+        return out
+
+    def can_extend(self, rid: Optional[Hashable], n_tokens: int) -> bool:
+        if rid is None or rid not in self.requests:
+            if self.state_slots.num_free == 0:
+                return False
+        need = self.pages_to_extend(rid, n_tokens)
+        return all(self.groups[gi].pool.num_free >= n for gi, n in need.items())
+
+    def peak_pages(self, n_tokens: int, max_portion: int) -> Dict[int, int]:
+        """Most pages a request of n_tokens holds at once in each group, when no step brings
+        more than max_portion of its tokens: all of them without a window, else the portion
+        plus the window (and the partial pages at both ends)."""
+        n_logical = -(-n_tokens // self.page_size)
+        out = {}
+        for g in self.groups:
+            if g.window is None:
+                out[g.index] = n_logical
+            else:
+                span = min(n_tokens, max_portion) + g.window - 1
+                out[g.index] = min(n_logical, -(-span // self.page_size) + 1)
+        return out
+
+    def fits_at_all(self, n_tokens: int, max_portion: int) -> bool:
+        """Whether an otherwise empty cache could hold a request of this length."""
+        peak = self.peak_pages(n_tokens, max_portion)
+        return all(peak[g.index] <= g.pool.num_pages for g in self.groups)
+
+    def can_admit(self, n_tokens: int, max_portion: int) -> bool:
+        """Whether a new request of this length can be taken in now: a state slot is free and
+        every group has, free at this moment, the most pages the request will hold at once."""
+        if self.state_slots.num_free == 0:
+            return False
+        peak = self.peak_pages(n_tokens, max_portion)
+        return all(g.pool.num_free >= peak[g.index] for g in self.groups)
+
+    # ------------------------------------------------------------------ life of a request
+
+    def admit(self, rid: Hashable) -> RequestCache:
+        if rid in self.requests:
+            raise RuntimeError(f"request {rid!r} is already admitted")
+        rc = RequestCache(state_slot=self.state_slots.allocate(rid))
+        for g in self.groups:
+            rc.tables[g.index] = []
+        self.requests[rid] = rc
+        return rc
+
+    def extend(self, rid: Hashable, n_tokens: int) -> None:
+        """Makes room for positions [0, n_tokens).  All or nothing: raises OutOfPages and
+        leaves the request as it was if any group cannot give its pages."""
+        rc = self.requests[rid]
+        if n_tokens < rc.committed:
+            raise ValueError("a request cannot shrink")
+        need = self.pages_to_extend(rid, n_tokens)
+        for gi, n in need.items():
+            if self.groups[gi].pool.num_free < n:
+                raise OutOfPages(
+                    f"request {rid!r}: group {gi} needs {n} pages, {self.groups[gi].pool.num_free} free"
+                )
+        for gi, n in need.items():
+            if n:
+                rc.tables[gi].extend(self.groups[gi].pool.allocate(n, (rid, gi)))
+        rc.reserved = max(rc.reserved, n_tokens)
+
+    def commit(self, rid: Hashable, n_tokens: int) -> None:
+        """The step that brought the request to n_tokens has run."""
+        rc = self.requests[rid]
+        if n_tokens < rc.committed:
+            raise ValueError(f"request {rid!r}: commit({n_tokens}) below what is committed")
+        for g in self.groups:
+            if n_tokens > len(rc.tables[g.index]) * self.page_size:
+                raise ValueError(f"request {rid!r}: commit({n_tokens}) beyond what was reserved")
+        rc.committed = n_tokens
+        for g in self.groups:
+            if g.window is None:
+                continue
+            table = rc.tables[g.index]
+            first = min(self._first_needed_page(g, n_tokens), len(table))
+            gone = [p for p in table[:first] if p != NO_PAGE]
+            if gone:
+                g.pool.free(gone, (rid, g.index))
+                for i in range(first):
+                    table[i] = NO_PAGE
+
+    def release(self, rid: Hashable) -> None:
+        rc = self.requests.pop(rid)
+        for g in self.groups:
+            held = [p for p in rc.tables[g.index] if p != NO_PAGE]
+            # Freed in reverse so that the lowest ids are handed out first again
+            # (atom/model_engine/block_manager.py:1083-1107 frees in reverse order too).
+            g.pool.free(reversed(held), (rid, g.index))
+        self.state_slots.free(rc.state_slot)
+
+    # ------------------------------------------------------------------ views
+
+    def table(self, rid: Hashable, group: int) -> List[int]:
+        return self.requests[rid].tables[group]
+
+    def committed(self, rid: Hashable) -> int:
+        return self.requests[rid].committed
+
+    def num_free_pages(self, group: int = 0) -> int:
+        return self.groups[group].pool.num_free
+
+    def check(self) -> None:
+        """Accounting invariants: no page lost, held twice or by a request that is gone."""
+        self.state_slots.check()
+        for g in self.groups:
+            g.pool.check()
+            seen = set()
+            for rid, rc in self.requests.items():
+                for p in rc.tables[g.index]:
+                    if p == NO_PAGE:
+                        continue
+                    if p in seen:
+                        raise AssertionError(f"page {p} of group {g.index} is in two tables")
+                    seen.add(p)
+                    if g.pool.owner_of(p) != (rid, g.index):
+                        raise AssertionError(f"page {p} of group {g.index}: owner mismatch")
+            if len(seen) != g.pool.num_used:
+                raise AssertionError(f"group {g.index}: {g.pool.num_used} pages held, {len(seen)} in tables")

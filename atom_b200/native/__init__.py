@@ -1,0 +1,250 @@
+"""ctypes binding of the sm_100a kernel library.
+
+``lib()`` builds the library on first use (see ``build.py``) and loads it; every kernel
+wrapper below takes torch tensors, passes raw device pointers and the current stream, and
+raises if the kernel refuses its arguments.  There is no fallback: without the library the
+product path does not run.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .build import NativeBuildError, build
+
+F32, BF16 = 0, 1
+_ERR = {1: "argument the kernel does not take", 2: "CUDA launch failed", 3: "library call failed"}
+
+_lib = None
+_lock = threading.Lock()
+launches = 0  # number of kernel-library calls made by this process (a launch counter)
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise NativeError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = build()
+                try:
+                    _lib = ctypes.CDLL(path)
+                except OSError as e:  # pragma: no cover
+                    raise NativeBuildError(f"cannot load {path}: {e}") from e
+                _declare(_lib)
+    return _lib
+
+
+def lib_path() -> str:
+    return build(verbose=False)
+
+
+_vp, _i, _i64, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
+
+_SIGNATURES = {
+    "atom_embedding": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "atom_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp],
+    "atom_rmsnorm": [_vp, _vp, _i, _vp, _i, _f, _i, _i, _vp],
+    "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+    "atom_qknorm_rope_kvwrite": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _vp,
+                                 _vp, _i, _i, _vp, _vp, _i64, _vp, _vp],
+    "atom_paged_attention_generic": [_vp, _vp, _i64, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i,
+                                     _i, _i, _f, _i, _vp],
+    "atom_gemm_f32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _vp],
+    "atom_gemm_bf16": [_vp, _i, _vp, _vp, _i, _i, _i, _i64, _vp, _sz, _vp],
+    "atom_add_bias": [_vp, _i, _vp, _i, _i, _i, _vp],
+}
+
+
+def _declare(l) -> None:
+    for name, args in _SIGNATURES.items():
+        if not hasattr(l, name):
+            continue  # optional kernels are declared by the module that owns them
+        fn = getattr(l, name)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+
+
+def declare(name: str, args) -> None:
+    """Declares the signature of one more exported function (used by kernel modules)."""
+    _SIGNATURES[name] = args
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+
+
+def _check(code: int, name: str) -> None:
+    global launches
+    launches += 1
+    if code != 0:
+        raise NativeError(f"{name}: {_ERR.get(code, f'error {code}')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise NativeError("kernels take CUDA tensors only (there is no CPU path)")
+
+
+# --------------------------------------------------------------------------- wrappers
+
+
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] widened to float32.  out [T,H] f32, table [V,H], ids [T] i32."""
+    _cuda(out, table, ids)
+    T, H = out.shape
+    assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
+    assert out.is_contiguous() and table.is_contiguous() and ids.numel() >= T
+    _check(lib().atom_embedding(out.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
+                                ids.data_ptr(), T, H, table.shape[0], _stream()), "embedding")
+
+
+def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                weight: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+                n_rows: Optional[int] = None) -> None:
+    """residual (+= delta); out = rmsnorm(residual) * weight.  With ``rows`` (int32 indices)
+    only those rows are normalised, written densely to ``out``, and residual is left as is."""
+    _cuda(out, residual, delta, weight, rows)
+    H = residual.shape[-1]
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
+    assert weight.numel() == H and (delta is None or (delta.dtype == out.dtype and delta.is_contiguous()))
+    n = (rows.numel() if n_rows is None else n_rows) if rows is not None else residual.shape[0]
+    assert out.shape[0] >= n and out.shape[-1] == H
+    _check(lib().atom_add_rmsnorm(out.data_ptr(), dtype_code(out.dtype), residual.data_ptr(),
+                                  _ptr(delta), weight.data_ptr(), dtype_code(weight.dtype),
+                                  float(eps), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    _cuda(out, x, weight)
+    H = x.shape[-1]
+    assert x.is_contiguous() and out.is_contiguous() and out.dtype == x.dtype and weight.numel() == H
+    _check(lib().atom_rmsnorm(out.data_ptr(), x.data_ptr(), dtype_code(x.dtype), weight.data_ptr(),
+                              dtype_code(weight.dtype), float(eps), x.numel() // H, H, _stream()),
+           "rmsnorm")
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _cuda(out, gate_up)
+    T, I2 = gate_up.shape
+    assert I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
+    assert out.is_contiguous() and gate_up.is_contiguous()
+    _check(lib().atom_silu_mul(out.data_ptr(), gate_up.data_ptr(), dtype_code(out.dtype), T, I2 // 2,
+                               _stream()), "silu_mul")
+
+
+def qknorm_rope_kvwrite(qkv: torch.Tensor, nh: int, nkv: int, hd: int,
+                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                        eps: float, cos_sin: Optional[torch.Tensor], rotary_dim: int,
+                        positions: torch.Tensor, seq_of_token: torch.Tensor,
+                        block_table: torch.Tensor, page_size: int,
+                        k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                        status: torch.Tensor) -> None:
+    """Per-head q/k norm, rotation and cache write for the packed [T, (nh+2nkv)*hd] projection."""
+    _cuda(qkv, q_weight, k_weight, cos_sin, positions, seq_of_token, block_table, k_pages, v_pages, status)
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * hd
+    assert (q_weight is None) == (k_weight is None)
+    wd = dtype_code(q_weight.dtype) if q_weight is not None else F32
+    if q_weight is not None:
+        assert k_weight.dtype == q_weight.dtype and q_weight.numel() == hd and k_weight.numel() == hd
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] == rotary_dim
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    num_pages = 0
+    if k_pages is not None:
+        assert k_pages.dtype == qkv.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (nkv, page_size, hd) and v_pages.shape == k_pages.shape
+        num_pages = k_pages.shape[0]
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    assert positions.dtype == torch.int32 and seq_of_token.dtype == torch.int32
+    assert status.dtype == torch.int32
+    _check(lib().atom_qknorm_rope_kvwrite(
+        qkv.data_ptr(), dtype_code(qkv.dtype), T, nh, nkv, hd, _ptr(q_weight), _ptr(k_weight), wd,
+        float(eps), _ptr(cos_sin), rotary_dim, max_pos, positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
+        num_pages, status.data_ptr(), _stream()), "qknorm_rope_kvwrite")
+
+
+def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, q_stride: int,
+                            k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                            positions: torch.Tensor, seq_of_token: torch.Tensor, T: int, nh: int,
+                            nkv: int, hd: int, scale: float, window: int) -> None:
+    """out[T, nh*hd]: causal attention of every token over its request's pages (any sizes)."""
+    _cuda(out, q, k_pages, v_pages, block_table, positions, seq_of_token)
+    page_size = k_pages.shape[2]
+    assert out.is_contiguous() and out.dtype == q.dtype == k_pages.dtype
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, hd) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    _check(lib().atom_paged_attention_generic(
+        out.data_ptr(), q.data_ptr(), q_stride, dtype_code(q.dtype), k_pages.data_ptr(),
+        v_pages.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+        positions.data_ptr(), seq_of_token.data_ptr(), T, nh, nkv, hd, float(scale), int(window),
+        _stream()), "paged_attention_generic")
+
+
+def gemm_f32(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) in true 32-bit arithmetic."""
+    _cuda(out, a, w, bias)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == w.dtype == out.dtype == torch.float32 and w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
+    _check(lib().atom_gemm_f32(out.data_ptr(), a.data_ptr(), w.data_ptr(), _ptr(bias), M, N, K,
+                               a.stride(0), out.stride(0), _stream()), "gemm_f32")
+
+
+_workspaces = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def gemm_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
+    """out[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T, bf16 operands, 32-bit accumulation (cuBLAS)."""
+    _cuda(out, a, w)
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and out.is_contiguous() and w.is_contiguous()
+    ws = _workspace(out.device)
+    _check(lib().atom_gemm_bf16(out.data_ptr(), dtype_code(out.dtype), a.data_ptr(), w.data_ptr(), M, N,
+                                K, a.stride(0), ws.data_ptr(), ws.numel(), _stream()), "gemm_bf16")
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    _cuda(out, bias)
+    M, N = out.shape
+    assert out.is_contiguous() and bias.numel() == N
+    _check(lib().atom_add_bias(out.data_ptr(), dtype_code(out.dtype), bias.data_ptr(),
+                               dtype_code(bias.dtype), M, N, _stream()), "add_bias")

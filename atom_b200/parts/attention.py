@@ -1,0 +1,88 @@
+"""Grouped-query attention over the paged cache (atom/models/qwen3.py:59-163).
+
+   qkv = x W_qkv^T (+ b);  q, k, v = split(qkv, [nh*hd, nkv*hd, nkv*hd])          (:146-147)
+   q_h = RMSNorm_hd(q_h; w_q),  k_g = RMSNorm_hd(k_g; w_k)   per head, if qk_norm   (:159-160)
+   q, k rotated by the position encoding; k, v written to the request's pages
+   o_t = softmax_j(scale * q_t . k_j) v_j  over j <= pos(t) (and j > pos(t) - window)
+   y = o W_o^T                                                                      (:162)
+scale = hd^-0.5 (:88) unless given.  Query head h reads kv head h // (nh / nkv).
+One kernel semantics serves prompt portions and decoded tokens: every token attends to
+the keys of its own request that lie in the cache after this step's write.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import native
+from . import registry
+from .base import Mixer
+from .linear import linear
+from .registry import register
+from .spec import CacheNeed, ParamSpec, PartSpec
+
+
+@register("mixer", "paged_attention")
+class PagedAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PartSpec, qk_norm: bool = False, norm_eps: float = 0.0,
+                 bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.hidden_size, self.nh, self.nkv, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qk_norm, self.norm_eps, self.bias, self.window = qk_norm, norm_eps, bias, window
+        self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.position = registry.build("position", position)
+        self._table = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        q, kv = self.nh * self.hd, self.nkv * self.hd
+        p = {
+            "qkv.weight": ParamSpec((q + 2 * kv, self.hidden_size), rows=(q, kv, kv)),
+            "o.weight": ParamSpec((self.hidden_size, q)),
+        }
+        if self.bias:
+            p["qkv.bias"] = ParamSpec((q + 2 * kv,), role="vector", init="zeros", rows=(q, kv, kv))
+        if self.qk_norm:
+            p["q_norm.weight"] = ParamSpec((self.hd,), role="vector", init="norm")
+            p["k_norm.weight"] = ParamSpec((self.hd,), role="vector", init="norm")
+        return p
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("pages", num_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self._table = self.position.table(rt)
+        self._check_sizes()
+
+    def _check_sizes(self) -> None:
+        if self.hd > 512:
+            raise ValueError(f"paged_attention: head_dim {self.hd} is beyond what the kernels take (512)")
+
+    def forward(self, x, step, cache, writes_cache):
+        T = x.shape[0]
+        ws, dt = self.rt.workspace, self.rt.dtype
+        nh, nkv, hd = self.nh, self.nkv, self.hd
+        qkv = linear(x, self.w_qkv_weight, getattr(self, "w_qkv_bias", None),
+                     ws.get("attn.qkv", (T, (nh + 2 * nkv) * hd), dt))
+        bt = step.block_tables[cache.group]
+        native.qknorm_rope_kvwrite(
+            qkv, nh, nkv, hd,
+            self.w_q_norm_weight if self.qk_norm else None,
+            self.w_k_norm_weight if self.qk_norm else None,
+            self.norm_eps, self._table, self.position.rotary_dim,
+            step.positions, step.seq_of_token, bt, cache.page_size,
+            cache.k_pages if writes_cache else None, cache.v_pages if writes_cache else None,
+            step.status)
+        o = ws.get("attn.o", (T, nh * hd), dt)
+        self.attend(o, qkv, step, cache, bt)
+        return linear(o, self.w_o_weight, None, ws.get("attn.out", (T, self.hidden_size), dt))
+
+    def attend(self, o, qkv, step, cache, bt) -> None:
+        """Chooses the attention kernel for this step's tokens."""
+        native.paged_attention_generic(
+            o, qkv, qkv.shape[1], cache.k_pages, cache.v_pages, bt, step.positions,
+            step.seq_of_token, o.shape[0], self.nh, self.nkv, self.hd, self.scale,
+            self.window if self.window else 0)

@@ -1,0 +1,100 @@
+"""Interfaces of the parts a layer is put together from.
+
+Every part
+  * takes its sizes and constants as constructor arguments,
+  * declares its parameters with ``params()`` (name -> ParamSpec),
+  * receives the loaded tensors with ``bind(tensors, runtime)``,
+and does not know which model it is in.  ``Runtime`` carries what all parts share: the
+compute type, the device and a workspace of reusable activation buffers.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .spec import CacheNeed, ParamSpec
+
+
+class Workspace:
+    """Reusable activation buffers, keyed by a tag, grown on demand and viewed per call.
+
+    Steps run one after another on one stream, so a buffer is free again when the next
+    step asks for it.  Shapes depend on the number of tokens in the step only.
+    """
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.frozen = False  # set while a CUDA graph holds pointers into the buffers
+
+    def get(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        key = (tag, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen and buf is not None:
+                raise RuntimeError(f"workspace buffer '{tag}' would move while a graph holds it")
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:n].view(shape)
+
+
+@dataclass
+class Runtime:
+    dtype: torch.dtype          # compute type: torch.float32 or torch.bfloat16
+    device: torch.device
+    workspace: Workspace
+
+    @property
+    def true_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class Part:
+    kind = "?"
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        for k, v in tensors.items():
+            setattr(self, "w_" + k.replace(".", "_"), v)
+
+
+class Norm(Part):
+    """``add_norm``: residual (+= delta), returns the normalised rows in the compute type."""
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], tag: str,
+                 rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Gives the mixer what it needs to encode positions (for rotary kinds: a table)."""
+
+    rotary_dim = 0
+
+    def table(self, rt: Runtime) -> Optional[torch.Tensor]:
+        return None
+
+
+class Mixer(Part):
+    """Mixes information along the sequence.  ``cache_need`` says what it keeps per request."""
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, x: torch.Tensor, step, cache, writes_cache: bool) -> torch.Tensor:
+        """x: [T, hidden] normalised input.  ``step`` is the StepContext of this batch,
+        ``cache`` the view of this run entry's cache slot.  Returns [T, hidden]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError

@@ -1,0 +1,32 @@
+"""SiLU-gated feed-forward (atom/models/qwen3.py:166-198, atom/model_ops/activation.py:78-82):
+   gu = x W_gate_up^T;  f = silu(gu[:, :I]) * gu[:, I:];  y = f W_down^T."""
+from __future__ import annotations
+
+from typing import Dict
+
+from .. import native
+from .base import FeedForward
+from .linear import linear
+from .registry import register
+from .spec import ParamSpec
+
+
+@register("ffn", "gated_silu")
+class GatedSiluMLP(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+
+    def params(self) -> Dict[str, ParamSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return {
+            "gate_up.weight": ParamSpec((2 * I, H), rows=(I, I)),
+            "down.weight": ParamSpec((H, I)),
+        }
+
+    def forward(self, x, step):
+        T = x.shape[0]
+        ws, dt = self.rt.workspace, self.rt.dtype
+        gu = linear(x, self.w_gate_up_weight, None, ws.get("ffn.gate_up", (T, 2 * self.intermediate_size), dt))
+        f = ws.get("ffn.act", (T, self.intermediate_size), dt)
+        native.silu_mul(f, gu)
+        return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))

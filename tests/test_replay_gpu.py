@@ -1,0 +1,102 @@
+"""The engine against the plain implementation, under every way of cutting the work:
+each request alone and whole; most of it in one step and the last 32 tokens one by one; in
+portions of changing size down to two tokens; and mixed, up to four live requests, with so
+few pages that they are used again.  In 32-bit and in bfloat16."""
+import numpy as np
+import pytest
+
+import tiny
+import traces
+from replay_util import make_runner, max_err, plain_logits, replay
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [1, 7, 16, 33, 100, 70], "B": [3, 5, 12, 29, 64, 100, 131], "C": [2, 31, 77, 49, 120]}
+PAGE = {"A": 16, "B": 8, "C": 16}
+# 32-bit: the engine and the plain implementation differ by the order of float32 sums only:
+# 1e-4 absolute on logits of magnitude ~1.
+# bfloat16: activations are rounded to 8 bits of mantissa (relative 2^-9) between kernels.
+# Over all positions the error is a fraction of a percent of the logit scale (bound: 1 % rms);
+# single positions reach a few percent where a sharpened softmax (scores up to ~16)
+# multiplies the rounding of q and k (bound: 8 % of the largest logit).  Faults of the cache
+# or the batch are far larger, and the 32-bit runs of the same code catch the small ones.
+TOL = {"float32": 1e-4, "bfloat16": 8e-2}
+RMS_TOL_BF16 = 1e-2
+
+
+def _seqs(name):
+    ps = tiny.prompts(name, LENGTHS[name], seed={"A": 1, "B": 3, "C": 5}[name])
+    return {f"r{i}": p for i, p in enumerate(ps)}
+
+
+def _tol(dtype, ref):
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    return TOL[dtype] * max(1.0, scale) if dtype == "float32" else TOL[dtype] * scale
+
+
+@pytest.fixture(scope="module")
+def runners(model_dirs):
+    cache = {}
+
+    def get(name, dtype, max_tokens):
+        key = (name, dtype, max_tokens)
+        if key not in cache:
+            cache[key] = make_runner(model_dirs[name], dtype, max_tokens, PAGE[name])
+        return cache[key]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "ragged", "mixed"])
+def test_cut_matches_plain(model_dirs, runners, name, dtype, cut):
+    seqs = _seqs(name)
+    ref = plain_logits(model_dirs[name], seqs)
+    if cut == "whole":
+        steps, peak = traces.whole(seqs), 192
+    elif cut == "tail":
+        steps, peak = traces.tail_by_token(seqs, 32), 192
+    elif cut == "ragged":
+        steps, peak = traces.ragged(seqs), 192
+    else:
+        steps, peak = traces.mixed(seqs, max_live=4, budget_tokens=320)
+        assert peak <= 320
+    runner = runners(name, dtype, peak)
+    got = traces.collect(steps, replay(runner, steps))
+    err, rid, pos = max_err(got, ref)
+    tol = _tol(dtype, ref)
+    assert err <= tol, f"{name}/{dtype}/{cut}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+    if dtype == "bfloat16":
+        scale = max(float(np.abs(r).max()) for r in ref.values())
+        for r in ref:
+            rms = float(np.sqrt(((got[r] - ref[r]) ** 2).mean()))
+            assert rms <= RMS_TOL_BF16 * scale, f"{name}/{cut}: rms error {rms:.3e} in {r}"
+    # every page and slot is back
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+    if dtype == "float32":
+        for r in ref:
+            assert (got[r].argmax(1) == ref[r].argmax(1)).all(), f"{name}/{cut}: greedy token differs in {r}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_reuses_pages(model_dirs, runners, dtype):
+    """With a pool this small the later requests must run on pages the earlier ones freed."""
+    name = "B"
+    seqs = _seqs(name)
+    steps, peak = traces.mixed(seqs, max_live=4, budget_tokens=320)
+    total = sum(-(-len(t) // 64) * 64 for t in seqs.values())
+    assert peak < total, "the trace does not force re-use"
+    runner = runners(name, dtype, peak)
+    seen, reused = set(), False
+    from atom_b200.engine.batch import StepEntry
+    for s in steps:
+        runner.step([StepEntry(e["id"], e["tokens"], ()) for e in s["entries"]])
+        for rid in s["end"]:
+            before = set(runner.cache.table(rid, 0))
+            runner.finish(rid)
+            seen |= {p for p in before if p >= 0}
+        now = {p for rc in runner.cache.requests.values() for p in rc.tables[0] if p >= 0}
+        reused = reused or bool(now & seen)
+    runner.check_status()
+    assert reused
