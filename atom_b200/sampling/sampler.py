@@ -1,0 +1,53 @@
+"""Turns logits into token ids on the device: greedy, temperature (the exponential race of
+atom/model_ops/sampler.py:104-132) and top-k / top-p (:134-295), one kernel for all rows."""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import native
+from .params import SamplingParams
+
+_vp, _i = ctypes.c_void_p, ctypes.c_int
+native.declare("atom_sample", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp])
+
+
+class Sampler:
+    def __init__(self, device, default_seed: int = 0):
+        self.device = torch.device(device)
+        self.default_seed = default_seed
+        self._probs = None
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               indices: Sequence[int]) -> torch.Tensor:
+        """logits [R, V] float32 on the device.  seeds[r] is the request's random stream,
+        indices[r] counts the tokens the request has generated so far.  Returns int32 [R]."""
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.is_contiguous() and len(params) == R
+        host = np.zeros((5, R), dtype=np.float32)
+        hi = host.view(np.uint32)
+        any_filter = False
+        for r, p in enumerate(params):
+            host[0, r] = p.temperature
+            hi[1, r] = seeds[r] & 0xFFFFFFFF
+            hi[2, r] = indices[r] & 0xFFFFFFFF
+            host.view(np.int32)[3, r] = p.top_k
+            host[4, r] = p.top_p
+            any_filter = any_filter or (p.filters and not p.greedy)
+        dev = torch.from_numpy(host).to(self.device, non_blocking=False)
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        probs = None
+        if any_filter:
+            if self._probs is None or self._probs.numel() < R * V:
+                self._probs = torch.empty(R * V, dtype=torch.float32, device=self.device)
+            probs = self._probs
+        code = native.lib().atom_sample(
+            out.data_ptr(), logits.data_ptr(), dev[0].data_ptr(), dev[1].data_ptr(), dev[2].data_ptr(),
+            dev[3].data_ptr() if any_filter else None, dev[4].data_ptr() if any_filter else None,
+            probs.data_ptr() if probs is not None else None, R, V,
+            torch.cuda.current_stream().cuda_stream)
+        native._check(code, "sample")
+        return out

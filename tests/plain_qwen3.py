@@ -195,7 +195,7 @@ def exponential_noise(seed: int, index: int, vocab: int) -> np.ndarray:
     v = np.arange(vocab, dtype=np.uint64)
     k = _mix32(np.uint64(seed & 0xFFFFFFFF) ^ _mix32(np.uint64(index & 0xFFFFFFFF) + np.uint64(0x9E3779B9)))
     bits = _mix32((v + np.uint64(1)) * np.uint64(0x9E3779B1) & np.uint64(0xFFFFFFFF) ^ k)
-    u = (bits.astype(np.float64) + 0.5) / 4294967296.0
+    u = ((bits >> np.uint64(8)).astype(np.float64) + 0.5) / 16777216.0
     return -np.log(u)
 
 

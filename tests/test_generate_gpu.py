@@ -1,0 +1,162 @@
+"""Generation through the Python entry point against the plain implementation: greedy and
+temperature sampling, alone and batched, with a pool so small that requests are preempted
+and recomputed, long decoding, and the first tokens of a sequence."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(model_dir, dtype, pages, page, **kw):
+    from atom_b200 import LLMEngine
+    return LLMEngine(model_dir, dtype=dtype, kv_cache_block_size=page, num_kvcache_blocks=pages,
+                     enforce_eager=kw.pop("enforce_eager", True), **kw)
+
+
+def _plain(model_dir):
+    return plain.read_config(model_dir), plain.read_tensors(model_dir)
+
+
+def _check_greedy_against_plain(cfg, w, prompt, out_ids, margin):
+    """Teacher-forced check: every generated token is the plain implementation's argmax at
+    its place (within ``margin`` of the largest logit, for the reduced-precision run)."""
+    full = list(prompt) + list(out_ids)
+    logits = plain.forward(cfg, w, full[:-1]).numpy()
+    for i, tok in enumerate(out_ids):
+        row = logits[len(prompt) - 1 + i]
+        if margin == 0:
+            assert tok == int(row.argmax()), f"token {i}: got {tok}, plain says {int(row.argmax())}"
+        else:
+            assert row[tok] >= row.max() - margin, f"token {i}: logit {row[tok]:.4f} vs max {row.max():.4f}"
+
+
+@pytest.mark.parametrize("name,page,chunk", [("A", 16, 8), ("B", 8, 13)])
+def test_greedy_generate_fp32_equals_plain(model_dirs, name, page, chunk):
+    from atom_b200 import SamplingParams
+    cfg, w = _plain(model_dirs[name])
+    lengths = [1, 7, 16, 33] if name == "A" else [3, 5, 12, 29, 64, 100]
+    n_new = 8 if name == "A" else 12
+    prompts = tiny.prompts(name, lengths, seed=1 if name == "A" else 3)
+    eng = _engine(model_dirs[name], "float32", pages=64, page=page, max_num_batched_tokens=chunk + 4,
+                  long_prefill_token_threshold=chunk)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o["num_tokens_output"] == n_new and o["finish_reason"] == "max_tokens"
+        assert o["token_ids"] == plain.generate_greedy(cfg, w, p, n_new)
+    assert all(g.pool.num_used == 0 for g in eng.runner.cache.groups)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generate_bf16_is_plain_argmax_within_rounding(model_dirs, name):
+    from atom_b200 import SamplingParams
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [5, 40, 90], seed=7)
+    eng = _engine(model_dirs[name], "bfloat16", pages=64, page=16)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        _check_greedy_against_plain(cfg, w, p, o["token_ids"], margin=0.08)
+
+
+def test_tiny_pool_preempts_and_still_matches(model_dirs):
+    """12 pages of 8 tokens; four requests are admitted on their prompts (8 pages) and then
+    grow by 40 tokens each: the newest are preempted, recomputed later, and every token is
+    still the plain implementation's."""
+    from atom_b200 import SamplingParams
+    name = "B"
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [3, 5, 12, 29], seed=3)
+    eng = _engine(model_dirs[name], "float32", pages=12, page=8, max_num_batched_tokens=24, max_num_seqs=4)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    assert eng.stats()["preemptions"] > 0
+    for p, o in zip(prompts, outs):
+        assert o["token_ids"] == plain.generate_greedy(cfg, w, p, 40)
+    eng.runner.cache.check()
+    assert eng.runner.cache.num_free_pages(0) == 12
+
+
+def test_request_too_large_is_rejected_not_hung(model_dirs):
+    from atom_b200 import SamplingParams
+    eng = _engine(model_dirs["A"], "float32", pages=2, page=16)
+    outs = eng.generate([list(range(40)), [1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert outs[0]["finish_reason"].startswith("unschedulable") and outs[0]["token_ids"] == []
+    assert outs[1]["num_tokens_output"] == 4
+
+
+def test_temperature_sampling_matches_plain_and_ignores_batching(model_dirs):
+    from atom_b200 import SamplingParams
+    name = "B"
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [3, 5, 12, 29, 64, 100], seed=3)
+    sps = [SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True) if i % 2 == 0 else
+           SamplingParams(temperature=0.7, max_tokens=12, ignore_eos=True, seed=100 + i) for i in range(6)]
+    eng = _engine(model_dirs[name], "float32", pages=64, page=8, max_num_batched_tokens=30)
+    batched = eng.generate(prompts, sps)
+    alone = [eng.generate([p], sp)[0] for p, sp in zip(prompts, sps)]
+    for i, (p, sp) in enumerate(zip(prompts, sps)):
+        assert batched[i]["token_ids"] == alone[i]["token_ids"], f"request {i} depends on its batch"
+        ids = list(p)
+        for j, tok in enumerate(batched[i]["token_ids"]):
+            row = plain.forward(cfg, w, ids)[-1]
+            want = plain.sample_temperature(row, sp.temperature, sp.seed or 0, j)
+            assert tok == want, f"request {i} token {j}: got {tok}, plain draws {want}"
+            ids.append(tok)
+    # other seeds, other tokens
+    other = eng.generate([prompts[3]], SamplingParams(temperature=0.7, max_tokens=12, ignore_eos=True, seed=999))[0]
+    assert other["token_ids"] != batched[3]["token_ids"]
+
+
+def test_top_k_top_p_match_plain(model_dirs):
+    from atom_b200 import SamplingParams
+    name = "A"
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [9, 21], seed=5)
+    for sp in (SamplingParams(temperature=1.3, top_k=5, max_tokens=10, ignore_eos=True, seed=4),
+               SamplingParams(temperature=1.5, top_p=0.3, max_tokens=10, ignore_eos=True, seed=5),
+               SamplingParams(temperature=2.0, top_k=12, top_p=0.6, max_tokens=10, ignore_eos=True, seed=6)):
+        eng = _engine(model_dirs[name], "float32", pages=16, page=16)
+        for p, o in zip(prompts, eng.generate(prompts, sp)):
+            ids = list(p)
+            for j, tok in enumerate(o["token_ids"]):
+                row = plain.forward(cfg, w, ids)[-1]
+                assert tok == plain.sample_temperature(row, sp.temperature, sp.seed, j, sp.top_k, sp.top_p)
+                ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype):
+    """One short prompt, 400 decoded tokens over many pages; checked teacher-forced."""
+    from atom_b200 import SamplingParams
+    name = "C"      # has sliding-window layers: pages are given back while decoding
+    cfg, w = _plain(model_dirs[name])
+    prompt = tiny.prompts(name, [6], seed=9)[0]
+    eng = _engine(model_dirs[name], dtype, pages=32, page=16)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=400, ignore_eos=True))[0]
+    assert out["num_tokens_output"] == 400
+    _check_greedy_against_plain(cfg, w, prompt, out["token_ids"], margin=0 if dtype == "float32" else 0.08)
+
+
+def test_stop_token_and_eos(model_dirs):
+    from atom_b200 import SamplingParams
+    name = "A"
+    cfg, w = _plain(model_dirs[name])
+    prompt = tiny.prompts(name, [11], seed=2)[0]
+    ref = plain.generate_greedy(cfg, w, prompt, 8)
+    eng = _engine(model_dirs[name], "float32", pages=16, page=16)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[ref[3]]))[0]
+    first = ref.index(ref[3])
+    assert out["token_ids"] == ref[:first + 1] and out["finish_reason"] == f"stop_{ref[3]}"
+
+
+def test_command_line(model_dirs, capsys):
+    from atom_b200.examples import simple_inference
+    rc = simple_inference.main(["--model", model_dirs["A"], "--dtype", "float32", "--temperature", "0",
+                                "--max-tokens", "5", "--num-kvcache-blocks", "16", "--enforce-eager",
+                                "--prompt-token-ids", "5,17,3", "--ignore-eos"])
+    assert rc == 0
+    text = capsys.readouterr().out
+    cfg, w = _plain(model_dirs["A"])
+    assert "Prompt: [5, 17, 3]" in text and f"Completion: {plain.generate_greedy(cfg, w, [5, 17, 3], 5)!r}" in text
