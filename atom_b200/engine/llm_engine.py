@@ -56,6 +56,7 @@ class LLMEngine:
         self.num_steps = 0
         self.num_prompt_tokens = 0
         self.num_generated_tokens = 0
+        self.d2h_bytes = 0      # bytes of sampled token ids read back to the host so far
 
     # ------------------------------------------------------------------ requests
 
@@ -109,6 +110,7 @@ class LLMEngine:
                 logits, [s.params for s in sampling], [self._seed_of(s) for s in sampling],
                 [s.num_output_tokens for s in sampling])
             tokens = ids.tolist()
+            self.d2h_bytes += 4 * len(tokens)
         self.num_steps += 1
         self.num_prompt_tokens += sum(e.num_tokens for e in sched.entries if not (e.samples and e.num_tokens == 1))
         self.num_generated_tokens += len(tokens)

@@ -69,6 +69,7 @@ class ModelRunner:
         self._staging_events: List[Optional[torch.cuda.Event]] = [None] * 4
         self._staging_next = 0
         self.steps_run = 0
+        self.h2d_bytes = 0      # bytes of step metadata copied host -> device so far
 
     # ------------------------------------------------------------------ sizing
 
@@ -194,6 +195,7 @@ class ModelRunner:
                 bt[i, :len(t)] = t
         dev = self._meta_dev
         dev[:total].copy_(self._staging[k][:total], non_blocking=True)
+        self.h2d_bytes += 4 * total
         ev = torch.cuda.Event()
         ev.record()
         self._staging_events[k] = ev

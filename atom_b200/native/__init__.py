@@ -20,7 +20,8 @@ _ERR = {1: "argument the kernel does not take", 2: "CUDA launch failed", 3: "lib
 
 _lib = None
 _lock = threading.Lock()
-launches = 0  # number of kernel-library calls made by this process (a launch counter)
+launches = 0        # launches of this library's own kernels made by this process
+library_gemms = 0   # calls into the vendor GEMM library (counted apart from own kernels)
 
 
 class NativeError(RuntimeError):
@@ -88,9 +89,12 @@ def declare(name: str, args) -> None:
         fn.restype = ctypes.c_int
 
 
-def _check(code: int, name: str) -> None:
-    global launches
-    launches += 1
+def _check(code: int, name: str, own: bool = True) -> None:
+    global launches, library_gemms
+    if own:
+        launches += 1
+    else:
+        library_gemms += 1
     if code != 0:
         raise NativeError(f"{name}: {_ERR.get(code, f'error {code}')}")
 
@@ -239,7 +243,8 @@ def gemm_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
     assert a.stride(1) == 1 and out.is_contiguous() and w.is_contiguous()
     ws = _workspace(out.device)
     _check(lib().atom_gemm_bf16(out.data_ptr(), dtype_code(out.dtype), a.data_ptr(), w.data_ptr(), M, N,
-                                K, a.stride(0), ws.data_ptr(), ws.numel(), _stream()), "gemm_bf16")
+                                K, a.stride(0), ws.data_ptr(), ws.numel(), _stream()), "gemm_bf16",
+           own=False)
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

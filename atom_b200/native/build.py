@@ -183,5 +183,10 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str]) 
     return lib
 
 
+def build_all(verbose: bool = True) -> str:
+    """Compiles everything the package can need (the build check); returns the library path."""
+    return build(verbose=verbose)
+
+
 if __name__ == "__main__":
-    print(build())
+    print(build_all())

@@ -20,6 +20,7 @@ class Sampler:
         self.device = torch.device(device)
         self.default_seed = default_seed
         self._probs = None
+        self.h2d_bytes = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int]) -> torch.Tensor:
@@ -38,6 +39,7 @@ class Sampler:
             host[4, r] = p.top_p
             any_filter = any_filter or (p.filters and not p.greedy)
         dev = torch.from_numpy(host).to(self.device, non_blocking=False)
+        self.h2d_bytes += host.nbytes
         out = torch.empty(R, dtype=torch.int32, device=self.device)
         probs = None
         if any_filter:
