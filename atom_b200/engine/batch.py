@@ -43,6 +43,7 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     logits_out: Optional[torch.Tensor] = None   # where the head writes, if preallocated
+    plans: Dict = field(default_factory=dict)    # launch plans that parts share within the step
 
 
 def pack_layout(T: int, S: int, R: int, widths: Sequence[int]):

@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from .build import NativeBuildError, build
+from .build import NativeBuildError, build, build_variant
 
 F32, BF16 = 0, 1
 _ERR = {1: "argument the kernel does not take", 2: "CUDA launch failed", 3: "library call failed"}
@@ -253,3 +253,83 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     assert out.is_contiguous() and bias.numel() == N
     _check(lib().atom_add_bias(out.data_ptr(), dtype_code(out.dtype), bias.data_ptr(),
                                dtype_code(bias.dtype), M, N, _stream()), "add_bias")
+
+
+# --------------------------------------------------------------------------- tensor-core attention
+
+_flash_libs = {}
+_FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i,
+              _vp, _vp]
+
+
+def flash_supports(hd: int, dtype: torch.dtype) -> bool:
+    """The tensor-core attention takes bfloat16 and head sizes that are multiples of 16 up to 256."""
+    return dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 256
+
+
+def flash_lib(hd: int):
+    """The attention library compiled for this head size (built on first use)."""
+    l = _flash_libs.get(hd)
+    if l is None:
+        with _lock:
+            l = _flash_libs.get(hd)
+            if l is None:
+                path = build_variant("attention_flash.cu", {"ATOM_HD": hd})
+                l = ctypes.CDLL(path)
+                l.atom_flash_attention.argtypes = _FLASH_SIG
+                l.atom_flash_attention.restype = ctypes.c_int
+                l.atom_flash_scratch_bytes.argtypes = [_i, _i, _i]
+                l.atom_flash_scratch_bytes.restype = ctypes.c_int64
+                if l.atom_flash_head_dim() != hd:
+                    raise NativeBuildError(f"{path} was built for another head size")
+                _flash_libs[hd] = l
+    return l
+
+
+def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sm_count: int = 148):
+    """Host-side launch plan: (64-row tiles of the long requests, any short request?, splits).
+
+    Short requests (at most 16 packed rows) are split along their keys so that about two
+    waves of CTAs stream the cache, each split at least 256 keys long."""
+    tiles, short = 0, 0
+    for n in q_lens:
+        rows = n * group
+        if rows > 16:
+            tiles += -(-rows // 64)
+        elif rows > 0:
+            short += 1
+    splits = 1
+    if short:
+        want = -(-4 * sm_count // max(1, len(q_lens) * nkv))
+        splits = max(1, min(want, -(-max_ctx // 256), 64))
+    return tiles, short > 0, splits
+
+
+def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: torch.Tensor,
+                    v_pages: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor,
+                    ctx_len: torch.Tensor, seq_of_token: torch.Tensor, T: int, num_seqs: int, nh: int,
+                    nkv: int, hd: int, scale: float, window: int, plan, scratch: Optional[torch.Tensor]) -> None:
+    """out[T, nh*hd] (bf16): causal attention of every token over its request's pages, on the
+    tensor cores.  ``plan`` comes from ``flash_plan``; ``scratch`` (float32) must hold
+    ``flash_scratch_elems`` elements when the plan has more than one split."""
+    _cuda(out, q, k_pages, v_pages, block_table, cu_q, ctx_len, seq_of_token, scratch)
+    page_size = k_pages.shape[2]
+    assert out.dtype == q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, hd) and v_pages.shape == k_pages.shape
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    assert cu_q.dtype == ctx_len.dtype == seq_of_token.dtype == torch.int32
+    tiles, has_short, splits = plan
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32
+        assert scratch.numel() >= flash_scratch_elems(T, nh, hd, splits)
+    l = flash_lib(hd)
+    _check(l.atom_flash_attention(
+        out.data_ptr(), q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
+        seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(tiles),
+        int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")
+
+
+def flash_scratch_elems(T: int, nh: int, hd: int, splits: int) -> int:
+    return 0 if splits <= 1 else T * nh * splits * (hd + 2)

@@ -50,25 +50,38 @@ def find_nvcc() -> str:
     raise NativeBuildError("nvcc not found (looked in $CUDA_HOME/bin, /usr/local/cuda/bin, PATH)")
 
 
+_build_dir: Optional[str] = None
+_build_dir_lock = threading.Lock()
+
+
 def build_dir() -> str:
-    """Where objects and the library go: inside the package if writable."""
-    d = os.path.join(_HERE, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return d
-    except OSError:
-        tag = hashlib.sha1(_HERE.encode()).hexdigest()[:10]
-        d = os.path.join(tempfile.gettempdir(), f"atom_b200_build_{os.getuid()}_{tag}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """Where objects and the libraries go: inside the package if writable, else a per-user
+    folder under the system's temporary directory."""
+    global _build_dir
+    with _build_dir_lock:
+        if _build_dir is None:
+            d = os.path.join(_HERE, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                probe = os.path.join(d, f".w{os.getpid()}")
+                with open(probe, "w"):
+                    pass
+                os.remove(probe)
+            except OSError:
+                tag = hashlib.sha1(_HERE.encode()).hexdigest()[:10]
+                d = os.path.join(tempfile.gettempdir(), f"atom_b200_build_{os.getuid()}_{tag}")
+                os.makedirs(d, exist_ok=True)
+            _build_dir = d
+        return _build_dir
+
+
+# Sources that are compiled per variant (one library per value of their -D parameters), on
+# first use by a model that needs that variant; everything else goes into the core library.
+VARIANT_SOURCES = {"attention_flash.cu"}
 
 
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu") and f not in VARIANT_SOURCES)
 
 
 def _headers_hash() -> str:
@@ -96,23 +109,37 @@ def _run(cmd: List[str], what: str) -> None:
         raise NativeBuildError(f"{what} failed:\n{' '.join(cmd)}\n{p.stdout}")
 
 
-def build(verbose: bool = True, extra_defines: Optional[Dict[str, str]] = None) -> str:
-    """Compiles what is out of date and returns the path of the shared library."""
+def build(verbose: bool = True) -> str:
+    """Compiles what is out of date of the core library and returns its path."""
+    return _build(LIB_NAME, sources(), {}, verbose, ["-lcublas"])
+
+
+def build_variant(source: str, defines: Dict[str, object], verbose: bool = True) -> str:
+    """Compiles one variant source with its -D parameters into a library of its own, e.g.
+    attention_flash.cu with ATOM_HD=128 -> libatom_attention_flash_ATOM_HD128.so."""
+    if source not in VARIANT_SOURCES:
+        raise NativeBuildError(f"{source} is not a variant source")
+    tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items()))
+    name = f"libatom_{os.path.splitext(source)[0]}_{tag}.so"
+    return _build(name, [source], {k: str(v) for k, v in defines.items()}, verbose, [])
+
+
+def _build(lib_name: str, srcs: List[str], defines: Dict[str, str], verbose: bool, link_libs: List[str]) -> str:
     nvcc = find_nvcc()
     bdir = build_dir()
-    lock_path = os.path.join(bdir, ".lock")
+    lock_path = os.path.join(bdir, f".lock.{lib_name}")
     with open(lock_path, "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
-            return _build_locked(nvcc, bdir, verbose, extra_defines or {})
+            return _build_locked(nvcc, bdir, verbose, defines, lib_name, srcs, link_libs)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
-def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str]) -> str:
+def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str], lib_name: str,
+                  srcs: List[str], link_libs: List[str]) -> str:
     flags = ARCH_FLAGS + NVCC_FLAGS + [f"-D{k}={v}" for k, v in sorted(defines.items())]
     hdr = _headers_hash()
-    srcs = sources()
     if not srcs:
         raise NativeBuildError(f"no .cu sources under {CSRC}")
     objs, todo = [], []
@@ -123,8 +150,8 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str]) 
         if not os.path.isfile(obj):
             todo.append((s, obj))
     link_key = hashlib.sha1("".join(os.path.basename(o) for o in objs).encode()).hexdigest()[:16]
-    lib = os.path.join(bdir, LIB_NAME)
-    stamp = os.path.join(bdir, "link.stamp")
+    lib = os.path.join(bdir, lib_name)
+    stamp = os.path.join(bdir, lib_name + ".stamp")
     linked = ""
     if os.path.isfile(stamp) and os.path.isfile(lib):
         with open(stamp) as f:
@@ -133,7 +160,7 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str]) 
         return lib
 
     if todo and verbose:
-        _log(f"compiling {len(todo)} CUDA source(s) for sm_100a into {bdir} (first call only)")
+        _log(f"compiling {len(todo)} CUDA source(s) of {lib_name} for sm_100a into {bdir} (first call only)")
     t0 = time.time()
     done = [0]
     stop = threading.Event()
@@ -159,33 +186,38 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str]) 
         if todo:
             with concurrent.futures.ThreadPoolExecutor(workers) as ex:
                 list(ex.map(compile_one, todo))
-        # Remove objects of older source versions.
+        # Remove objects of older versions of these sources.
         keep = {os.path.basename(o) for o in objs}
+        stems = {os.path.splitext(x)[0] for x in srcs}
         for f in os.listdir(bdir):
-            if f.endswith(".o") and f not in keep:
+            if f.endswith(".o") and f not in keep and f.split(".")[0] in stems and len(stems) > 1:
                 try:
                     os.remove(os.path.join(bdir, f))
                 except OSError:
                     pass
         tmp = lib + f".tmp{os.getpid()}"
         cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
-        _run(
-            [nvcc, "-shared", "-o", tmp] + objs + ["-L", cuda_lib, "-lcublas"],
-            "link",
-        )
+        _run([nvcc, "-shared", "-o", tmp] + objs + ["-L", cuda_lib] + link_libs, "link")
         os.replace(tmp, lib)
         with open(stamp, "w") as f:
             f.write(link_key)
     finally:
         stop.set()
     if verbose:
-        _log(f"built {LIB_NAME} in {time.time() - t0:.1f} s")
+        _log(f"built {lib_name} in {time.time() - t0:.1f} s")
     return lib
 
 
+# Head sizes whose attention variant the build check compiles ahead of use.
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 128, 256)
+
+
 def build_all(verbose: bool = True) -> str:
-    """Compiles everything the package can need (the build check); returns the library path."""
-    return build(verbose=verbose)
+    """Compiles the core library and the usual variants (the build check); returns the core's path."""
+    core = build(verbose=verbose)
+    with concurrent.futures.ThreadPoolExecutor(max(1, min(len(PREBUILT_HEAD_DIMS), os.cpu_count() or 1))) as ex:
+        list(ex.map(lambda hd: build_variant("attention_flash.cu", {"ATOM_HD": hd}, verbose), PREBUILT_HEAD_DIMS))
+    return core
 
 
 if __name__ == "__main__":

@@ -1,0 +1,583 @@
+// Paged causal attention on the tensor cores (bf16 operands, 32-bit softmax and accumulation),
+// for one head size fixed at compile time (-DATOM_HD=<multiple of 16, at most 256>).
+//
+// A step's batch holds, per request s, q_len(s) new tokens at positions
+// [ctx_len(s) - q_len(s), ctx_len(s)); their keys and values are already in the pages.  Query
+// rows of the G = nh / nkv heads that share one kv head are packed into one tile
+// (row = token * G + head in group), so a tile reads each key once for all G heads.
+//
+//   portions (more than 16 packed rows): one CTA = 64 rows of one (request, kv head); its 4
+//       warps take 16 rows each and walk over the keys in tiles of 64.
+//   short (at most 16 packed rows: decoded tokens, portions of a few tokens): one CTA = one
+//       (request, kv head, split of the keys); its 4 warps take 16 keys each of every tile of
+//       64 and are merged at the end.  With more than one split the CTA writes unnormalised
+//       partial sums with their maximum and denominator to scratch, and a second kernel
+//       merges the splits.
+//
+// Keys of a tile come into shared memory with cp.async (rows beyond the request's length, or
+// on pages a window has given back, are zero-filled), in a ring of stages; S = Q K^T and
+// O += P V run on mma.sync.m16n8k16 with P rounded to bf16.
+#include "common.cuh"
+
+#ifndef ATOM_HD
+#error "compile with -DATOM_HD=<head size>"
+#endif
+
+namespace atom {
+namespace flash {
+
+constexpr int HD = ATOM_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16, at most 256");
+constexpr int LDS = HD + 8;   // shared-memory row stride in elements: rows shift by one 16-byte bank group
+constexpr int BN = 64;        // keys per tile
+constexpr int BM = 64;        // packed query rows per CTA (portions)
+constexpr int NT = 128;       // threads per CTA
+constexpr int CH = HD / 8;    // 16-byte chunks per row
+constexpr bool Q_IN_REGS = HD <= 128;
+
+struct Params {
+  __nv_bfloat16* out;          // [T, nh * HD]
+  const __nv_bfloat16* q;      // token t, head h at q + t * q_stride + h * HD
+  int64_t q_stride;
+  const __nv_bfloat16* k_pages;  // [pages, nkv, page_size, HD]
+  const __nv_bfloat16* v_pages;
+  const int* block_table;      // [S, max_pages]
+  int max_pages, page_size, page_shift;   // page_shift >= 0 when page_size is a power of two
+  const int* cu_q;             // [S + 1]
+  const int* ctx_len;          // [S] tokens of the request in the cache after this step
+  int num_seqs, nh, nkv, group;
+  float scale_log2;            // scale * log2(e)
+  int window;                  // <= 0: all keys
+  int num_splits;
+  float* part_o;               // [T, nh, num_splits, HD]
+  float* part_ml;              // [T, nh, num_splits, 2]
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// What one CTA works on.
+struct Work {
+  int seq, kvh;
+  int q_begin;        // first token row of the request in the batch
+  int q_start;        // position of the request's first new token
+  int rows_total;     // q_len * group
+  int row0;           // first packed row of this CTA
+  int ctx;            // ctx_len
+  const int* bt;
+};
+
+// Copies keys and values [tile * BN, tile * BN + BN) of the request into one stage.
+__device__ __forceinline__ void load_kv_tile(const Params& p, const Work& w, int tile, int key_end,
+                                             __nv_bfloat16* sK, __nv_bfloat16* sV) {
+  const int64_t head_stride = (int64_t)p.page_size * HD;
+  const int64_t page_stride = head_stride * p.nkv;
+  for (int c = threadIdx.x; c < BN * CH; c += NT) {
+    const int row = c / CH, ch = c % CH;
+    const int j = tile * BN + row;
+    bool valid = j < key_end;
+    int64_t off = 0;
+    if (valid) {
+      const int lp = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+      const int in_page = j - lp * p.page_size;
+      const int page = w.bt[lp];
+      valid = page >= 0;
+      if (valid) off = (int64_t)page * page_stride + (int64_t)w.kvh * head_stride + (int64_t)in_page * HD + ch * 8;
+    }
+    cp_async16(sK + row * LDS + ch * 8, p.k_pages + off, valid);
+    cp_async16(sV + row * LDS + ch * 8, p.v_pages + off, valid);
+  }
+}
+
+// Copies ROWS packed query rows starting at w.row0 into shared memory (zero beyond the last).
+template <int ROWS>
+__device__ __forceinline__ void load_q_tile(const Params& p, const Work& w, __nv_bfloat16* sQ) {
+  for (int c = threadIdx.x; c < ROWS * CH; c += NT) {
+    const int row = c / CH, ch = c % CH;
+    const int R = w.row0 + row;
+    const bool valid = R < w.rows_total;
+    int64_t off = 0;
+    if (valid) {
+      const int tok = R / p.group, hig = R - tok * p.group;
+      off = (int64_t)(w.q_begin + tok) * p.q_stride + (int64_t)(w.kvh * p.group + hig) * HD + ch * 8;
+    }
+    cp_async16(sQ + row * LDS + ch * 8, p.q + off, valid);
+  }
+}
+
+// Per-warp running state of 16 query rows: this thread holds rows g and g + 8.
+struct Acc {
+  float o[HD / 8][4];
+  float m[2], l[2];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+  }
+};
+
+// One tile step of a warp: 16 query rows (fragments in qf or read from sQ) against KT * 8
+// keys starting at row `kw` of the stage.  pos0 / pos1: positions of the thread's two rows
+// (-1: row does not exist).  key0: index of the stage's first key.
+template <int KT>
+__device__ __forceinline__ void warp_tile(Acc& acc, uint32_t (*qf)[4], const __nv_bfloat16* sQw,
+                                          const __nv_bfloat16* sK, const __nv_bfloat16* sV, int kw,
+                                          int key0, int pos0, int pos1, int window, float c, bool mask) {
+  const int lane = threadIdx.x & 31;
+  float s[KT][4];
+#pragma unroll
+  for (int i = 0; i < KT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+
+  // S = Q K^T
+  {
+    const int mat = lane >> 3, r8 = lane & 7;
+    const __nv_bfloat16* kbase = sK + (kw + (mat >> 1) * 8 + r8) * LDS + (mat & 1) * 8;
+    const __nv_bfloat16* qbase = sQw + ((mat & 1) * 8 + r8) * LDS + (mat >> 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t a[4];
+      if (Q_IN_REGS) {
+        a[0] = qf[ks][0]; a[1] = qf[ks][1]; a[2] = qf[ks][2]; a[3] = qf[ks][3];
+      } else {
+        ldmatrix_x4(a, qbase + ks * 16);
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < KT / 2; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kbase + n2 * 16 * LDS + ks * 16);
+        mma_bf16(s[2 * n2], a, b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+  }
+
+  // mask
+  if (mask) {
+    const int t4 = lane & 3;
+#pragma unroll
+    for (int n = 0; n < KT; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = key0 + kw + n * 8 + 2 * t4 + (e & 1);
+        const int pos = (e < 2) ? pos0 : pos1;
+        bool ok = j <= pos;
+        if (window > 0) ok = ok && (j > pos - window);
+        if (!ok) s[n][e] = -INFINITY;
+      }
+    }
+  }
+
+  // online softmax
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < KT; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * r], s[n][2 * r + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(acc.m[r], mx);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float corr = exp2f((acc.m[r] - m_use) * c);
+    acc.m[r] = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int n = 0; n < KT; ++n) {
+      const float p0 = exp2f((s[n][2 * r] - m_use) * c);
+      const float p1 = exp2f((s[n][2 * r + 1] - m_use) * c);
+      s[n][2 * r] = p0;
+      s[n][2 * r + 1] = p1;
+      sum += p0 + p1;
+    }
+    acc.l[r] = acc.l[r] * corr + sum;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      acc.o[d][2 * r] *= corr;
+      acc.o[d][2 * r + 1] *= corr;
+    }
+  }
+
+  // O += P V
+  {
+    const int mat = lane >> 3, r8 = lane & 7;
+    const __nv_bfloat16* vbase = sV + (kw + (mat & 1) * 8 + r8) * LDS + (mat >> 1) * 8;
+#pragma unroll
+    for (int kk = 0; kk < KT / 2; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int d2 = 0; d2 < HD / 16; ++d2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vbase + kk * 16 * LDS + d2 * 16);
+        mma_bf16(acc.o[2 * d2], a, b[0], b[1]);
+        mma_bf16(acc.o[2 * d2 + 1], a, b[2], b[3]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void load_q_frags(uint32_t (*qf)[4], const __nv_bfloat16* sQw) {
+  const int lane = threadIdx.x & 31;
+  const int mat = lane >> 3, r8 = lane & 7;
+  const __nv_bfloat16* qbase = sQw + ((mat & 1) * 8 + r8) * LDS + (mat >> 1) * 8;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[ks], qbase + ks * 16);
+}
+
+// ------------------------------------------------------------------ portions
+
+constexpr int PREFILL_STAGES = 2;
+constexpr size_t prefill_smem_bytes() {
+  return sizeof(__nv_bfloat16) * (size_t)(BM * LDS + PREFILL_STAGES * 2 * BN * LDS);
+}
+
+__global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* sKV = sQ + BM * LDS;
+
+  // Which (request, row tile) is this CTA?  Requests with at most 16 packed rows belong to
+  // the other kernel.  Within a request the last (longest) tiles come first.
+  Work w;
+  {
+    int tile = blockIdx.x, s = 0, nt = 0;
+    for (; s < p.num_seqs; ++s) {
+      const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
+      nt = rows > 16 ? (rows + BM - 1) / BM : 0;
+      if (tile < nt) break;
+      tile -= nt;
+    }
+    if (s == p.num_seqs) return;
+    w.seq = s;
+    w.kvh = blockIdx.y;
+    w.q_begin = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - w.q_begin;
+    w.ctx = p.ctx_len[s];
+    w.q_start = w.ctx - q_len;
+    w.rows_total = q_len * p.group;
+    w.row0 = (nt - 1 - tile) * BM;
+    w.bt = p.block_table + (int64_t)s * p.max_pages;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+
+  const int row_last = min(w.row0 + BM, w.rows_total) - 1;
+  const int pos_first = w.q_start + w.row0 / p.group;
+  const int pos_last = w.q_start + row_last / p.group;
+  const int key_end = pos_last + 1;
+  int key_lo = 0;
+  if (p.window > 0) key_lo = max(0, pos_first - p.window + 1);
+  const int tile_begin = key_lo / BN, tile_end = (key_end + BN - 1) / BN;
+
+  load_q_tile<BM>(p, w, sQ);
+  load_kv_tile(p, w, tile_begin, key_end, sKV, sKV + BN * LDS);
+  cp_async_commit();
+
+  const int R0 = w.row0 + warp * 16 + g, R1 = R0 + 8;
+  const int pos0 = R0 < w.rows_total ? w.q_start + R0 / p.group : -1;
+  const int pos1 = R1 < w.rows_total ? w.q_start + R1 / p.group : -1;
+  // Positions of this warp's first and last row decide which tiles need the mask.
+  const int wr_first = w.row0 + warp * 16, wr_last = min(wr_first + 15, w.rows_total - 1);
+  const int wpos_first = w.q_start + wr_first / p.group;
+  const int wpos_last = w.q_start + max(wr_last, wr_first) / p.group;
+  const bool warp_has_rows = wr_first < w.rows_total;
+
+  Acc acc;
+  acc.init();
+  uint32_t qf[Q_IN_REGS ? HD / 16 : 1][4];
+  const __nv_bfloat16* sQw = sQ + warp * 16 * LDS;
+
+  for (int t = tile_begin; t < tile_end; ++t) {
+    const int st = (t - tile_begin) & 1;
+    __nv_bfloat16* sK = sKV + st * 2 * BN * LDS;
+    __nv_bfloat16* sV = sK + BN * LDS;
+    cp_async_wait<0>();
+    __syncthreads();
+    if (t + 1 < tile_end) {
+      __nv_bfloat16* nK = sKV + (st ^ 1) * 2 * BN * LDS;
+      load_kv_tile(p, w, t + 1, key_end, nK, nK + BN * LDS);
+    }
+    cp_async_commit();
+    if (t == tile_begin && Q_IN_REGS) load_q_frags(qf, sQw);
+    const int key0 = t * BN;
+    // Skip tiles that lie wholly after this warp's last position (another warp needs them).
+    if (!warp_has_rows || key0 > wpos_last) continue;
+    bool mask = (key0 + BN - 1 > wpos_first) || !(wr_first + 15 < w.rows_total);
+    if (p.window > 0) mask = mask || (key0 <= wpos_last - p.window);
+    warp_tile<BN / 8>(acc, qf, sQw, sK, sV, 0, key0, pos0, pos1, p.window, p.scale_log2, mask);
+  }
+  cp_async_wait<0>();
+
+  // normalise and write
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = acc.l[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int R = r == 0 ? R0 : R1;
+    if (R >= w.rows_total) continue;
+    const float inv = 1.f / l;
+    const int tok = R / p.group, hig = R - tok * p.group;
+    __nv_bfloat16* orow = p.out + ((int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig)) * HD;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      *reinterpret_cast<__nv_bfloat162*>(orow + d * 8 + 2 * t4) =
+          __floats2bfloat162_rn(acc.o[d][2 * r] * inv, acc.o[d][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ short requests (decode)
+
+constexpr int DECODE_STAGES = 3;
+constexpr size_t decode_smem_bytes() {
+  const size_t ring = sizeof(__nv_bfloat16) * (size_t)(16 * LDS + DECODE_STAGES * 2 * BN * LDS);
+  const size_t merge = sizeof(float) * (size_t)(4 * 16 * (HD + 2));
+  return ring > merge ? ring : merge;
+}
+
+__global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* sKV = sQ + 16 * LDS;
+
+  Work w;
+  w.seq = blockIdx.x;
+  w.kvh = blockIdx.y;
+  const int split = blockIdx.z;
+  w.q_begin = p.cu_q[w.seq];
+  const int q_len = p.cu_q[w.seq + 1] - w.q_begin;
+  w.rows_total = q_len * p.group;
+  if (w.rows_total <= 0 || w.rows_total > 16) return;
+  w.ctx = p.ctx_len[w.seq];
+  w.q_start = w.ctx - q_len;
+  w.row0 = 0;
+  w.bt = p.block_table + (int64_t)w.seq * p.max_pages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int key_end = w.ctx;
+  int key_lo = 0;
+  if (p.window > 0) key_lo = max(0, w.q_start - p.window + 1);
+  const int first_tile = key_lo / BN, n_tiles = (key_end + BN - 1) / BN - first_tile;
+  const int per_split = (n_tiles + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int tile_end = min(tile_begin + per_split, first_tile + n_tiles);
+
+  const int pos0 = g < w.rows_total ? w.q_start + g / p.group : -1;
+  const int pos1 = g + 8 < w.rows_total ? w.q_start + (g + 8) / p.group : -1;
+
+  Acc acc;
+  acc.init();
+  if (tile_begin < tile_end) {
+    load_q_tile<16>(p, w, sQ);
+#pragma unroll
+    for (int i = 0; i < DECODE_STAGES - 1; ++i) {
+      if (tile_begin + i < tile_end) {
+        __nv_bfloat16* sK = sKV + i * 2 * BN * LDS;
+        load_kv_tile(p, w, tile_begin + i, key_end, sK, sK + BN * LDS);
+      }
+      cp_async_commit();
+    }
+    uint32_t qf[Q_IN_REGS ? HD / 16 : 1][4];
+    for (int t = tile_begin; t < tile_end; ++t) {
+      const int st = (t - tile_begin) % DECODE_STAGES;
+      __nv_bfloat16* sK = sKV + st * 2 * BN * LDS;
+      __nv_bfloat16* sV = sK + BN * LDS;
+      cp_async_wait<DECODE_STAGES - 2>();
+      __syncthreads();
+      const int nx = t + DECODE_STAGES - 1;
+      if (nx < tile_end) {
+        __nv_bfloat16* nK = sKV + ((nx - tile_begin) % DECODE_STAGES) * 2 * BN * LDS;
+        load_kv_tile(p, w, nx, key_end, nK, nK + BN * LDS);
+      }
+      cp_async_commit();
+      if (t == tile_begin && Q_IN_REGS) load_q_frags(qf, sQ);
+      warp_tile<2>(acc, qf, sQ, sK, sV, warp * 16, t * BN, pos0, pos1, p.window, p.scale_log2, true);
+    }
+    cp_async_wait<0>();
+  }
+  __syncthreads();   // the ring is free: it becomes the merge buffer
+
+  // Merge the four warps (each saw other keys).
+  float* mo = reinterpret_cast<float*>(smem_raw);       // [4][16][HD]
+  float* mm = mo + 4 * 16 * HD;                          // [4][16]
+  float* ml = mm + 4 * 16;                               // [4][16]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = acc.l[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = g + 8 * r;
+    if (t4 == 0) {
+      mm[warp * 16 + row] = acc.m[r];
+      ml[warp * 16 + row] = l;
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      float2 v = make_float2(acc.o[d][2 * r], acc.o[d][2 * r + 1]);
+      *reinterpret_cast<float2*>(mo + (warp * 16 + row) * HD + d * 8 + 2 * t4) = v;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < w.rows_total * HD; idx += NT) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) M = fmaxf(M, mm[k * 16 + row]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float f = exp2f((mm[k * 16 + row] - Mu) * p.scale_log2);
+      L += ml[k * 16 + row] * f;
+      O += mo[(k * 16 + row) * HD + d] * f;
+    }
+    const int tok = row / p.group, hig = row - tok * p.group;
+    const int64_t th = (int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig);
+    if (p.num_splits == 1) {
+      p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+    } else {
+      p.part_o[(th * p.num_splits + split) * HD + d] = O;
+      if (d == 0) {
+        p.part_ml[(th * p.num_splits + split) * 2] = M;
+        p.part_ml[(th * p.num_splits + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merges the splits of every (token, head) of the short requests: one warp each.
+__global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_of_token, int T) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= T * p.nh) return;
+  const int t = warp / p.nh;
+  const int s = seq_of_token[t];
+  const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
+  if (rows > 16) return;
+  const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;
+  const float* po = p.part_o + (int64_t)warp * p.num_splits * HD;
+  float M = -INFINITY;
+  for (int k = 0; k < p.num_splits; ++k) M = fmaxf(M, ml[2 * k]);
+  const float Mu = (M == -INFINITY) ? 0.f : M;
+  float L = 0.f;
+  for (int k = 0; k < p.num_splits; ++k) L += ml[2 * k + 1] * exp2f((ml[2 * k] - Mu) * p.scale_log2);
+  const float inv = 1.f / L;
+  for (int d = lane; d < HD; d += 32) {
+    float O = 0.f;
+    for (int k = 0; k < p.num_splits; ++k) O += po[k * HD + d] * exp2f((ml[2 * k] - Mu) * p.scale_log2);
+    p.out[(int64_t)warp * HD + d] = __float2bfloat16_rn(O * inv);
+  }
+}
+
+}  // namespace flash
+}  // namespace atom
+
+#define ATOM_CAT_(a, b) a##b
+#define ATOM_CAT(a, b) ATOM_CAT_(a, b)
+
+// Head size this library was compiled for.
+ATOM_EXPORT int atom_flash_head_dim() { return atom::flash::HD; }
+
+// Bytes of scratch that `num_splits` splits need for T tokens.
+ATOM_EXPORT int64_t atom_flash_scratch_bytes(int T, int nh, int num_splits) {
+  return num_splits <= 1 ? 0 : (int64_t)T * nh * num_splits * (atom::flash::HD + 2) * (int64_t)sizeof(float);
+}
+
+// prefill_tiles: sum over requests with more than 16 packed rows of ceil(rows / 64); 0: none.
+// has_short: some request has at most 16 packed rows.  scratch: atom_flash_scratch_bytes bytes
+// when num_splits > 1.
+ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride, const void* k_pages,
+                                     const void* v_pages, const int* block_table, int max_pages,
+                                     int page_size, const int* cu_q, const int* ctx_len,
+                                     const int* seq_of_token, int T, int num_seqs, int nh, int nkv,
+                                     int hd, float scale, int window, int prefill_tiles, int has_short,
+                                     int num_splits, void* scratch, cudaStream_t stream) {
+  using namespace atom::flash;
+  if (T <= 0 || num_seqs <= 0) return ATOM_OK;
+  if (hd != HD || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || num_splits < 1 ||
+      nkv > 65535 || num_splits > 65535 || (q_stride % 8) != 0 || (num_splits > 1 && scratch == nullptr) ||
+      !(scale > 0.f))
+    return ATOM_ERR_ARG;
+  Params p;
+  p.out = (__nv_bfloat16*)out;
+  p.q = (const __nv_bfloat16*)q;
+  p.q_stride = q_stride;
+  p.k_pages = (const __nv_bfloat16*)k_pages;
+  p.v_pages = (const __nv_bfloat16*)v_pages;
+  p.block_table = block_table;
+  p.max_pages = max_pages;
+  p.page_size = page_size;
+  p.page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    int s = 0;
+    while ((1 << s) < page_size) ++s;
+    p.page_shift = s;
+  }
+  p.cu_q = cu_q;
+  p.ctx_len = ctx_len;
+  p.num_seqs = num_seqs;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.group = nh / nkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.num_splits = num_splits;
+  p.part_o = (float*)scratch;
+  p.part_ml = p.part_o ? p.part_o + (int64_t)T * nh * num_splits * HD : nullptr;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)prefill_smem_bytes()) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)decode_smem_bytes()) != cudaSuccess)
+      return ATOM_ERR_LAUNCH;
+    attr_set = true;
+  }
+  if (prefill_tiles > 0) {
+    dim3 grid(prefill_tiles, nkv);
+    flash_prefill_kernel<<<grid, NT, prefill_smem_bytes(), stream>>>(p);
+  }
+  if (has_short) {
+    dim3 grid(num_seqs, nkv, num_splits);
+    flash_decode_kernel<<<grid, NT, decode_smem_bytes(), stream>>>(p);
+    if (num_splits > 1) {
+      const int warps = T * nh;
+      flash_merge_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(p, seq_of_token, T);
+    }
+  }
+  return atom::check_launch();
+}

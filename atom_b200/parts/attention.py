@@ -81,7 +81,23 @@ class PagedAttention(Mixer):
         return linear(o, self.w_o_weight, None, ws.get("attn.out", (T, self.hidden_size), dt))
 
     def attend(self, o, qkv, step, cache, bt) -> None:
-        """Chooses the attention kernel for this step's tokens."""
+        """Chooses the attention kernel for this step's tokens: the tensor-core kernel for
+        bfloat16 and head sizes in steps of 16, else the 32-bit kernel that takes any size."""
+        if native.flash_supports(self.hd, qkv.dtype):
+            T = o.shape[0]
+            plan = step.plans.get(("flash", self.nh, self.nkv))
+            if plan is None:
+                plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len)
+                step.plans[("flash", self.nh, self.nkv)] = plan
+            scratch = None
+            if plan[2] > 1:
+                n = native.flash_scratch_elems(T, self.nh, self.hd, plan[2])
+                scratch = self.rt.workspace.get("attn.splits", (n,), torch.float32)
+            native.flash_attention(
+                o, qkv, qkv.shape[1], cache.k_pages, cache.v_pages, bt, step.cu_q, step.ctx_len,
+                step.seq_of_token, T, step.num_seqs, self.nh, self.nkv, self.hd, self.scale,
+                self.window if self.window else 0, plan, scratch)
+            return
         native.paged_attention_generic(
             o, qkv, qkv.shape[1], cache.k_pages, cache.v_pages, bt, step.positions,
             step.seq_of_token, o.shape[0], self.nh, self.nkv, self.hd, self.scale,

@@ -1,0 +1,369 @@
+"""Each kernel alone against a plain PyTorch 32-bit reference of the same operation, at
+sizes other than the engine's tiny models: widths and vocabularies that are no power of two,
+head sizes in steps of 16, group sizes 1 to 8, pages of 8, 16 and 24 tokens, windows, and
+inputs made so that a single far key decides the result."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def native():
+    from atom_b200 import native as n
+    n.lib()
+    return n
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+
+
+# ----------------------------------------------------------------------------- small kernels
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,T", [(389, 96, 7), (1000, 200, 33), (151, 4104, 3)])
+def test_embedding(native, dtype, V, H, T):
+    table = _rand((V, H), dtype, 1)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2)).to(torch.int32).to(DEV)
+    out = torch.empty((T, H), dtype=torch.float32, device=DEV)
+    native.embedding(out, table, ids)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,T,eps", [(96, 5, 1e-5), (1000, 17, 1e-6), (4104, 3, 3e-6)])
+def test_add_rmsnorm(native, dtype, H, T, eps):
+    res = _rand((T, H), torch.float32, 3)
+    delta = _rand((T, H), dtype, 4)
+    w = (_rand((H,), torch.float32, 5) * 0.1 + 1).to(dtype)
+    r0 = res.clone()
+    out = torch.empty((T, H), dtype=dtype, device=DEV)
+    native.add_rmsnorm(out, res, delta, w, eps)
+    r = r0 + delta.float()
+    want = r * torch.rsqrt((r * r).mean(-1, keepdim=True) + eps) * w.float()
+    assert torch.allclose(res, r, rtol=0, atol=0)
+    torch.testing.assert_close(out.float(), want.to(dtype).float(), **_tol(dtype))
+    # picked rows: normalised densely, the residual stays as it is
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    res2 = r0.clone()
+    out2 = torch.empty((2, H), dtype=dtype, device=DEV)
+    native.add_rmsnorm(out2, res2, delta, w, eps, rows, 2)
+    assert torch.equal(res2, r0)
+    torch.testing.assert_close(out2.float(), want[[T - 1, 0]].to(dtype).float(), **_tol(dtype))
+    # no delta
+    res3 = r0.clone()
+    native.add_rmsnorm(out, res3, None, w, eps)
+    want3 = r0 * torch.rsqrt((r0 * r0).mean(-1, keepdim=True) + eps) * w.float()
+    torch.testing.assert_close(out.float(), want3.to(dtype).float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I,T", [(160, 5), (1001, 9), (12288, 2)])
+def test_silu_mul(native, dtype, I, T):
+    gu = _rand((T, 2 * I), dtype, 6, 2.0)
+    out = torch.empty((T, I), dtype=dtype, device=DEV)
+    native.silu_mul(out, gu)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    torch.testing.assert_close(out.float(), (g * torch.sigmoid(g) * u).to(dtype).float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 389, 96), (37, 130, 257), (129, 64, 1000)])
+def test_gemm_f32_is_true_32_bit(native, M, N, K):
+    a, w = _rand((M, K), torch.float32, 7), _rand((N, K), torch.float32, 8)
+    bias = _rand((N,), torch.float32, 9)
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    native.gemm_f32(out, a, w, bias)
+    want = (a.double() @ w.double().T + bias.double())
+    # a reduced-precision matrix mode (10-bit mantissa) would be off by ~1e-2 here
+    assert (out.double() - want).abs().max().item() < 1e-4 * math.sqrt(K / 96)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 392, 96), (37, 136, 264), (300, 1000, 512)])
+def test_gemm_bf16(native, out_dtype, M, N, K):
+    a, w = _rand((M, K), torch.bfloat16, 10), _rand((N, K), torch.bfloat16, 11)
+    out = torch.empty((M, N), dtype=out_dtype, device=DEV)
+    native.gemm_bf16(out, a, w)
+    want = a.float() @ w.float().T
+    torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+
+
+def _rope_table(max_pos, rd, theta):
+    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float32) / rd))
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    return torch.cat([ang.cos(), ang.sin()], 1).contiguous().to(DEV)
+
+
+def _ref_qknorm_rope(qkv, nh, nkv, hd, qw, kw, eps, table, rd, positions):
+    T = qkv.shape[0]
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+
+    def norm(t, w):
+        if w is None:
+            return t
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.float()
+
+    def rope(t):
+        cs = table[positions.long()]
+        c, s = cs[:, None, :rd // 2], cs[:, None, rd // 2:]
+        x1, x2 = t[..., :rd // 2], t[..., rd // 2:rd]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, t[..., rd:]], -1)
+
+    return rope(norm(q, qw)), rope(norm(k, kw)), v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rd,page,use_norm", [(4, 2, 16, 16, 16, True), (5, 5, 48, 48, 8, True),
+                                                          (8, 1, 128, 64, 24, False), (6, 2, 80, 80, 16, True)])
+def test_qknorm_rope_kvwrite(native, dtype, nh, nkv, hd, rd, page, use_norm):
+    q_lens, starts = [3, 1, 19], [5, 40, 0]
+    S, T = len(q_lens), sum(q_lens)
+    max_pos, eps, theta = 128, 1e-5, 10000.0
+    table = _rope_table(max_pos, rd, theta)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, q_lens)]).to(torch.int32).to(DEV)
+    sot = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEV)
+    n_pages, P = 40, 8
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(12))[: S * P].view(S, P)
+    bt = perm.to(torch.int32).to(DEV)
+    qkv = _rand((T, (nh + 2 * nkv) * hd), dtype, 13)
+    qw = (_rand((hd,), torch.float32, 14) * 0.1 + 1).to(dtype) if use_norm else None
+    kw = (_rand((hd,), torch.float32, 15) * 0.1 + 1).to(dtype) if use_norm else None
+    kp = torch.zeros((n_pages, nkv, page, hd), dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rq, rk, rv = _ref_qknorm_rope(qkv, nh, nkv, hd, qw, kw, eps, table, rd, pos)
+    native.qknorm_rope_kvwrite(qkv, nh, nkv, hd, qw, kw, eps, table, rd, pos, sot, bt, page, kp, vp, status)
+    assert int(status.item()) == 0
+    got_q = qkv.float().view(T, nh + 2 * nkv, hd)[:, :nh]
+    torch.testing.assert_close(got_q, rq.to(dtype).float(), **_tol(dtype))
+    written = torch.zeros((n_pages, page), dtype=torch.bool)
+    for t in range(T):
+        s, p = int(sot[t]), int(pos[t])
+        pg = int(bt[s, p // page])
+        written[pg, p % page] = True
+        torch.testing.assert_close(kp[pg, :, p % page].float(), rk[t].to(dtype).float(), **_tol(dtype))
+        assert torch.equal(vp[pg, :, p % page].float(), rv[t].to(dtype).float())
+    # nothing else was touched
+    untouched = ~written.to(DEV)
+    assert float(kp.float().abs().sum(dim=(1, 3))[untouched].sum()) == 0.0
+
+
+# ----------------------------------------------------------------------------- attention
+
+
+def _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, dtype, seed, n_extra_pages=7, holes=None):
+    """Random q and a paged cache with shuffled pages.  Returns the kernel inputs and dense
+    per-request keys/values for the reference."""
+    S, T = len(q_lens), sum(q_lens)
+    P = max(-(-c // page) for c in ctx_lens)
+    n_pages = sum(-(-c // page) for c in ctx_lens) + n_extra_pages
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    bt = torch.full((S, P), -1, dtype=torch.int32)
+    kp = torch.randn((n_pages, nkv, page, hd), generator=g).to(dtype)     # stale values on unused pages
+    vp = torch.randn((n_pages, nkv, page, hd), generator=g).to(dtype)
+    dense = []
+    for s, c in enumerate(ctx_lens):
+        k = torch.randn((c, nkv, hd), generator=g).to(dtype)
+        v = torch.randn((c, nkv, hd), generator=g).to(dtype)
+        dense.append((k, v))
+        for lp in range(-(-c // page)):
+            pg = perm.pop()
+            bt[s, lp] = pg
+            n = min(page, c - lp * page)
+            kp[pg, :, :n] = k[lp * page: lp * page + n].transpose(0, 1)
+            vp[pg, :, :n] = v[lp * page: lp * page + n].transpose(0, 1)
+    q = torch.randn((T, nh, hd), generator=g).to(dtype)
+    return q, kp, vp, bt, dense
+
+
+def _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, scale, window):
+    outs = []
+    t0 = 0
+    G = nh // nkv
+    for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        k, v = dense[s][0].double(), dense[s][1].double()
+        qs = q[t0:t0 + n].double()
+        pos = torch.arange(c - n, c)
+        j = torch.arange(c)
+        mask = j[None, :] <= pos[:, None]
+        if window:
+            mask &= j[None, :] > pos[:, None] - window
+        o = torch.empty((n, nh, q.shape[-1]), dtype=torch.float64)
+        for h in range(nh):
+            sc = (qs[:, h] @ k[:, h // G].T) * scale
+            sc = sc.masked_fill(~mask, float("-inf"))
+            o[:, h] = torch.softmax(sc, -1) @ v[:, h // G]
+        outs.append(o)
+        t0 += n
+    return torch.cat(outs).float()
+
+
+def _run_attention(native, kind, q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, scale, window, force_splits=None):
+    T, S = sum(q_lens), len(q_lens)
+    dev = lambda x: x.to(DEV)
+    qd, kpd, vpd, btd = dev(q.reshape(T, nh * hd).contiguous()), dev(kp), dev(vp), dev(bt.contiguous())
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(c - n, c) for n, c in zip(q_lens, ctx_lens)]).to(torch.int32).to(DEV)
+    sot = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEV)
+    out = torch.full((T, nh * hd), float("nan"), dtype=q.dtype, device=DEV)
+    if kind == "generic":
+        native.paged_attention_generic(out, qd, nh * hd, kpd, vpd, btd, pos, sot, T, nh, nkv, hd, scale, window)
+    else:
+        plan = native.flash_plan(q_lens, nh // nkv, nkv, max(ctx_lens))
+        if force_splits:
+            plan = (plan[0], plan[1], force_splits)
+        scratch = None
+        if plan[2] > 1:
+            scratch = torch.empty(native.flash_scratch_elems(T, nh, hd, plan[2]), dtype=torch.float32, device=DEV)
+        native.flash_attention(out, qd, nh * hd, kpd, vpd, btd, cu, ctx, sot, T, S, nh, nkv, hd, scale,
+                               window, plan, scratch)
+    torch.cuda.synchronize()
+    return out.float().cpu().view(T, nh, hd)
+
+
+ATTN_CASES = [
+    # nh, nkv, hd, page, window, q_lens, ctx_lens
+    (4, 2, 16, 16, 0, [1, 7, 33], [1, 7, 33]),
+    (8, 2, 32, 8, 0, [1, 2, 13, 1, 70], [100, 37, 64, 9, 70]),
+    (5, 5, 48, 16, 24, [1, 40, 3], [77, 120, 31]),
+    (8, 1, 64, 24, 0, [2, 1, 90], [50, 300, 91]),
+    (32, 8, 128, 16, 0, [1, 1, 200, 5], [700, 129, 333, 64]),
+    (6, 3, 80, 16, 50, [1, 130], [260, 130]),
+    (16, 2, 256, 16, 0, [1, 35], [97, 35]),
+]
+
+
+@pytest.mark.parametrize("case", ATTN_CASES, ids=lambda c: f"nh{c[0]}kv{c[1]}hd{c[2]}pg{c[3]}w{c[4]}")
+@pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("generic", torch.bfloat16),
+                                        ("flash", torch.bfloat16)])
+def test_paged_attention(native, case, kind, dtype):
+    nh, nkv, hd, page, window, q_lens, ctx_lens = case
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, dtype, seed=hd + page)
+    scale = hd ** -0.5
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, scale, window)
+    got = _run_attention(native, kind, q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, scale, window)
+    assert torch.isfinite(got).all()
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    err = (got - want).abs().max().item()
+    assert err <= tol, f"max abs error {err:.3e}"
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_flash_decode_splits_agree(native, splits):
+    nh, nkv, hd, page = 8, 2, 64, 16
+    q_lens, ctx_lens = [1, 1, 2, 1], [1000, 65, 513, 3]
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=5)
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, hd ** -0.5, 0)
+    got = _run_attention(native, "flash", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, hd ** -0.5, 0,
+                         force_splits=splits)
+    assert (got - want).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("kind,dtype", [("generic", torch.float32), ("flash", torch.bfloat16)])
+@pytest.mark.parametrize("far", [0, 17, 255, 256, 600])
+def test_one_far_key_decides(native, kind, dtype, far):
+    """One key among hundreds gets a score that stands out: the output must be its value.
+    A kernel that skips, repeats or misplaces a key (a page's edge, a tile's edge, a split's
+    edge) returns an average of values instead."""
+    nh, nkv, hd, page = 4, 2, 32, 16
+    q_lens, ctx_lens = [1, 3], [800, 801]
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, dtype, seed=far)
+    # put a key equal to 6*q/|q| at position `far` of request 0, kv head 0, for query head 1
+    qv = q[0, 1].float()
+    key = (qv / qv.norm() * 6.0).to(dtype)
+    k0, v0 = dense[0]
+    k0[far, 0] = key
+    pg = int(bt[0, far // page])
+    kp[pg, 0, far % page] = key
+    scale = 4.0          # score = 4 * 6 * |q| ~ 24 * 5.6: every other key is e^-100 away
+    got = _run_attention(native, kind, q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, scale, 0)
+    torch.testing.assert_close(got[0, 1], v0[far, 0].float(), rtol=2e-2, atol=2e-2)
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, scale, 0)
+    assert (got - want).abs().max().item() <= (3e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+def test_window_edge(native):
+    """The key exactly `window` back is out, the one after it is in."""
+    nh, nkv, hd, page, window = 2, 1, 32, 8, 40
+    q_lens, ctx_lens = [1], [200]
+    for kind, dtype in (("generic", torch.float32), ("flash", torch.bfloat16)):
+        q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, dtype, seed=3)
+        qv = q[0, 0].float()
+        key = (qv / qv.norm() * 6.0).to(dtype)
+        pos = 199
+        for j, inside in ((pos - window, False), (pos - window + 1, True)):
+            k0 = dense[0][0].clone()
+            kp2 = kp.clone()
+            k0[j, 0] = key
+            kp2[int(bt[0, j // page]), 0, j % page] = key
+            got = _run_attention(native, kind, q, kp2, vp, bt, q_lens, ctx_lens, nh, nkv, hd, 4.0, window)
+            hit = torch.allclose(got[0, 0], dense[0][1][j, 0].float(), rtol=3e-2, atol=3e-2)
+            assert hit == inside, f"{kind}: key at distance {pos - j} inside={inside}"
+
+
+def test_freed_pages_are_not_read(native):
+    """Pages that a window has passed are marked -1 in the block table; the kernels must not
+    follow them."""
+    nh, nkv, hd, page, window = 4, 2, 64, 16, 32
+    q_lens, ctx_lens = [1, 20], [300, 150]
+    for kind, dtype in (("generic", torch.float32), ("flash", torch.bfloat16)):
+        q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, dtype, seed=8)
+        bt2 = bt.clone()
+        bt2[0, : (300 - 1 - window + 1) // page] = -1
+        bt2[1, : (150 - 20 - window + 1) // page] = -1
+        want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, hd ** -0.5, window)
+        got = _run_attention(native, kind, q, kp, vp, bt2, q_lens, ctx_lens, nh, nkv, hd, hd ** -0.5, window)
+        assert (got - want).abs().max().item() <= (2e-2 if dtype == torch.bfloat16 else 2e-5)
+
+
+def test_flash_refuses_other_head_sizes(native):
+    assert not native.flash_supports(40, torch.bfloat16)
+    assert not native.flash_supports(272, torch.bfloat16)
+    assert not native.flash_supports(64, torch.float32)
+
+
+# ----------------------------------------------------------------------------- sampling
+
+
+def test_sampler_greedy_and_distribution():
+    from atom_b200.sampling.params import SamplingParams
+    from atom_b200.sampling.sampler import Sampler
+
+    V = 389
+    logits = _rand((6, V), torch.float32, 21, 2.0)
+    logits[2, 7] = logits[2, 300] = 50.0           # a tie: the lowest index wins
+    sm = Sampler(DEV)
+    ids = sm.sample(logits, [SamplingParams(temperature=0.0)] * 6, [0] * 6, [0] * 6).tolist()
+    assert ids == logits.argmax(-1).tolist() and ids[2] == 7
+    # the empirical distribution of temperature sampling follows softmax(logits / T)
+    V2, n = 11, 4000
+    row = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0, 1.5, -3.0, 0.2, 0.1, -0.5, 0.7]], device=DEV)
+    rows = row.repeat(n, 1).contiguous()
+    T = 0.8
+    ids = sm.sample(rows, [SamplingParams(temperature=T)] * n, [1234] * n, list(range(n))).cpu().numpy()
+    p = torch.softmax(row[0] / T, -1).cpu().numpy()
+    counts = np.bincount(ids, minlength=V2)
+    chi2 = float(((counts - n * p) ** 2 / (n * p)).sum())
+    assert chi2 < 40.0, f"chi-square {chi2:.1f} over 10 degrees of freedom"
+    # the draw depends on (seed, index) only, not on the row's place in the batch
+    a = sm.sample(rows[:5], [SamplingParams(temperature=T)] * 5, [9] * 5, [0, 1, 2, 3, 4]).tolist()
+    b = sm.sample(rows[:5], [SamplingParams(temperature=T)] * 5, [9] * 5, [4, 3, 2, 1, 0]).tolist()
+    assert a == b[::-1]
