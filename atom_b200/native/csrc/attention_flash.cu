@@ -581,3 +581,58 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   }
   return atom::check_launch();
 }
+
+// ------------------------------------------------------------------ allocation-free entry point
+// See attention_flash_static.h for who this is for and the rules of use.
+#include "attention_flash_static.h"
+
+namespace atom {
+namespace flash {
+
+// Scratch for the partial results of the key splits.  In host code this name is only a
+// stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_static_scratch[ATOM_FLASH_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_addr[kMaxDevices] = {};
+
+// Once per device, with that device current: the array's address on that device.
+static float* static_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    g_static_scratch_addr[dev] = ptr;
+  }
+  return g_static_scratch_addr[dev];
+}
+
+}  // namespace flash
+}  // namespace atom
+
+ATOM_EXPORT int atom_flash_attention_static(void* out, const void* q, int64_t q_stride,
+                                            const void* k_pages, const void* v_pages,
+                                            const int* block_table, int max_pages, int page_size,
+                                            const int* cu_q, const int* ctx_len,
+                                            const int* seq_of_token, int T, int num_seqs, int nh,
+                                            int nkv, int hd, float scale, int window,
+                                            int prefill_tiles, int has_short, int num_splits,
+                                            cudaStream_t stream) {
+  using namespace atom::flash;
+  if (T <= 0 || num_seqs <= 0) return ATOM_OK;
+  if (nh <= 0 || num_splits < 1) return ATOM_ERR_ARG;
+  float* scratch = nullptr;
+  if (num_splits > 1) {
+    const int64_t need = (int64_t)T * nh * num_splits * (HD + 2);
+    if (need > (int64_t)ATOM_FLASH_STATIC_SCRATCH_FLOATS) return ATOM_ERR_SCRATCH;
+    scratch = static_scratch_for_current_device();
+    if (scratch == nullptr) return ATOM_ERR_SETUP;
+  }
+  return atom_flash_attention(out, q, q_stride, k_pages, v_pages, block_table, max_pages, page_size,
+                              cu_q, ctx_len, seq_of_token, T, num_seqs, nh, nkv, hd, scale, window,
+                              prefill_tiles, has_short, num_splits, scratch, stream);
+}
