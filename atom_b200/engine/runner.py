@@ -23,13 +23,15 @@ from ..models.model import Model
 from ..models.registry import build_model_spec
 from ..parts.base import Runtime, Workspace
 from ..weights import load_weights, random_weights_on_device
-from .batch import StepContext, StepEntry, pack_layout
+from .batch import StepBuilder, StepContext, StepEntry, StepError
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
-class StepError(RuntimeError):
-    pass
+class _DecodeGraph:
+    graph = None
+    workspace = None
+    logits = None
 
 
 class ModelRunner:
@@ -64,12 +66,14 @@ class ModelRunner:
         self.storage = CacheStorage(self.cache, self.dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self._meta_dev = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
-        self._staging = [torch.zeros(1 << 16, dtype=torch.int32).pin_memory() for _ in range(4)]
-        self._staging_events: List[Optional[torch.cuda.Event]] = [None] * 4
-        self._staging_next = 0
+        self.builder = StepBuilder(self.cache, self.device, self.spec.vocab_size, self.status)
         self.steps_run = 0
-        self.h2d_bytes = 0      # bytes of step metadata copied host -> device so far
+        # Decode steps (one token per request) of these batch sizes replay a captured CUDA graph.
+        self.graphs_enabled = not engine_config.enforce_eager
+        self._graph_sizes = sorted(set(int(b) for b in engine_config.cudagraph_capture_sizes if int(b) > 0))
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._table_width = max(1, -(-self.max_model_len // self.page_size))
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ sizing
 
@@ -135,85 +139,6 @@ class ModelRunner:
             cache.extend(e.rid, target)
         return targets
 
-    def build_context(self, entries: Sequence[StepEntry], targets: List[int]) -> StepContext:
-        cache = self.cache
-        S = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
-        q_starts = [t - n for t, n in zip(targets, q_lens)]
-        T = sum(q_lens)
-        V = self.spec.vocab_size
-        cu = np.zeros(S + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=cu[1:])
-        rows: List[int] = []
-        for i, e in enumerate(entries):
-            for w in e.want:
-                if not 0 <= w < q_lens[i]:
-                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its {q_lens[i]} tokens")
-                rows.append(int(cu[i]) + int(w))
-        R = len(rows)
-        widths = [max(1, max(len(cache.table(e.rid, g.index)) for e in entries)) for g in cache.groups]
-        layout, total = pack_layout(T, S, R, widths)
-        if total > self._meta_dev.numel():
-            n = 1 << (total - 1).bit_length()
-            if self.rt.workspace.frozen:
-                raise StepError("step metadata outgrew its buffer while a graph holds it")
-            self._meta_dev = torch.zeros(n, dtype=torch.int32, device=self.device)
-            self._staging = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(4)]
-            self._staging_events = [None] * 4
-        k = self._staging_next
-        self._staging_next = (k + 1) % len(self._staging)
-        if self._staging_events[k] is not None:
-            self._staging_events[k].synchronize()
-        host = self._staging[k].numpy()
-
-        def sec(name):
-            o, n = layout[name]
-            return host[o:o + n]
-
-        tok = sec("token_ids")
-        pos = sec("positions")
-        sot = sec("seq_of_token")
-        for i, e in enumerate(entries):
-            a, b = cu[i], cu[i + 1]
-            tok[a:b] = np.asarray(e.tokens, dtype=np.int64)
-            pos[a:b] = np.arange(q_starts[i], targets[i], dtype=np.int32)
-            sot[a:b] = i
-        if T and (tok.min() < 0 or tok.max() >= V):
-            raise StepError(f"token id outside [0, {V})")
-        sec("cu_q")[:] = cu
-        sec("ctx_len")[:] = targets
-        slots = [cache.requests[e.rid].state_slot for e in entries]
-        sec("state_slots")[:] = slots
-        lr = sec("logits_rows")
-        lr[:] = 0
-        lr[:R] = rows
-        for g, w in zip(cache.groups, widths):
-            bt = sec(f"bt{g.index}").reshape(S, w)
-            bt[:] = NO_PAGE
-            for i, e in enumerate(entries):
-                t = cache.table(e.rid, g.index)
-                bt[i, :len(t)] = t
-        dev = self._meta_dev
-        dev[:total].copy_(self._staging[k][:total], non_blocking=True)
-        self.h2d_bytes += 4 * total
-        ev = torch.cuda.Event()
-        ev.record()
-        self._staging_events[k] = ev
-
-        def dsec(name):
-            o, n = layout[name]
-            return dev[o:o + n]
-
-        return StepContext(
-            num_tokens=T, num_seqs=S, num_logits_rows=R,
-            token_ids=dsec("token_ids"), positions=dsec("positions"), seq_of_token=dsec("seq_of_token"),
-            cu_q=dsec("cu_q"), ctx_len=dsec("ctx_len"), state_slots=dsec("state_slots"),
-            logits_rows=dsec("logits_rows")[:R] if R else dsec("logits_rows")[:0],
-            block_tables={g.index: dsec(f"bt{g.index}").view(S, w) for g, w in zip(cache.groups, widths)},
-            status=self.status, q_lens=q_lens, q_starts=q_starts, host_state_slots=slots,
-            max_q_len=max(q_lens), max_ctx_len=max(targets),
-        )
-
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns logits [R, vocab] float32 on the device, rows in the order
@@ -221,12 +146,82 @@ class ModelRunner:
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         targets = self._reserve(entries)
-        ctx = self.build_context(entries, targets)
-        logits = self.model.forward(ctx, self.storage)
+        size = self._graph_size(entries)
+        if size:
+            logits = self._step_graph(entries, targets, size)
+        else:
+            ctx = self.builder.build(entries, targets)
+            logits = self.model.forward(ctx, self.storage)
         for e, t in zip(entries, targets):
             self.cache.commit(e.rid, t)
         self.steps_run += 1
         return logits
+
+    @property
+    def h2d_bytes(self) -> int:
+        """Bytes of step metadata copied host -> device so far."""
+        return self.builder.h2d_bytes
+
+    # ------------------------------------------------------------------ captured decode steps
+
+    def _graph_size(self, entries: Sequence[StepEntry]) -> int:
+        """The captured batch size a step replays, 0 if it runs eagerly: every request brings
+        exactly one token, and the batch fits the largest captured size."""
+        if not self.graphs_enabled or not self._graph_sizes:
+            return 0
+        n = len(entries)
+        if n > self._graph_sizes[-1] or any(len(e.tokens) != 1 for e in entries):
+            return 0
+        for b in self._graph_sizes:
+            if b >= n:
+                return b
+        return 0
+
+    def _capture(self, size: int) -> "_DecodeGraph":
+        """Runs a decode step of ``size`` padding rows once eagerly (loads kernels, sizes the
+        buffers), then records the same launches into a graph.  The graph has its own
+        activation buffers and logits, so steps of other shapes cannot move them."""
+        g = _DecodeGraph()
+        g.workspace = Workspace(self.device)
+        g.logits = torch.empty((size, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        saved = self.rt.workspace
+        self.rt.workspace = g.workspace
+        try:
+            def run():
+                # launch plans are made for the longest request the engine takes
+                ctx = self.builder.fixed_context(size, self._table_width, self.max_model_len)
+                ctx.logits_out = g.logits
+                self.model.forward(ctx, self.storage)
+
+            self.builder.build_fixed([], [], size, self._table_width)   # all rows padding
+            run()
+            torch.cuda.current_stream().synchronize()
+            g.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g.graph):
+                run()
+            g.workspace.frozen = True
+        finally:
+            self.rt.workspace = saved
+        return g
+
+    def _step_graph(self, entries: Sequence[StepEntry], targets: List[int], size: int) -> torch.Tensor:
+        g = self._graphs.get(size)
+        if g is None:
+            g = self._graphs[size] = self._capture(size)
+        self.builder.build_fixed(entries, targets, size, self._table_width)
+        g.graph.replay()
+        self.graph_replays += 1
+        rows = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if w != 0:
+                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its 1 token")
+                rows.append(i)
+        if rows == list(range(len(entries))):
+            return g.logits[: len(entries)]       # valid until the next step of this size
+        if not rows:
+            return g.logits[:0]
+        return g.logits[torch.tensor(rows, device=self.device)]
 
     def finish(self, rid: Hashable) -> None:
         """The request is over (or preempted): its pages and its state slot go back."""
@@ -239,3 +234,4 @@ class ModelRunner:
         torch.cuda.current_stream().synchronize()
         if int(self._status_host[0]) != 0:
             raise StepError("a kernel found a token position without a cache page")
+        native.check_error_flags()

@@ -68,6 +68,8 @@ _SIGNATURES = {
     "atom_gemm_f32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _vp],
     "atom_gemm_bf16": [_vp, _i, _vp, _vp, _i, _i, _i, _i64, _vp, _sz, _vp],
     "atom_add_bias": [_vp, _i, _vp, _i, _i, _i, _vp],
+    "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "atom_gemm_smallm_supports": [_i, _i, _i, _i64],
 }
 
 
@@ -247,6 +249,49 @@ def gemm_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
            own=False)
 
 
+_error_flags = {}
+
+
+def error_flag(device: torch.device) -> torch.Tensor:
+    """A device int that kernels with bounded waits set when a wait ran out (0: all well)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    f = _error_flags.get(key)
+    if f is None:
+        f = _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return f
+
+
+def check_error_flags() -> None:
+    """Raises if a kernel gave up a bounded wait (synchronises the device)."""
+    for f in _error_flags.values():
+        if int(f.item()) != 0:
+            f.zero_()
+            raise NativeError("a kernel's bounded wait ran out (device error flag set)")
+
+
+SMALL_M = 8     # rows up to which the weight-streaming product beats the library's (measured)
+
+
+def gemm_smallm_supports(M: int, N: int, K: int, lda: int) -> bool:
+    return bool(lib().atom_gemm_smallm_supports(M, N, K, lda))
+
+
+def gemm_smallm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                gated: bool = False) -> None:
+    """out[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T (+ bias) for M <= 16: the weight-streaming
+    kernel.  gated: w is [2N, K] = [gate ; up] and out = silu(a gate^T) * (a up^T)."""
+    _cuda(out, a, w, bias)
+    M, K = a.shape
+    N = out.shape[1]
+    assert a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous()
+    assert w.shape[0] == (2 * N if gated else N) and out.shape[0] == M
+    assert a.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().atom_gemm_smallm(
+        out.data_ptr(), dtype_code(out.dtype), out.stride(0), a.data_ptr(), a.stride(0), w.data_ptr(),
+        _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, M, N, K, int(gated),
+        error_flag(out.device).data_ptr(), _stream()), "gemm_smallm")
+
+
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     _cuda(out, bias)
     M, N = out.shape
@@ -300,7 +345,7 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sm_count: int = 148):
             short += 1
     splits = 1
     if short:
-        want = -(-4 * sm_count // max(1, len(q_lens) * nkv))
+        want = (4 * sm_count) // max(1, len(q_lens) * nkv)      # two CTAs per SM, two waves at most
         splits = max(1, min(want, -(-max_ctx // 256), 64))
     return tiles, short > 0, splits
 

@@ -485,6 +485,7 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
   if (warp >= T * p.nh) return;
   const int t = warp / p.nh;
   const int s = seq_of_token[t];
+  if (s < 0) return;  // a padding row of a fixed-size batch
   const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
   if (rows > 16) return;
   const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;

@@ -30,6 +30,7 @@ paged_attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int
   const int t = blockIdx.x, h = blockIdx.y;
   const int g = h / (nh / nkv);
   const int p = positions[t];
+  if (seq_of_token[t] < 0) return;  // a padding row of a fixed-size batch
   const int* bt = block_table + (int64_t)seq_of_token[t] * max_pages;
   const T* qrow = q + (int64_t)t * q_stride + (int64_t)h * hd;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) qs[i] = to_float(qrow[i]);

@@ -32,13 +32,15 @@ __global__ void qknorm_rope_kvwrite_kernel(
   const bool write_cache = k_pages != nullptr;
   if (!is_q && !write_cache) return;
 
+  const int seq = seq_of_token[t];
+  if (seq < 0) return;  // a padding row of a fixed-size batch: belongs to no request
+
   T* x = qkv + ((int64_t)t * n_heads_total + head) * hd;
   const int pos = positions[t];
 
   // Destination in the cache for k and v heads.
   T* dst = nullptr;
   if (!is_q) {
-    const int seq = seq_of_token[t];
     const int page = block_table[(int64_t)seq * max_pages + pos / page_size];
     if (page < 0 || page >= num_pages) {
       // A position without a page is a host-side accounting fault: record it, write nothing.

@@ -1,7 +1,8 @@
 """Matrix product y = x W^T (+ b) with weights [out, in], as atom/model_ops/linear.py:946-965.
 
-bfloat16: the GEMM library, as the reference does (tgemm.mm, linear.py:960), with 32-bit
-accumulation.  float32: the framework's own FMA kernel, never a reduced-precision mode.
+bfloat16: for more than 8 rows the GEMM library, as the reference does (tgemm.mm,
+linear.py:960); for up to 8 rows (decode) the framework's weight-streaming kernel.  Both
+accumulate in 32-bit.  float32: the framework's own FMA kernel, never a reduced-precision mode.
 """
 from __future__ import annotations
 
@@ -19,8 +20,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         if b is not None and b.dtype != torch.float32:
             b = b.float()
         native.gemm_f32(out, x, weight, b)
+    elif x.shape[0] <= native.SMALL_M and native.gemm_smallm_supports(
+            x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
+        native.gemm_smallm(out, x, weight, bias)          # few rows: the product is a read of W
     else:
         native.gemm_bf16(out, x, weight)
         if bias is not None:
             native.add_bias(out, bias)
+    return out
+
+
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch) -> torch.Tensor:
+    """out[M, I] = silu(x W_gate^T) * (x W_up^T) for weight [2I, K] = [gate ; up].  Few rows:
+    one kernel, the activation fused into the product.  Else the product into
+    ``scratch(M, 2I)`` and the activation kernel."""
+    M, K = x.shape
+    I = weight.shape[0] // 2
+    if (x.dtype == torch.bfloat16 and M <= native.SMALL_M
+            and native.gemm_smallm_supports(M, I, K, x.stride(0))):
+        native.gemm_smallm(out, x, weight, None, gated=True)
+        return out
+    gu = linear(x, weight, None, scratch(M, 2 * I))
+    native.silu_mul(out, gu)
     return out

@@ -6,7 +6,7 @@ from typing import Dict
 
 from .. import native
 from .base import FeedForward
-from .linear import linear
+from .linear import gated_linear, linear
 from .registry import register
 from .spec import ParamSpec
 
@@ -26,7 +26,6 @@ class GatedSiluMLP(FeedForward):
     def forward(self, x, step):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
-        gu = linear(x, self.w_gate_up_weight, None, ws.get("ffn.gate_up", (T, 2 * self.intermediate_size), dt))
-        f = ws.get("ffn.act", (T, self.intermediate_size), dt)
-        native.silu_mul(f, gu)
+        f = gated_linear(x, self.w_gate_up_weight, ws.get("ffn.act", (T, self.intermediate_size), dt),
+                         lambda m, n: ws.get("ffn.gate_up", (m, n), dt))
         return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))

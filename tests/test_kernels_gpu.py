@@ -367,3 +367,52 @@ def test_sampler_greedy_and_distribution():
     a = sm.sample(rows[:5], [SamplingParams(temperature=T)] * 5, [9] * 5, [0, 1, 2, 3, 4]).tolist()
     b = sm.sample(rows[:5], [SamplingParams(temperature=T)] * 5, [9] * 5, [4, 3, 2, 1, 0]).tolist()
     assert a == b[::-1]
+
+
+# ----------------------------------------------------------------------------- few-row matrix product
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 389, 64), (3, 130, 320), (8, 4096, 4096), (9, 1000, 576), (16, 77, 1024),
+                                   (7, 301, 192), (4, 200, 448), (13, 640, 2112), (2, 2500, 512), (5, 151, 12288)])
+def test_gemm_smallm(native, out_dtype, M, N, K):
+    a, w = _rand((M, K), torch.bfloat16, 30), _rand((N, K), torch.bfloat16, 31)
+    bias = _rand((N,), torch.bfloat16, 32) if N % 2 else None
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    assert native.gemm_smallm_supports(M, N, K, K)
+    native.gemm_smallm(out, a, w, bias)
+    native.check_error_flags()
+    want = a.float() @ w.float().T + (bias.float() if bias is not None else 0)
+    torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 160, 128), (7, 1001, 320), (8, 12288, 4096), (12, 112, 64), (16, 333, 1024)])
+def test_gemm_smallm_gated(native, M, I, K):
+    a, w = _rand((M, K), torch.bfloat16, 33), _rand((2 * I, K), torch.bfloat16, 34, 0.3)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    native.gemm_smallm(out, a, w, None, gated=True)
+    native.check_error_flags()
+    gu = a.float() @ w.float().T
+    g, u = gu[:, :I], gu[:, I:]
+    want = g * torch.sigmoid(g) * u
+    torch.testing.assert_close(out.float(), want.bfloat16().float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
+
+
+def test_gemm_smallm_rows_do_not_depend_on_the_batch(native):
+    """A row's result does not depend on the rows beside it: bit-equal within one tile shape
+    (up to 8 rows), and equal up to the order of 32-bit sums across tile shapes."""
+    N, K = 520, 1088
+    a, w = _rand((16, K), torch.bfloat16, 35), _rand((N, K), torch.bfloat16, 36)
+    outs = {}
+    for m in (1, 5, 8, 9, 16):
+        outs[m] = torch.empty((m, N), dtype=torch.float32, device=DEV)
+        native.gemm_smallm(outs[m], a[:m], w)
+    assert torch.equal(outs[1], outs[8][:1]) and torch.equal(outs[5], outs[8][:5])
+    assert torch.equal(outs[9], outs[16][:9])
+    torch.testing.assert_close(outs[8], outs[16][:8], rtol=1e-5, atol=1e-4)
+
+
+def test_gemm_smallm_refuses_other_sizes(native):
+    assert not native.gemm_smallm_supports(17, 64, 64, 64)
+    assert not native.gemm_smallm_supports(4, 64, 96, 96)      # K no multiple of 64
+    assert not native.gemm_smallm_supports(4, 64, 64, 100)     # leading dimension no multiple of 8

@@ -100,3 +100,26 @@ def test_mixed_reuses_pages(model_dirs, runners, dtype):
         reused = reused or bool(now & seen)
     runner.check_status()
     assert reused
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_captured_decode_steps_match_plain(model_dirs, name, dtype):
+    """Decode steps replayed from CUDA graphs (batch sizes 1, 2 and 4, the last with padding
+    rows when three requests are live) give the logits of the plain implementation."""
+    from atom_b200.config import EngineConfig
+    from atom_b200.engine.runner import ModelRunner
+
+    seqs = _seqs(name)
+    ref = plain_logits(model_dirs[name], seqs)
+    cfg = EngineConfig(model=model_dirs[name], dtype=dtype, kv_cache_block_size=PAGE[name],
+                       num_kvcache_blocks=64, max_num_seqs=8, enforce_eager=False,
+                       cudagraph_capture_sizes=[1, 2, 4], max_model_len=256)
+    runner = ModelRunner(cfg)
+    for steps in (traces.tail_by_token(seqs, 32), traces.mixed(seqs, max_live=3, tail=40)[0]):
+        got = traces.collect(steps, replay(runner, steps))
+        err, rid, pos = max_err(got, ref)
+        tol = _tol(dtype, ref)
+        assert err <= tol, f"{name}/{dtype}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+    assert runner.graph_replays > 50 and set(runner._graphs) >= {1, 4}
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
