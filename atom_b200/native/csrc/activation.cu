@@ -16,6 +16,28 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// bf16, I a multiple of 8: 16 bytes of gate and of up per thread.
+__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
+                                         int64_t nvec, int I8) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += stride) {
+    const int64_t t = idx / I8;
+    const int i = (int)(idx - t * I8);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + i) * 8);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + (t * 2 * I8 + I8 + i) * 8);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(gh[e]), u = __bfloat1622float2(uh[e]);
+      oh[e] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = o4;
+  }
+}
+
 }  // namespace atom
 
 ATOM_EXPORT int atom_silu_mul(void* out, const void* gu, int dtype, int T, int I,
@@ -25,6 +47,14 @@ ATOM_EXPORT int atom_silu_mul(void* out, const void* gu, int dtype, int T, int I
   const int64_t n = (int64_t)T * I;
   const int threads = 256;
   int64_t blocks = (n + threads - 1) / threads;
+  if (dtype == ATOM_BF16 && I % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gu % 16 == 0) {
+    const int64_t nvec = n / 8;
+    int64_t vb = (nvec + threads - 1) / threads;
+    if (vb > 148 * 32) vb = 148 * 32;
+    atom::silu_mul_bf16_vec_kernel<<<(int)vb, threads, 0, stream>>>((__nv_bfloat16*)out,
+                                                                    (const __nv_bfloat16*)gu, nvec, I / 8);
+    return atom::check_launch();
+  }
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == ATOM_F32) {
     atom::silu_mul_kernel<float>

@@ -96,24 +96,52 @@ struct Work {
 };
 
 // Copies keys and values [tile * BN, tile * BN + BN) of the request into one stage.
+// Consecutive threads take consecutive 16-byte chunks of a row (whole 128-byte lines per
+// request); a thread's rows are row0, row0 + NT / CH, ...  Offsets are formed in units of 16
+// bytes in 32-bit arithmetic (a layer's pages stay below 64 GB).
 __device__ __forceinline__ void load_kv_tile(const Params& p, const Work& w, int tile, int key_end,
                                              __nv_bfloat16* sK, __nv_bfloat16* sV) {
-  const int64_t head_stride = (int64_t)p.page_size * HD;
-  const int64_t page_stride = head_stride * p.nkv;
-  for (int c = threadIdx.x; c < BN * CH; c += NT) {
-    const int row = c / CH, ch = c % CH;
-    const int j = tile * BN + row;
-    bool valid = j < key_end;
-    int64_t off = 0;
-    if (valid) {
-      const int lp = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
-      const int in_page = j - lp * p.page_size;
-      const int page = w.bt[lp];
-      valid = page >= 0;
-      if (valid) off = (int64_t)page * page_stride + (int64_t)w.kvh * head_stride + (int64_t)in_page * HD + ch * 8;
+  constexpr int ROWS_PER_PASS = NT / CH > 0 ? NT / CH : 1;   // rows covered by one pass of the CTA
+  const uint32_t head_stride = (uint32_t)p.page_size * CH;           // 16-byte units
+  const uint32_t page_stride = head_stride * (uint32_t)p.nkv;
+  const uint4* kp = reinterpret_cast<const uint4*>(p.k_pages);
+  const uint4* vp = reinterpret_cast<const uint4*>(p.v_pages);
+  if (NT % CH == 0) {
+    const int ch = threadIdx.x % CH, row0 = threadIdx.x / CH;
+    const uint32_t fixed = (uint32_t)w.kvh * head_stride + ch;
+    const int soff = ch * 8;
+#pragma unroll
+    for (int i = 0; i < BN / ROWS_PER_PASS; ++i) {
+      const int row = row0 + i * ROWS_PER_PASS;
+      const int j = tile * BN + row;
+      bool valid = j < key_end;
+      uint32_t off = 0;
+      if (valid) {
+        const int lp = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+        const int in_page = j - lp * p.page_size;
+        const int page = w.bt[lp];
+        valid = page >= 0;
+        if (valid) off = (uint32_t)page * page_stride + (uint32_t)in_page * CH + fixed;
+      }
+      cp_async16(sK + row * LDS + soff, kp + off, valid);
+      cp_async16(sV + row * LDS + soff, vp + off, valid);
     }
-    cp_async16(sK + row * LDS + ch * 8, p.k_pages + off, valid);
-    cp_async16(sV + row * LDS + ch * 8, p.v_pages + off, valid);
+  } else {
+    for (int c = threadIdx.x; c < BN * CH; c += NT) {
+      const int row = c / CH, ch = c % CH;
+      const int j = tile * BN + row;
+      bool valid = j < key_end;
+      uint32_t off = 0;
+      if (valid) {
+        const int lp = p.page_shift >= 0 ? (j >> p.page_shift) : (j / p.page_size);
+        const int in_page = j - lp * p.page_size;
+        const int page = w.bt[lp];
+        valid = page >= 0;
+        if (valid) off = (uint32_t)page * page_stride + (uint32_t)w.kvh * head_stride + (uint32_t)in_page * CH + ch;
+      }
+      cp_async16(sK + row * LDS + ch * 8, kp + off, valid);
+      cp_async16(sV + row * LDS + ch * 8, vp + off, valid);
+    }
   }
 }
 
@@ -364,7 +392,7 @@ __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
 constexpr int DECODE_STAGES = 3;
 constexpr size_t decode_smem_bytes() {
   const size_t ring = sizeof(__nv_bfloat16) * (size_t)(16 * LDS + DECODE_STAGES * 2 * BN * LDS);
-  const size_t merge = sizeof(float) * (size_t)(4 * 16 * (HD + 2));
+  const size_t merge = sizeof(float) * (size_t)(4 * 16 * (HD + 8 + 2));
   return ring > merge ? ring : merge;
 }
 
@@ -425,15 +453,21 @@ __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
       }
       cp_async_commit();
       if (t == tile_begin && Q_IN_REGS) load_q_frags(qf, sQ);
-      warp_tile<2>(acc, qf, sQ, sK, sV, warp * 16, t * BN, pos0, pos1, p.window, p.scale_log2, true);
+      // The mask is needed where a key of the warp's 16 may lie after the first new token, or
+      // before the window of the last one.
+      const int kfirst = t * BN + warp * 16;
+      bool mask = kfirst + 15 > w.q_start;
+      if (p.window > 0) mask = mask || (kfirst <= w.ctx - 1 - p.window);
+      warp_tile<2>(acc, qf, sQ, sK, sV, warp * 16, t * BN, pos0, pos1, p.window, p.scale_log2, mask);
     }
     cp_async_wait<0>();
   }
   __syncthreads();   // the ring is free: it becomes the merge buffer
 
   // Merge the four warps (each saw other keys).
-  float* mo = reinterpret_cast<float*>(smem_raw);       // [4][16][HD]
-  float* mm = mo + 4 * 16 * HD;                          // [4][16]
+  constexpr int MLD = HD + 8;                            // padded row: conflict-free fragment stores
+  float* mo = reinterpret_cast<float*>(smem_raw);       // [4][16][MLD]
+  float* mm = mo + 4 * 16 * MLD;                         // [4][16]
   float* ml = mm + 4 * 16;                               // [4][16]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -448,7 +482,7 @@ __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
 #pragma unroll
     for (int d = 0; d < HD / 8; ++d) {
       float2 v = make_float2(acc.o[d][2 * r], acc.o[d][2 * r + 1]);
-      *reinterpret_cast<float2*>(mo + (warp * 16 + row) * HD + d * 8 + 2 * t4) = v;
+      *reinterpret_cast<float2*>(mo + (warp * 16 + row) * MLD + d * 8 + 2 * t4) = v;
     }
   }
   __syncthreads();
@@ -463,7 +497,7 @@ __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
     for (int k = 0; k < 4; ++k) {
       const float f = exp2f((mm[k * 16 + row] - Mu) * p.scale_log2);
       L += ml[k * 16 + row] * f;
-      O += mo[(k * 16 + row) * HD + d] * f;
+      O += mo[(k * 16 + row) * MLD + d] * f;
     }
     const int tok = row / p.group, hig = row - tok * p.group;
     const int64_t th = (int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig);
@@ -479,7 +513,9 @@ __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
   }
 }
 
-// Merges the splits of every (token, head) of the short requests: one warp each.
+// Merges the splits of every (token, head) of the short requests: one warp each.  Lanes
+// first take one split each to find the common maximum and the weights, then one output
+// element each (all loads of a pass are independent).  At most 64 splits.
 __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_of_token, int T) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T * p.nh) return;
@@ -490,16 +526,37 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
   if (rows > 16) return;
   const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;
   const float* po = p.part_o + (int64_t)warp * p.num_splits * HD;
-  float M = -INFINITY;
-  for (int k = 0; k < p.num_splits; ++k) M = fmaxf(M, ml[2 * k]);
+  const int k0 = lane, k1 = lane + 32;
+  const float m0 = k0 < p.num_splits ? ml[2 * k0] : -INFINITY;
+  const float m1 = k1 < p.num_splits ? ml[2 * k1] : -INFINITY;
+  const float l0 = k0 < p.num_splits ? ml[2 * k0 + 1] : 0.f;
+  const float l1 = k1 < p.num_splits ? ml[2 * k1 + 1] : 0.f;
+  float M = fmaxf(m0, m1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
   const float Mu = (M == -INFINITY) ? 0.f : M;
-  float L = 0.f;
-  for (int k = 0; k < p.num_splits; ++k) L += ml[2 * k + 1] * exp2f((ml[2 * k] - Mu) * p.scale_log2);
+  float w0 = exp2f((m0 - Mu) * p.scale_log2), w1 = exp2f((m1 - Mu) * p.scale_log2);
+  float L = l0 * w0 + l1 * w1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
   const float inv = 1.f / L;
-  for (int d = lane; d < HD; d += 32) {
-    float O = 0.f;
-    for (int k = 0; k < p.num_splits; ++k) O += po[k * HD + d] * exp2f((ml[2 * k] - Mu) * p.scale_log2);
-    p.out[(int64_t)warp * HD + d] = __float2bfloat16_rn(O * inv);
+  w0 *= inv;
+  w1 *= inv;
+  float acc[(HD + 31) / 32];
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
+  for (int k = 0; k < p.num_splits; ++k) {
+    const float wk = __shfl_sync(0xffffffffu, k < 32 ? w0 : w1, k & 31);
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) {
+      const int d = lane + i * 32;
+      if (d < HD) acc[i] += po[k * HD + d] * wk;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < (HD + 31) / 32; ++i) {
+    const int d = lane + i * 32;
+    if (d < HD) p.out[(int64_t)warp * HD + d] = __float2bfloat16_rn(acc[i]);
   }
 }
 

@@ -59,6 +59,78 @@ __global__ void rmsnorm_kernel(TA* __restrict__ out, const TA* __restrict__ x,
 
 static inline int norm_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
 
+// bf16 activations, H a multiple of 8, at most 8 * NV * blockDim: every thread keeps its
+// 8 * NV elements in registers, so the row is read once and written once, 16 bytes at a time.
+template <int NV>
+__global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual,
+                                            const __nv_bfloat16* __restrict__ delta,
+                                            const void* __restrict__ w, int w_dtype, float eps,
+                                            const int* __restrict__ rows, int H) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int64_t src = rows ? rows[r] : r;
+  float* res = residual + src * H;
+  const __nv_bfloat16* d = delta ? delta + src * H : nullptr;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      const float4 a = *reinterpret_cast<const float4*>(res + i);
+      const float4 b = *reinterpret_cast<const float4*>(res + i + 4);
+      v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
+      v[k][4] = b.x; v[k][5] = b.y; v[k][6] = b.z; v[k][7] = b.w;
+      if (d) {
+        const uint4 q = *reinterpret_cast<const uint4*>(d + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[k][2 * e] += f.x;
+          v[k][2 * e + 1] += f.y;
+        }
+        if (!rows) {
+          *reinterpret_cast<float4*>(res + i) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+          *reinterpret_cast<float4*>(res + i + 4) = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[k][e] * v[k][e];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  __nv_bfloat16* o = out + (int64_t)r * H;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      float wv[8];
+      if (w_dtype == ATOM_F32) {
+        const float4 a = *reinterpret_cast<const float4*>((const float*)w + i);
+        const float4 b = *reinterpret_cast<const float4*>((const float*)w + i + 4);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+      } else {
+        const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          wv[2 * e] = f.x;
+          wv[2 * e + 1] = f.y;
+        }
+      }
+      uint4 q;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        h[e] = __floats2bfloat162_rn(v[k][2 * e] * rstd * wv[2 * e], v[k][2 * e + 1] * rstd * wv[2 * e + 1]);
+      *reinterpret_cast<uint4*>(o + i) = q;
+    }
+  }
+}
+
 }  // namespace atom
 
 ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, const void* delta,
@@ -67,6 +139,25 @@ ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, cons
   if (n_rows <= 0) return ATOM_OK;
   if (H <= 0 || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
   const int threads = atom::norm_threads(H);
+  const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
+                       ((uintptr_t)delta % 16 == 0) && ((uintptr_t)w % 16 == 0);
+  if (act_dtype == ATOM_BF16 && H % 8 == 0 && H <= 8 * 2 * 1024 && aligned) {
+    // one pass over the row, 16-byte accesses: 128 to 1024 threads, one or two vectors each
+    const int vecs = H / 8;
+    int nv = 1, th = ((vecs + 31) / 32) * 32;
+    if (th > 1024) {
+      nv = 2;
+      th = (((vecs + 1) / 2 + 31) / 32) * 32;
+    }
+    if (th < 64) th = 64;
+    if (nv == 1)
+      atom::add_rmsnorm_bf16_vec_kernel<1><<<n_rows, th, 0, stream>>>(
+          (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+    else
+      atom::add_rmsnorm_bf16_vec_kernel<2><<<n_rows, th, 0, stream>>>(
+          (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+    return atom::check_launch();
+  }
   if (act_dtype == ATOM_F32) {
     atom::add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(
         (float*)out, residual, (const float*)delta, w, w_dtype, eps, rows, H);
