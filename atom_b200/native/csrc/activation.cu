@@ -6,6 +6,8 @@ namespace atom {
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int I) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
     const int64_t t = idx / I;
@@ -19,6 +21,8 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
 // bf16, I a multiple of 8: 16 bytes of gate and of up per thread.
 __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
                                          int64_t nvec, int I8) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < nvec; idx += stride) {
     const int64_t t = idx / I8;
@@ -51,17 +55,15 @@ ATOM_EXPORT int atom_silu_mul(void* out, const void* gu, int dtype, int T, int I
     const int64_t nvec = n / 8;
     int64_t vb = (nvec + threads - 1) / threads;
     if (vb > 148 * 32) vb = 148 * 32;
-    atom::silu_mul_bf16_vec_kernel<<<(int)vb, threads, 0, stream>>>((__nv_bfloat16*)out,
+    atom::launch_pdl(atom::silu_mul_bf16_vec_kernel, dim3((int)vb), dim3(threads), 0, stream, (__nv_bfloat16*)out,
                                                                     (const __nv_bfloat16*)gu, nvec, I / 8);
     return atom::check_launch();
   }
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == ATOM_F32) {
-    atom::silu_mul_kernel<float>
-        <<<(int)blocks, threads, 0, stream>>>((float*)out, (const float*)gu, n, I);
+    atom::launch_pdl(atom::silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (float*)out, (const float*)gu, n, I);
   } else if (dtype == ATOM_BF16) {
-    atom::silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
+    atom::launch_pdl(atom::silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I);
   } else {
     return ATOM_ERR_ARG;
   }

@@ -291,6 +291,8 @@ constexpr size_t prefill_smem_bytes() {
 }
 
 __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sKV = sQ + BM * LDS;
@@ -397,6 +399,8 @@ constexpr size_t decode_smem_bytes() {
 }
 
 __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sKV = sQ + 16 * LDS;
@@ -517,6 +521,8 @@ __global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
 // first take one split each to find the common maximum and the weights, then one output
 // element each (all loads of a pass are independent).  At most 64 splits.
 __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_of_token, int T) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T * p.nh) return;
   const int t = warp / p.nh;
@@ -627,14 +633,14 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   }
   if (prefill_tiles > 0) {
     dim3 grid(prefill_tiles, nkv);
-    flash_prefill_kernel<<<grid, NT, prefill_smem_bytes(), stream>>>(p);
+    atom::launch_pdl(flash_prefill_kernel, dim3(grid), dim3(NT), prefill_smem_bytes(), stream, p);
   }
   if (has_short) {
     dim3 grid(num_seqs, nkv, num_splits);
-    flash_decode_kernel<<<grid, NT, decode_smem_bytes(), stream>>>(p);
+    atom::launch_pdl(flash_decode_kernel, dim3(grid), dim3(NT), decode_smem_bytes(), stream, p);
     if (num_splits > 1) {
       const int warps = T * nh;
-      flash_merge_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(p, seq_of_token, T);
+      atom::launch_pdl(flash_merge_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, p, seq_of_token, T);
     }
   }
   return atom::check_launch();

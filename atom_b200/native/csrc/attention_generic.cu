@@ -21,6 +21,8 @@ paged_attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int
                                const int* __restrict__ positions,
                                const int* __restrict__ seq_of_token, int nh, int nkv, int hd,
                                float scale, int window) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int64_t* row_off = (int64_t*)smem_raw;           // [kAttnChunk] element offset of a key's row
   float* prob = (float*)(row_off + kAttnChunk);    // [kAttnChunk]
@@ -107,13 +109,10 @@ ATOM_EXPORT int atom_paged_attention_generic(void* out, const void* q, int64_t q
   const size_t smem = sizeof(float) * (hd + atom::kAttnChunk) + sizeof(int64_t) * atom::kAttnChunk;
   dim3 grid(T, nh);
   if (dtype == ATOM_F32) {
-    atom::paged_attention_generic_kernel<float><<<grid, atom::kAttnThreads, smem, stream>>>(
-        (float*)out, (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages,
+    atom::launch_pdl(atom::paged_attention_generic_kernel<float>, dim3(grid), dim3(atom::kAttnThreads), smem, stream, (float*)out, (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages,
         block_table, max_pages, page_size, positions, seq_of_token, nh, nkv, hd, scale, window);
   } else if (dtype == ATOM_BF16) {
-    atom::paged_attention_generic_kernel<__nv_bfloat16>
-        <<<grid, atom::kAttnThreads, smem, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride,
+    atom::launch_pdl(atom::paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(atom::kAttnThreads), smem, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages,
             page_size, positions, seq_of_token, nh, nkv, hd, scale, window);
   } else {

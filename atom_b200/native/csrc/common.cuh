@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 // Element type codes of the C interface.
 #define ATOM_F32 0
@@ -72,6 +73,42 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
   r = warp_max(r);
   return r;
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// Every kernel of the library starts with pdl_wait(): it returns when the kernels before it
+// in the stream have completed and their writes are visible.  Launched with launch_pdl, a
+// kernel may be scheduled while the one before it is still draining (after all of that
+// kernel's CTAs have passed pdl_trigger() or exited), so launch latency, the prologue, and,
+// where a kernel has inputs that no earlier kernel writes (weights), their first loads
+// overlap the predecessor's tail.  Nothing that depends on an earlier kernel may be read, and
+// nothing written, before pdl_wait().  Set ATOM_PDL=0 in the environment for plain launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ATOM_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface in check_launch()
 }
 
 inline int check_launch() {

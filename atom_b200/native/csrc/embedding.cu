@@ -7,6 +7,8 @@ namespace atom {
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int H, int V) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int t = blockIdx.x;
   int id = ids[t];
   // Ids are validated on the host; the clamp only keeps a bad id from reading outside the table.
@@ -24,10 +26,9 @@ ATOM_EXPORT int atom_embedding(float* out, const void* table, int table_dtype, c
   if (H <= 0 || V <= 0) return ATOM_ERR_ARG;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == ATOM_F32) {
-    atom::embedding_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, H, V);
+    atom::launch_pdl(atom::embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, out, (const float*)table, ids, H, V);
   } else if (table_dtype == ATOM_BF16) {
-    atom::embedding_kernel<__nv_bfloat16>
-        <<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+    atom::launch_pdl(atom::embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V);
   } else {
     return ATOM_ERR_ARG;
   }

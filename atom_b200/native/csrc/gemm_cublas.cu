@@ -21,6 +21,8 @@ static cublasHandle_t handle_for_current_device() {
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ C, const void* __restrict__ bias, int bias_dtype,
                                 int64_t n, int N) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     C[i] = from_float<T>(to_float(C[i]) + load_as_float(bias, bias_dtype, i % N));
@@ -60,10 +62,9 @@ ATOM_EXPORT int atom_add_bias(void* C, int c_dtype, const void* bias, int bias_d
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (c_dtype == ATOM_F32)
-    atom::add_bias_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)C, bias, bias_dtype, n, N);
+    atom::launch_pdl(atom::add_bias_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, (float*)C, bias, bias_dtype, n, N);
   else if (c_dtype == ATOM_BF16)
-    atom::add_bias_kernel<__nv_bfloat16>
-        <<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)C, bias, bias_dtype, n, N);
+    atom::launch_pdl(atom::add_bias_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, (__nv_bfloat16*)C, bias, bias_dtype, n, N);
   else
     return ATOM_ERR_ARG;
   return atom::check_launch();

@@ -75,6 +75,7 @@ template <int MT, int RT, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    const Params p, int num_slabs) {
+  atom::pdl_trigger();   // the next kernel may be scheduled; this one waits below, after its first loads of W
   using C = Cfg<MT, RT, NS>;
   constexpr int ROWS = C::ROWS, MP = C::MP, RLD = C::RLD;
   extern __shared__ unsigned char smem_raw[];
@@ -106,32 +107,43 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
       prefetch_map(&wmap);
       prefetch_map(&xmap);
     }
-    int it = 0;   // stages issued so far, over all slabs
-    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
+    // W is written by no kernel, X by the one before this: the first ring of W loads goes out
+    // at once, then the producer waits for the kernels before it, then X follows.
+    const int my_slabs = blockIdx.x < num_slabs ? (num_slabs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total = my_slabs * num_kt;
+    const int early = total < NS ? total : NS;
+    auto issue = [&](int it, bool w_part, bool x_part) {
+      const int s = it % NS;
+      const int slab = blockIdx.x + (it / num_kt) * gridDim.x;
+      const int kc = (it % num_kt) * NCONS;
       const int n0 = slab * out_per_slab;
-      for (int kt = 0; kt < num_kt; ++kt, ++it) {
-        const int s = it % NS, u = it / NS;
-        mbar_wait(&empty[s], (u & 1) ^ 1, &aborted, p.error);
-        if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)C::STAGE);
-        __syncwarp();
-        unsigned char* stage = ring + (size_t)s * C::STAGE;
-        const int k0 = kt * BK;
-        // One operation per operand: W rows (gate rows when gated), X, and the up rows when
-        // gated.  A gated stage is [gate: 4 blocks of ROWS/2 rows][up: the same][X].
-        const int kc = k0 / BOX_COLS;
+      unsigned char* stage = ring + (size_t)s * C::STAGE;
+      // One operation per operand: W rows (gate rows when gated), X, and the up rows when
+      // gated.  A gated stage is [gate: 4 blocks of ROWS/2 rows][up: the same][X].
+      if (w_part) {
         if (lane == 0) {
+          mbar_expect_tx(&full[s], (uint32_t)C::STAGE);
           load_chunks(stage, &wmap, n0, kc, &full[s]);
-        } else if (lane == 1) {
-          load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
         } else if (lane == 2 && p.gated) {
           load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, kc, &full[s]);
         }
       }
+      if (x_part && lane == 1) load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
+    };
+    for (int it = 0; it < early; ++it) issue(it, true, false);
+    atom::pdl_wait();
+    for (int it = 0; it < early; ++it) issue(it, false, true);
+    for (int it = early; it < total; ++it) {
+      mbar_wait(&empty[it % NS], ((it / NS) & 1) ^ 1, &aborted, p.error);
+      __syncwarp();
+      issue(it, true, true);
     }
     return;
   }
 
   // ------------------------------------------------------------------ consumers
+  // (their first full barrier completes only after the producer's wait, so the outputs below
+  // are written after the kernels before this one have completed)
   const int mat = lane >> 3, r8 = lane & 7;
   const int tid = threadIdx.x;   // 0 .. NCONS * 32 - 1
   int it = 0;
@@ -268,7 +280,7 @@ static int launch(const Params& p, const void* X, int64_t lda, const void* W, cu
   const int out_per_slab = p.gated ? C::ROWS / 2 : C::ROWS;
   const int num_slabs = (p.N + out_per_slab - 1) / out_per_slab;
   const int grid = num_slabs < sm_count() ? num_slabs : sm_count();
-  kern<<<grid, NTHREADS, C::SMEM, stream>>>(wmap, xmap, p, num_slabs);
+  atom::launch_pdl(kern, dim3(grid), dim3(NTHREADS), C::SMEM, stream, wmap, xmap, p, num_slabs);
   return check_launch();
 }
 

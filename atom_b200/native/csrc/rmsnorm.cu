@@ -13,6 +13,8 @@ template <typename TA>
 __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ residual,
                                    const TA* __restrict__ delta, const void* __restrict__ w,
                                    int w_dtype, float eps, const int* __restrict__ rows, int H) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
@@ -43,6 +45,8 @@ __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ res
 template <typename TA>
 __global__ void rmsnorm_kernel(TA* __restrict__ out, const TA* __restrict__ x,
                                const void* __restrict__ w, int w_dtype, float eps, int H) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const TA* xi = x + (int64_t)blockIdx.x * H;
   TA* o = out + (int64_t)blockIdx.x * H;
@@ -66,6 +70,8 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
                                             const __nv_bfloat16* __restrict__ delta,
                                             const void* __restrict__ w, int w_dtype, float eps,
                                             const int* __restrict__ rows, int H) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
@@ -151,19 +157,15 @@ ATOM_EXPORT int atom_add_rmsnorm(void* out, int act_dtype, float* residual, cons
     }
     if (th < 64) th = 64;
     if (nv == 1)
-      atom::add_rmsnorm_bf16_vec_kernel<1><<<n_rows, th, 0, stream>>>(
-          (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<1>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
     else
-      atom::add_rmsnorm_bf16_vec_kernel<2><<<n_rows, th, 0, stream>>>(
-          (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+      atom::launch_pdl(atom::add_rmsnorm_bf16_vec_kernel<2>, dim3(n_rows), dim3(th), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
     return atom::check_launch();
   }
   if (act_dtype == ATOM_F32) {
-    atom::add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(
-        (float*)out, residual, (const float*)delta, w, w_dtype, eps, rows, H);
+    atom::launch_pdl(atom::add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, residual, (const float*)delta, w, w_dtype, eps, rows, H);
   } else if (act_dtype == ATOM_BF16) {
-    atom::add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-        (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
+    atom::launch_pdl(atom::add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, w_dtype, eps, rows, H);
   } else {
     return ATOM_ERR_ARG;
   }
@@ -176,11 +178,9 @@ ATOM_EXPORT int atom_rmsnorm(void* out, const void* x, int act_dtype, const void
   if (H <= 0 || (w_dtype != ATOM_F32 && w_dtype != ATOM_BF16)) return ATOM_ERR_ARG;
   const int threads = atom::norm_threads(H);
   if (act_dtype == ATOM_F32) {
-    atom::rmsnorm_kernel<float>
-        <<<n_rows, threads, 0, stream>>>((float*)out, (const float*)x, w, w_dtype, eps, H);
+    atom::launch_pdl(atom::rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (float*)out, (const float*)x, w, w_dtype, eps, H);
   } else if (act_dtype == ATOM_BF16) {
-    atom::rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)x, w, w_dtype, eps, H);
+    atom::launch_pdl(atom::rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, w, w_dtype, eps, H);
   } else {
     return ATOM_ERR_ARG;
   }

@@ -21,6 +21,8 @@ __global__ void qknorm_rope_kvwrite_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
     int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int64_t num_pages,
     int* __restrict__ status) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
@@ -99,6 +101,8 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
     int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
     int64_t num_pages, int* __restrict__ status) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   constexpr int MAXP = 4;   // pairs per lane and region: hd <= 512
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -205,20 +209,17 @@ ATOM_EXPORT int atom_qknorm_rope_kvwrite(void* qkv, int dtype, int T, int nh, in
   const int warps = 4;
   dim3 grid(T, (nh + 2 * nkv + warps - 1) / warps);
   if (dtype == ATOM_F32) {
-    atom::qknorm_rope_kvwrite_kernel<float><<<grid, warps * 32, 0, stream>>>(
-        (float*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos, positions,
+    atom::launch_pdl(atom::qknorm_rope_kvwrite_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, (float*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos, positions,
         seq_of_token, block_table, max_pages, page_size, (float*)k_pages, (float*)v_pages,
         num_pages, status);
   } else if (dtype == ATOM_BF16 && hd % 2 == 0 && hd <= 512 && rotary_dim % 4 == 0 &&
              (uintptr_t)qkv % 4 == 0 && (uintptr_t)k_pages % 4 == 0 && (uintptr_t)v_pages % 4 == 0 &&
              (uintptr_t)cos_sin % 8 == 0) {
-    atom::qknorm_rope_kvwrite_bf16_kernel<<<grid, warps * 32, 0, stream>>>(
-        (__nv_bfloat16*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos, positions,
+    atom::launch_pdl(atom::qknorm_rope_kvwrite_bf16_kernel, dim3(grid), dim3(warps * 32), 0, stream, (__nv_bfloat16*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos, positions,
         seq_of_token, block_table, max_pages, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
         num_pages, status);
   } else if (dtype == ATOM_BF16) {
-    atom::qknorm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
-        (__nv_bfloat16*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos,
+    atom::launch_pdl(atom::qknorm_rope_kvwrite_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, (__nv_bfloat16*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, cos_sin, rotary_dim, max_pos,
         positions, seq_of_token, block_table, max_pages, page_size, (__nv_bfloat16*)k_pages,
         (__nv_bfloat16*)v_pages, num_pages, status);
   } else {

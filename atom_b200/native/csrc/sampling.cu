@@ -61,6 +61,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
               const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
               const uint32_t* __restrict__ indices, const int* __restrict__ top_k,
               const float* __restrict__ top_p, float* __restrict__ probs, int V) {
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float fscratch[32];
   __shared__ Best bscratch[32];
   const int r = blockIdx.x;
@@ -149,7 +151,7 @@ ATOM_EXPORT int atom_sample(int* out, const float* logits, const float* temperat
   if (V <= 0) return ATOM_ERR_ARG;
   if ((top_k != nullptr || top_p != nullptr) && probs == nullptr) return ATOM_ERR_ARG;
   const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 128);
-  atom::sample_kernel<<<R, threads, 0, stream>>>(out, logits, temperature, seeds, indices, top_k,
+  atom::launch_pdl(atom::sample_kernel, dim3(R), dim3(threads), 0, stream, out, logits, temperature, seeds, indices, top_k,
                                                  top_p, probs, V);
   return atom::check_launch();
 }

@@ -29,7 +29,9 @@ class Workspace:
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False  # set while a CUDA graph holds pointers into the buffers
 
-    def get(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A view of the buffer ``tag``.  zero: the buffer is zero when it is first made (or
+        made larger); its users keep it so."""
         n = 1
         for s in shape:
             n *= s
@@ -38,7 +40,8 @@ class Workspace:
         if buf is None or buf.numel() < n:
             if self.frozen and buf is not None:
                 raise RuntimeError(f"workspace buffer '{tag}' would move while a graph holds it")
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:n].view(shape)
 
