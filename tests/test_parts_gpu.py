@@ -1,0 +1,425 @@
+"""Each part of a layer alone against the plain implementation's function for that part, at
+sizes other than the tiny models'; and a toy mixer with state of its own, defined here,
+that is registered, built into a toy architecture, loaded from a random-weights folder and
+stepped through the engine without a change to the framework's files."""
+import os
+from dataclasses import dataclass
+from typing import Any, Dict
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _rt(dtype):
+    from atom_b200.parts.base import Runtime, Workspace
+    return Runtime(dtype, torch.device(DEV), Workspace(torch.device(DEV)))
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * scale
+
+
+def _bind(part, tensors, rt):
+    dev = {}
+    for k, v in tensors.items():
+        spec = part.params()[k]
+        dt = rt.dtype if spec.role == "matrix" else (torch.float32 if rt.dtype == torch.float32 else torch.bfloat16)
+        dev[k] = v.to(dt).to(DEV).contiguous()
+    part.bind(dev, rt)
+    # what the part actually holds, widened: the reference computes on the same values
+    return {k: v.double().cpu() for k, v in dev.items()}
+
+
+def _tol(dtype):
+    return dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+
+
+def _assert_mixer_close(got, want, dtype):
+    """32-bit: the order of sums only.  bfloat16: the bounds of tests/test_replay_gpu.py for
+    outputs that pass through a sharpened softmax: single elements within 8 % of the largest
+    magnitude, the whole within 1 % rms of it."""
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+        return
+    scale = float(want.abs().max())
+    err = (got - want).abs()
+    assert float(err.max()) <= 8e-2 * scale, f"max abs error {float(err.max()):.3e} of scale {scale:.3e}"
+    assert float((err ** 2).mean().sqrt()) <= 1e-2 * scale, f"rms error {float((err ** 2).mean().sqrt()):.3e}"
+
+
+class _Cache:
+    """A cache manager, its storage and a step builder for one mixer's need."""
+
+    def __init__(self, need, dtype, page=8, pages=64):
+        from atom_b200.cache import CacheManager
+        from atom_b200.cache.storage import CacheStorage
+        from atom_b200.engine.batch import StepBuilder
+
+        self.manager = CacheManager({0: need}, page, pages, 8)
+        self.storage = CacheStorage(self.manager, dtype, torch.device(DEV))
+        self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        self.builder = StepBuilder(self.manager, DEV, 1 << 30, self.status)
+
+    def step(self, portions: Dict[str, int]):
+        """portions: request -> number of new tokens.  Returns the StepContext."""
+        from atom_b200.engine.batch import StepEntry
+
+        entries, targets = [], []
+        for rid, n in portions.items():
+            if rid not in self.manager.requests:
+                self.manager.admit(rid)
+            t = self.manager.committed(rid) + n
+            self.manager.extend(rid, t)
+            entries.append(StepEntry(rid, [0] * n, ()))
+            targets.append(t)
+        ctx = self.builder.build(entries, targets)
+        self._pending = list(zip(portions, targets))
+        return ctx
+
+    def commit(self):
+        for rid, t in self._pending:
+            self.manager.commit(rid, t)
+
+
+# ----------------------------------------------------------------------------- norm, position, embedding, head
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    H, T, eps = 200, 6, 3e-6
+    rt = _rt(dtype)
+    norm = registry.build("norm", PartSpec("rmsnorm", {"size": H, "eps": eps}))
+    w = _bind(norm, {"weight": _rand((H,), 1, 0.1) + 1}, rt)["weight"]
+    res = _rand((T, H), 2).float().to(DEV)
+    delta = _rand((T, H), 3).to(dtype).to(DEV)
+    want_res = res.double().cpu() + delta.double().cpu()
+    out = norm.add_norm(res, delta, "t")
+    torch.testing.assert_close(res.double().cpu(), want_res, rtol=1e-6, atol=1e-6)
+    want = plain.rms_norm(want_res, w, eps)
+    torch.testing.assert_close(out.double().cpu(), want, **_tol(dtype))
+
+
+def test_rotary_table_part():
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    rd, theta, n = 48, 500000.0, 300
+    pos = registry.build("position", PartSpec("rope_neox", {"rotary_dim": rd, "theta": theta, "max_position": n}))
+    table = pos.table(_rt(torch.float32)).cpu()
+    cos, sin = plain.rope_cos_sin(torch.arange(n), rd, theta)
+    assert table.shape == (n, rd)
+    torch.testing.assert_close(table[:, : rd // 2], cos, rtol=0, atol=2e-6)
+    torch.testing.assert_close(table[:, rd // 2:], sin, rtol=0, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tied", [True, False])
+def test_embedding_and_head_parts(dtype, tied):
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    V, H = 301, 192
+    rt = _rt(dtype)
+    emb = registry.build("embedding", PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}))
+    head = registry.build("head", PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": tied}))
+    E = _bind(emb, {"weight": _rand((V, H), 4, 0.05)}, rt)["weight"]
+    if tied:
+        head.bind({}, rt)
+        head.tie(emb)
+        W = E
+    else:
+        W = _bind(head, {"weight": _rand((V, H), 5, 0.05)}, rt)["weight"]
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    r = emb.forward(ids, 5)
+    assert r.dtype == torch.float32
+    torch.testing.assert_close(r.double().cpu(), E[ids.long().cpu()], rtol=0, atol=0)
+    x = _rand((3, H), 6).to(dtype).to(DEV)
+    logits = head.forward(x)
+    assert logits.dtype == torch.float32 and logits.shape == (3, V)
+    torch.testing.assert_close(logits.double().cpu(), x.double().cpu() @ W.T, **_tol(dtype))
+
+
+# ----------------------------------------------------------------------------- feed-forward, mixer, block
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [3, 40])          # few rows: fused kernel; many rows: library product + activation
+def test_gated_silu_part(dtype, T):
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    H, I = 192, 320
+    rt = _rt(dtype)
+    ffn = registry.build("ffn", PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": I}))
+    w = _bind(ffn, {"gate_up.weight": _rand((2 * I, H), 7, 0.08), "down.weight": _rand((H, I), 8, 0.08)}, rt)
+    x = _rand((T, H), 9).to(dtype).to(DEV)
+    got = ffn.forward(x, None)
+    xd = x.double().cpu()
+    want = plain.silu_and_mul(xd @ w["gate_up.weight"].T) @ w["down.weight"].T
+    torch.testing.assert_close(got.double().cpu(), want, **_tol(dtype))
+
+
+def _attention_part(dtype, window=None, bias=False):
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    H, nh, nkv, hd, eps, theta = 160, 6, 3, 32, 1e-5, 10000.0
+    rt = _rt(dtype)
+    spec = PartSpec("paged_attention", dict(
+        hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, qk_norm=True, norm_eps=eps, bias=bias,
+        window=window, position=PartSpec("rope_neox", {"rotary_dim": hd, "theta": theta, "max_position": 512})))
+    attn = registry.build("mixer", spec)
+    q, kv = nh * hd, nkv * hd
+    t = {"qkv.weight": _rand((q + 2 * kv, H), 10, 0.08), "o.weight": _rand((H, q), 11, 0.08),
+         "q_norm.weight": (_rand((hd,), 12, 0.1) + 1) * 2, "k_norm.weight": (_rand((hd,), 13, 0.1) + 1) * 2}
+    if bias:
+        t["qkv.bias"] = _rand((q + 2 * kv,), 14, 0.05)
+    w = _bind(attn, t, rt)
+    cfg = dict(num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, hidden_size=H, rms_norm_eps=eps,
+               rope_theta=theta, attention_bias=bias)
+    pw = {"a.q_proj.weight": w["qkv.weight"][:q], "a.k_proj.weight": w["qkv.weight"][q:q + kv],
+          "a.v_proj.weight": w["qkv.weight"][q + kv:], "a.o_proj.weight": w["o.weight"],
+          "a.q_norm.weight": w["q_norm.weight"], "a.k_norm.weight": w["k_norm.weight"]}
+    if bias:
+        pw.update({"a.q_proj.bias": w["qkv.bias"][:q], "a.k_proj.bias": w["qkv.bias"][q:q + kv],
+                   "a.v_proj.bias": w["qkv.bias"][q + kv:]})
+    return attn, cfg, pw, H
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,bias", [(None, False), (20, True)])
+def test_attention_part_whole_and_in_portions(dtype, window, bias):
+    attn, cfg, pw, H = _attention_part(dtype, window, bias)
+    lens = {"a": 70, "b": 33}
+    x = {r: _rand((n, H), 20 + i).to(dtype) for i, (r, n) in enumerate(lens.items())}
+    want = {r: plain.attention_block(x[r].double(), pw, "a", cfg, torch.arange(n), window)
+            for r, n in lens.items()}
+    # whole, both requests in one batch
+    c = _Cache(attn.cache_need(), dtype)
+    ctx = c.step(lens)
+    got = attn.forward(torch.cat([x["a"], x["b"]]).to(DEV), ctx, c.storage.view(0), True).double().cpu()
+    c.commit()
+    _assert_mixer_close(got[:70], want["a"], dtype)
+    _assert_mixer_close(got[70:], want["b"], dtype)
+    assert int(c.status.item()) == 0
+    # in portions: a in 37 + 2 + 31, b whole beside a's second portion, then a decodes its last token
+    c = _Cache(attn.cache_need(), dtype)
+    outs = {"a": [], "b": []}
+    done = {"a": 0, "b": 0}
+    for portions in ({"a": 37}, {"a": 2, "b": 33}, {"a": 30}, {"a": 1}):
+        ctx = c.step(portions)
+        xs = torch.cat([x[r][done[r]:done[r] + n] for r, n in portions.items()]).to(DEV)
+        y = attn.forward(xs, ctx, c.storage.view(0), True).double().cpu()
+        c.commit()
+        o = 0
+        for r, n in portions.items():
+            outs[r].append(y[o:o + n])
+            done[r] += n
+            o += n
+    for r in lens:
+        _assert_mixer_close(torch.cat(outs[r]), want[r], dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prenorm_block(dtype):
+    """norm -> mixer -> norm -> feed-forward around the 32-bit residual (one block, then the
+    closing add that the next norm would do)."""
+    from atom_b200.parts import registry
+    from atom_b200.parts.spec import PartSpec
+
+    attn, cfg, pw, H = _attention_part(dtype)
+    rt = attn.rt
+    I, eps = 224, 1e-5
+    n1 = registry.build("norm", PartSpec("rmsnorm", {"size": H, "eps": eps}))
+    n2 = registry.build("norm", PartSpec("rmsnorm", {"size": H, "eps": eps}))
+    ffn = registry.build("ffn", PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": I}))
+    w1 = _bind(n1, {"weight": _rand((H,), 30, 0.1) + 1}, rt)["weight"]
+    w2 = _bind(n2, {"weight": _rand((H,), 31, 0.1) + 1}, rt)["weight"]
+    wf = _bind(ffn, {"gate_up.weight": _rand((2 * I, H), 32, 0.08), "down.weight": _rand((H, I), 33, 0.08)}, rt)
+    block = registry.lookup("arrangement", "prenorm")(n1, attn, n2, ffn)
+    T = 29
+    r0 = _rand((T, H), 34).float()
+    res = r0.clone().to(DEV)
+    c = _Cache(attn.cache_need(), dtype)
+    ctx = c.step({"a": T})
+    delta = block.run(res, None, ctx, c.storage.view(0), True)
+    got = res.double().cpu() + delta.double().cpu()
+    r = r0.double()
+    r = r + plain.attention_block(plain.rms_norm(r, w1, eps), pw, "a", cfg, torch.arange(T), None)
+    b = plain.rms_norm(r, w2, eps)
+    r = r + plain.silu_and_mul(b @ wf["gate_up.weight"].T) @ wf["down.weight"].T
+    _assert_mixer_close(got, r, dtype)
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+
+
+def _register_toy():
+    """A mixer that keeps a running, decayed sum of its projected inputs per request:
+         s_t = d * s_(t-1) + W x_t,   y_t = s_t      (s = 0 before the request's first token)
+    Its state is one float32 vector per request, held in the request's state slot.  It is a
+    toy for this test: plain torch on the device, nothing of it is in the framework."""
+    from atom_b200.config.model_config import ModelConfig
+    from atom_b200.models.registry import register_architecture
+    from atom_b200.parts import registry
+    from atom_b200.parts.base import Mixer
+    from atom_b200.parts.spec import CacheNeed, LayerSpec, ModelSpec, ParamSpec, PartSpec, RunEntry
+
+    if "toy_decay_sum" in registry._REGISTRIES["mixer"]:
+        return
+
+    @registry.register("mixer", "toy_decay_sum")
+    class DecaySum(Mixer):
+        def __init__(self, hidden_size: int):
+            self.hidden_size = hidden_size
+
+        def params(self):
+            H = self.hidden_size
+            return {"in.weight": ParamSpec((H, H)), "decay": ParamSpec((H,), role="vector", init="norm")}
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.hidden_size,), state_dtype="float32")
+
+        def forward(self, x, step, cache, writes_cache):
+            u = (x.float() @ self.w_in_weight.float().T)
+            d = self.w_decay.float() * 0.5
+            y = torch.empty_like(u)
+            t = 0
+            for i, n in enumerate(step.q_lens):
+                slot = step.host_state_slots[i]
+                s = cache.state[slot]
+                if step.q_starts[i] == 0:
+                    s.zero_()
+                for k in range(n):
+                    s.mul_(d).add_(u[t + k])
+                    y[t + k] = s
+                t += n
+            return y.to(self.rt.dtype)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        hidden_size: int = 0
+        num_hidden_layers: int = 0
+        vocab_size: int = 0
+        intermediate_size: int = 0
+        eps: float = 1e-5
+
+        def to_dict(self) -> Dict[str, Any]:
+            return {"architectures": [self.architecture], "hidden_size": self.hidden_size,
+                    "num_hidden_layers": self.num_hidden_layers, "vocab_size": self.vocab_size,
+                    "intermediate_size": self.intermediate_size, "eps": self.eps}
+
+    def from_dict(d):
+        return ToyConfig("ToyRecurrentLM", d["hidden_size"], d["num_hidden_layers"], d["vocab_size"],
+                         d["intermediate_size"], d["eps"])
+
+    def build_spec(cfg):
+        H = cfg.hidden_size
+        pos = PartSpec("rope_neox", {"rotary_dim": 16, "theta": 10000.0, "max_position": 512})
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"l{i}"
+            if i % 2 == 0:
+                mixer = PartSpec("toy_decay_sum", {"hidden_size": H},
+                                 {"in.weight": (f"{p}.mix.in",), "decay": (f"{p}.mix.decay",)})
+            else:
+                mixer = PartSpec("paged_attention",
+                                 dict(hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16, position=pos,
+                                      qk_norm=False),
+                                 {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",)})
+            norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": cfg.eps}, {"weight": (f"{p}.{n}",)})
+            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"),
+                                    PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": cfg.intermediate_size},
+                                             {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})))
+        return ModelSpec(
+            architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, max_position=512,
+            embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": H}, {"weight": ("emb",)}),
+            layers=tuple(layers), run_order=tuple(RunEntry(i, i) for i in range(cfg.num_hidden_layers)),
+            final_norm=PartSpec("rmsnorm", {"size": H, "eps": cfg.eps}, {"weight": ("norm",)}),
+            lm_head=PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": H, "tied": True}, {}))
+
+    register_architecture("ToyRecurrentLM", from_dict, build_spec)
+
+
+def _toy_plain(model_dir, tokens):
+    """The toy architecture written out plainly: whole sequence, float64, no cache."""
+    cfg = plain.read_config(model_dir)
+    w = plain.read_tensors(model_dir)
+    H, eps = cfg["hidden_size"], cfg["eps"]
+    T = len(tokens)
+    r = w["emb"][torch.as_tensor(tokens)]
+    att_cfg = dict(num_attention_heads=4, num_key_value_heads=2, head_dim=16, hidden_size=H, rms_norm_eps=eps,
+                   rope_theta=10000.0)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"l{i}"
+        a = plain.rms_norm(r, w[f"{p}.n1"], eps)
+        if i % 2 == 0:
+            u = a @ w[f"{p}.mix.in"].T
+            d = w[f"{p}.mix.decay"] * 0.5
+            s = torch.zeros(H, dtype=torch.float64)
+            m = torch.empty_like(u)
+            for t in range(T):
+                s = d * s + u[t]
+                m[t] = s
+        else:
+            q = (a @ w[f"{p}.q"].T).view(T, 4, 16)
+            k = (a @ w[f"{p}.k"].T).view(T, 2, 16)
+            v = (a @ w[f"{p}.v"].T).view(T, 2, 16)
+            cos, sin = plain.rope_cos_sin(torch.arange(T), 16, 10000.0)
+            o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, 16 ** -0.5)
+            m = o.reshape(T, 64) @ w[f"{p}.o"].T
+        r = r + m
+        b = plain.rms_norm(r, w[f"{p}.n2"], eps)
+        gu = torch.cat((b @ w[f"{p}.gate"].T, b @ w[f"{p}.up"].T), dim=-1)
+        r = r + plain.silu_and_mul(gu) @ w[f"{p}.down"].T
+    return (plain.rms_norm(r, w["norm"], eps) @ w["emb"].T).numpy()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from atom_b200.config import EngineConfig, config_from_dict
+    from atom_b200.engine.batch import StepEntry
+    from atom_b200.engine.runner import ModelRunner
+    from atom_b200.weights import write_random_model
+
+    _register_toy()
+    cfg = config_from_dict({"architectures": ["ToyRecurrentLM"], "hidden_size": 64, "num_hidden_layers": 4,
+                            "vocab_size": 97, "intermediate_size": 80, "eps": 1e-5})
+    d = str(tmp_path / "toy")
+    write_random_model(d, cfg, seed=21)
+    runner = ModelRunner(EngineConfig(model=d, dtype="float32", kv_cache_block_size=8, num_kvcache_blocks=32,
+                                      max_num_seqs=4, enforce_eager=True))
+    assert len(runner.cache.state_needs) == 2 and len(runner.cache.groups) == 1
+    rng = np.random.default_rng(3)
+    seqs = {"x": rng.integers(0, 97, 41).tolist(), "y": rng.integers(0, 97, 23).tolist(),
+            "z": rng.integers(0, 97, 9).tolist()}
+    ref = {r: _toy_plain(d, t) for r, t in seqs.items()}
+    got = {r: [] for r in seqs}
+    done = {r: 0 for r in seqs}
+    # portions of some beside single tokens of others; z enters after y has ended and takes its slot
+    plan = [{"x": 17}, {"x": 2, "y": 20}, {"x": 1, "y": 1}, {"x": 20, "y": 2}, {"x": 1, "z": 9}]
+    for portions in plan:
+        entries = [StepEntry(r, seqs[r][done[r]:done[r] + n], list(range(n))) for r, n in portions.items()]
+        logits = runner.step(entries).cpu().numpy()
+        o = 0
+        for r, n in portions.items():
+            got[r].append(logits[o:o + n])
+            o += n
+            done[r] += n
+            if done[r] == len(seqs[r]):
+                runner.finish(r)
+    runner.check_status()
+    for r in seqs:
+        assert done[r] == len(seqs[r])
+        err = np.abs(np.concatenate(got[r]) - ref[r]).max()
+        assert err < 2e-4, f"{r}: max abs error {err:.2e}"
+    assert runner.cache.state_slots.num_free == 4
