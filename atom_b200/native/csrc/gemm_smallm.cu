@@ -109,34 +109,46 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     }
     // W is written by no kernel, X by the one before this: the first ring of W loads goes out
     // at once, then the producer waits for the kernels before it, then X follows.
-    const int my_slabs = blockIdx.x < num_slabs ? (num_slabs - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int total = my_slabs * num_kt;
-    const int early = total < NS ? total : NS;
-    auto issue = [&](int it, bool w_part, bool x_part) {
-      const int s = it % NS;
-      const int slab = blockIdx.x + (it / num_kt) * gridDim.x;
-      const int kc = (it % num_kt) * NCONS;
+    // One operation per operand and stage: W rows (gate rows when gated), X, and the up rows
+    // when gated.  A gated stage is [gate: 4 blocks of ROWS/2 rows][up: the same][X].
+    {
+      int it = 0;
+      for (int slab = blockIdx.x; slab < num_slabs && it < NS; slab += gridDim.x) {
+        const int n0 = slab * out_per_slab;
+        for (int kt = 0; kt < num_kt && it < NS; ++kt, ++it) {
+          unsigned char* stage = ring + (size_t)it * C::STAGE;
+          if (lane == 0) {
+            mbar_expect_tx(&full[it], (uint32_t)C::STAGE);
+            load_chunks(stage, &wmap, n0, kt * NCONS, &full[it]);
+          } else if (lane == 2 && p.gated) {
+            load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, kt * NCONS, &full[it]);
+          }
+        }
+      }
+    }
+    atom::pdl_wait();
+    int it = 0;   // stages issued so far, over all slabs
+    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
       const int n0 = slab * out_per_slab;
-      unsigned char* stage = ring + (size_t)s * C::STAGE;
-      // One operation per operand: W rows (gate rows when gated), X, and the up rows when
-      // gated.  A gated stage is [gate: 4 blocks of ROWS/2 rows][up: the same][X].
-      if (w_part) {
+      for (int kt = 0; kt < num_kt; ++kt, ++it) {
+        const int s = it % NS, u = it / NS;
+        unsigned char* stage = ring + (size_t)s * C::STAGE;
+        const int kc = kt * NCONS;
+        if (it < NS) {   // W of the first ring is on its way already
+          if (lane == 1) load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
+          continue;
+        }
+        mbar_wait(&empty[s], (u & 1) ^ 1, &aborted, p.error);
+        if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)C::STAGE);
+        __syncwarp();
         if (lane == 0) {
-          mbar_expect_tx(&full[s], (uint32_t)C::STAGE);
           load_chunks(stage, &wmap, n0, kc, &full[s]);
+        } else if (lane == 1) {
+          load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
         } else if (lane == 2 && p.gated) {
           load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, kc, &full[s]);
         }
       }
-      if (x_part && lane == 1) load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
-    };
-    for (int it = 0; it < early; ++it) issue(it, true, false);
-    atom::pdl_wait();
-    for (int it = 0; it < early; ++it) issue(it, false, true);
-    for (int it = early; it < total; ++it) {
-      mbar_wait(&empty[it % NS], ((it / NS) & 1) ^ 1, &aborted, p.error);
-      __syncwarp();
-      issue(it, true, true);
     }
     return;
   }
