@@ -101,6 +101,12 @@ def _check(code: int, name: str, own: bool = True) -> None:
         raise NativeError(f"{name}: {_ERR.get(code, f'error {code}')}")
 
 
+def add_launches(n: int) -> None:
+    """Counts kernels that ran without passing through the wrappers (a replayed CUDA graph)."""
+    global launches
+    launches += n
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -331,11 +337,24 @@ def flash_lib(hd: int):
     return l
 
 
-def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sm_count: int = 148):
+_sm_counts = {}
+
+
+def sm_count() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _sm_counts:
+        _sm_counts[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_counts[dev]
+
+
+def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = None):
     """Host-side launch plan: (64-row tiles of the long requests, any short request?, splits).
 
-    Short requests (at most 16 packed rows) are split along their keys so that about two
-    waves of CTAs stream the cache, each split at least 256 keys long."""
+    Short requests (at most 16 packed rows) are split along their keys.  Two CTAs fit an SM.
+    Measured on B200: one wave of CTAs (at most 2 per SM) is best, with splits no shorter than
+    256 keys; when even one split per (request, kv head) is more than a wave, the split count
+    (up to 8) that fills whole waves best."""
+    sms = sms or sm_count()
     tiles, short = 0, 0
     for n in q_lens:
         rows = n * group
@@ -345,8 +364,18 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sm_count: int = 148):
             short += 1
     splits = 1
     if short:
-        want = (4 * sm_count) // max(1, len(q_lens) * nkv)      # two CTAs per SM, two waves at most
-        splits = max(1, min(want, -(-max_ctx // 256), 64))
+        slots = 2 * sms
+        pairs = max(1, len(q_lens) * nkv)
+        longest = max(1, -(-max_ctx // 256))
+        if pairs <= slots:
+            splits = max(1, min(slots // pairs, longest, 64))
+        else:
+            best = 0.0
+            for s in range(1, min(8, longest) + 1):
+                ctas = pairs * s
+                eff = ctas / (-(-ctas // slots) * slots)
+                if eff > best + 1e-9:
+                    best, splits = eff, s
     return tiles, short > 0, splits
 
 

@@ -141,7 +141,81 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
   if (threadIdx.x == 0) out[r] = (b.i == 0x7fffffff) ? top.i : b.i;
 }
 
+// Rows without top-k / top-p: the choice is one argmax over the vocabulary,
+//   temperature 0:  of the logits;   temperature T:  of logits / T - log(E_v)
+// (the race above without the row maximum, which does not change the winner).  The vocabulary is
+// cut into `chunks` pieces that as many blocks scan at once; a second kernel picks the best piece.
+__global__ void __launch_bounds__(256)
+sample_chunk_kernel(Best* __restrict__ part, const float* __restrict__ logits,
+                    const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
+                    const uint32_t* __restrict__ indices, int V, int chunk) {
+  atom::pdl_wait();
+  atom::pdl_trigger();
+  __shared__ Best bscratch[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (int64_t)r * V;
+  const float T = temperature[r];
+  const int v0 = c * chunk, v1 = min(V, v0 + chunk);
+  Best b{-INFINITY, 0x7fffffff};
+  if (T <= 0.f) {
+    for (int v = v0 + threadIdx.x; v < v1; v += 4 * 256) {
+      float x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = (v + k * 256 < v1) ? row[v + k * 256] : -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) b = better(b, Best{x[k], v + k * 256});
+    }
+  } else {
+    const float invT = 1.f / T;
+    const uint32_t key = mix32(seeds[r] ^ mix32(indices[r] + 0x9E3779B9u));
+    for (int v = v0 + threadIdx.x; v < v1; v += 4 * 256) {
+      float x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = (v + k * 256 < v1) ? row[v + k * 256] : -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int vv = v + k * 256;
+        const uint32_t bits = mix32(((uint32_t)(vv + 1) * 0x9E3779B1u) ^ key);
+        const float u = ((float)(bits >> 8) + 0.5f) * (1.f / 16777216.f);
+        const float e = -logf(u);
+        if (vv < v1) b = better(b, Best{x[k] * invT - logf(e), vv});
+      }
+    }
+  }
+  b = block_best(b, bscratch);
+  if (threadIdx.x == 0) part[(int64_t)r * gridDim.x + c] = b;
+}
+
+__global__ void sample_pick_kernel(int* __restrict__ out, const Best* __restrict__ part, int chunks) {
+  atom::pdl_wait();
+  atom::pdl_trigger();
+  const int r = blockIdx.x;
+  Best b{-INFINITY, 0x7fffffff};
+  for (int c = threadIdx.x; c < chunks; c += 32) b = better(b, part[(int64_t)r * chunks + c]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+    b = better(b, other);
+  }
+  if (threadIdx.x == 0) out[r] = b.i == 0x7fffffff ? 0 : b.i;
+}
+
 }  // namespace atom
+
+// Rows that use neither top-k nor top-p.  part: scratch of R * chunks * 8 bytes.
+ATOM_EXPORT int atom_sample_simple(int* out, const float* logits, const float* temperature,
+                                   const uint32_t* seeds, const uint32_t* indices, void* part, int chunks,
+                                   int R, int V, cudaStream_t stream) {
+  if (R <= 0) return ATOM_OK;
+  if (V <= 0 || chunks <= 0 || chunks > 1024 || part == nullptr || R > 65535) return ATOM_ERR_ARG;
+  const int chunk = (V + chunks - 1) / chunks;
+  atom::launch_pdl(atom::sample_chunk_kernel, dim3(chunks, R), dim3(256), 0, stream, (atom::Best*)part, logits,
+                   temperature, seeds, indices, V, chunk);
+  atom::launch_pdl(atom::sample_pick_kernel, dim3(R), dim3(32), 0, stream, out, (const atom::Best*)part, chunks);
+  return atom::check_launch();
+}
 
 // probs: scratch [R, V] floats, needed only when a row filters (may be null otherwise).
 ATOM_EXPORT int atom_sample(int* out, const float* logits, const float* temperature,

@@ -13,6 +13,7 @@ from .params import SamplingParams
 
 _vp, _i = ctypes.c_void_p, ctypes.c_int
 native.declare("atom_sample", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp])
+native.declare("atom_sample_simple", [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp])
 
 
 class Sampler:
@@ -20,7 +21,23 @@ class Sampler:
         self.device = torch.device(device)
         self.default_seed = default_seed
         self._probs = None
+        self._part = None
+        self._pinned = None
+        self._events = [None] * 4
+        self._next = 0
         self.h2d_bytes = 0
+
+    def _staging(self, R: int):
+        """A pinned host array [5, R] from a ring: written again only after its copy is done."""
+        if self._pinned is None or self._pinned[0].numel() < 5 * R:
+            n = max(5 * R, 5 * 64)
+            self._pinned = [torch.zeros(n, dtype=torch.float32).pin_memory() for _ in range(4)]
+            self._events = [None] * 4
+        k = self._next
+        self._next = (k + 1) % 4
+        if self._events[k] is not None:
+            self._events[k].synchronize()
+        return self._pinned[k].numpy()[: 5 * R].reshape(5, R), k
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                indices: Sequence[int]) -> torch.Tensor:
@@ -28,7 +45,7 @@ class Sampler:
         indices[r] counts the tokens the request has generated so far.  Returns int32 [R]."""
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.is_contiguous() and len(params) == R
-        host = np.zeros((5, R), dtype=np.float32)
+        host, k = self._staging(R)
         hi = host.view(np.uint32)
         any_filter = False
         for r, p in enumerate(params):
@@ -38,9 +55,23 @@ class Sampler:
             host.view(np.int32)[3, r] = p.top_k
             host[4, r] = p.top_p
             any_filter = any_filter or (p.filters and not p.greedy)
-        dev = torch.from_numpy(host).to(self.device, non_blocking=False)
+        dev = torch.empty((5, R), dtype=torch.float32, device=self.device)
+        dev.copy_(self._pinned[k][: 5 * R].view(5, R), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[k] = ev
         self.h2d_bytes += host.nbytes
         out = torch.empty(R, dtype=torch.int32, device=self.device)
+        if not any_filter:
+            # one argmax per row: many blocks scan pieces of the vocabulary at once
+            chunks = max(1, min(64, (2 * native.sm_count()) // R, -(-V // 1024)))
+            if self._part is None or self._part.numel() < R * chunks * 2:
+                self._part = torch.empty(max(R * chunks * 2, 4096), dtype=torch.float32, device=self.device)
+            code = native.lib().atom_sample_simple(
+                out.data_ptr(), logits.data_ptr(), dev[0].data_ptr(), dev[1].data_ptr(), dev[2].data_ptr(),
+                self._part.data_ptr(), chunks, R, V, torch.cuda.current_stream().cuda_stream)
+            native._check(code, "sample_simple")
+            return out
         probs = None
         if any_filter:
             if self._probs is None or self._probs.numel() < R * V:
