@@ -86,7 +86,8 @@ def bench_attention(args) -> None:
         cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=DEV)
         cl = torch.tensor([ctx] * B, dtype=torch.int32, device=DEV)
         sot = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEV)
-        plan = native.flash_plan(q_lens, nh // nkv, nkv, ctx)
+        long_rows = native.LONG_ROWS if (args.tc and native.flash_has_tc(hd)) else 0
+        plan = native.flash_plan(q_lens, nh // nkv, nkv, ctx, long_rows=long_rows)
         scratch = torch.empty(max(1, native.flash_scratch_elems(T, nh, hd, plan[2])), dtype=torch.float32, device=DEV)
 
         def run(k, v):
@@ -100,7 +101,8 @@ def bench_attention(args) -> None:
                   flush=True)
         else:
             fl = 4.0 * nh * hd * ctx * (ctx + 1) / 2 * B
-            print(f"prefill batch={B:3d} tokens={ctx}: {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s", flush=True)
+            kind = "tcgen05" if len(plan) > 3 and plan[3] else "mma.sync"
+            print(f"prefill batch={B:3d} tokens={ctx} ({kind}): {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s", flush=True)
 
 
 def main(argv=None) -> int:
@@ -123,6 +125,7 @@ def main(argv=None) -> int:
             p.add_argument("--batch", type=ints, default=[1, 8, 64])
             p.add_argument("--context", type=int, default=4096)
             p.add_argument("--page", type=int, default=16)
+            p.add_argument("--tc", type=int, default=1, help="0: keep long portions off the tcgen05 kernel")
     args = ap.parse_args(argv)
     native.lib()
     (bench_gemm if args.what == "gemm" else bench_attention)(args)

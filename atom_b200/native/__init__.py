@@ -267,8 +267,16 @@ def error_flag(device: torch.device) -> torch.Tensor:
     return f
 
 
+def flash_has_tc(hd: int) -> bool:
+    """Whether the attention library of this head size has the tcgen05 kernel for long portions."""
+    return flash_supports(hd, torch.bfloat16) and bool(flash_lib(hd).atom_flash_has_tc())
+
+
 def check_error_flags() -> None:
     """Raises if a kernel gave up a bounded wait (synchronises the device)."""
+    for hd, l in _flash_libs.items():
+        if l.atom_flash_take_error() != 0:
+            raise NativeError(f"a bounded wait of the attention kernels (head size {hd}) ran out")
     for f in _error_flags.values():
         if int(f.item()) != 0:
             f.zero_()
@@ -309,8 +317,9 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- tensor-core attention
 
 _flash_libs = {}
-_FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i,
-              _vp, _vp]
+_FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
+              _i, _vp, _vp]
+LONG_ROWS = 128    # packed rows from which a request runs on the tcgen05 attention kernel
 
 
 def flash_supports(hd: int, dtype: torch.dtype) -> bool:
@@ -331,6 +340,8 @@ def flash_lib(hd: int):
                 l.atom_flash_attention.restype = ctypes.c_int
                 l.atom_flash_scratch_bytes.argtypes = [_i, _i, _i]
                 l.atom_flash_scratch_bytes.restype = ctypes.c_int64
+                l.atom_flash_take_error.restype = ctypes.c_int
+                l.atom_flash_has_tc.restype = ctypes.c_int
                 if l.atom_flash_head_dim() != hd:
                     raise NativeBuildError(f"{path} was built for another head size")
                 _flash_libs[hd] = l
@@ -347,18 +358,21 @@ def sm_count() -> int:
     return _sm_counts[dev]
 
 
-def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = None):
-    """Host-side launch plan: (64-row tiles of the long requests, any short request?, splits).
+def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = None, long_rows: int = 0):
+    """Host-side launch plan: (64-row tiles of the mid-size requests, any short request?,
+    splits[, 128-row tiles of the long requests when long_rows > 0]).
 
     Short requests (at most 16 packed rows) are split along their keys.  Two CTAs fit an SM.
     Measured on B200: one wave of CTAs (at most 2 per SM) is best, with splits no shorter than
     256 keys; when even one split per (request, kv head) is more than a wave, the split count
     (up to 8) that fills whole waves best."""
     sms = sms or sm_count()
-    tiles, short = 0, 0
+    tiles, short, long_tiles = 0, 0, 0
     for n in q_lens:
         rows = n * group
-        if rows > 16:
+        if long_rows and rows >= long_rows:
+            long_tiles += -(-rows // 128)
+        elif rows > 16:
             tiles += -(-rows // 64)
         elif rows > 0:
             short += 1
@@ -376,6 +390,8 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = 
                 eff = ctas / (-(-ctas // slots) * slots)
                 if eff > best + 1e-9:
                     best, splits = eff, s
+    if long_rows:
+        return tiles, short > 0, splits, long_tiles
     return tiles, short > 0, splits
 
 
@@ -393,7 +409,8 @@ def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: 
     assert tuple(k_pages.shape[1:]) == (nkv, page_size, hd) and v_pages.shape == k_pages.shape
     assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
     assert cu_q.dtype == ctx_len.dtype == seq_of_token.dtype == torch.int32
-    tiles, has_short, splits = plan
+    tiles, has_short, splits = plan[:3]
+    long_tiles = plan[3] if len(plan) > 3 else 0
     if splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
         assert scratch.numel() >= flash_scratch_elems(T, nh, hd, splits)
@@ -401,8 +418,8 @@ def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: 
     _check(l.atom_flash_attention(
         out.data_ptr(), q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
-        seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(tiles),
-        int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")
+        seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(long_tiles),
+        LONG_ROWS, int(tiles), int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")
 
 
 def flash_scratch_elems(T: int, nh: int, hd: int, splits: int) -> int:

@@ -51,6 +51,8 @@ struct Params {
   int num_splits;
   float* part_o;               // [T, nh, num_splits, HD]
   float* part_ml;              // [T, nh, num_splits, 2]
+  int* error;                  // device flag raised when a bounded wait ran out
+  int long_rows;               // requests with at least this many packed rows go to the tcgen05 kernel
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
     int tile = blockIdx.x, s = 0, nt = 0;
     for (; s < p.num_seqs; ++s) {
       const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
-      nt = rows > 16 ? (rows + BM - 1) / BM : 0;
+      nt = (rows > 16 && rows < p.long_rows) ? (rows + BM - 1) / BM : 0;
       if (tile < nt) break;
       tile -= nt;
     }
@@ -398,7 +400,7 @@ constexpr size_t decode_smem_bytes() {
   return ring > merge ? ring : merge;
 }
 
-__global__ void __launch_bounds__(NT) flash_decode_kernel(const Params p) {
+__global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
   atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -569,6 +571,48 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
 }  // namespace flash
 }  // namespace atom
 
+#if ATOM_HD == 128
+#include "attention_flash_tc.cuh"
+#endif
+
+namespace atom {
+namespace flash {
+// Raised by a kernel of this library whose bounded wait ran out.
+static __device__ int g_error_flag;
+static int* error_flag_address() {
+  static int* addr[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (addr[dev] == nullptr && cudaGetSymbolAddress((void**)&addr[dev], g_error_flag) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return addr[dev];
+}
+}  // namespace flash
+}  // namespace atom
+
+// Reads and clears the error flag of this library on the current device (synchronises): 0 if all is well.
+ATOM_EXPORT int atom_flash_take_error() {
+  int* a = atom::flash::error_flag_address();
+  int v = 0;
+  if (a == nullptr || cudaMemcpy(&v, a, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v != 0) {
+    const int zero = 0;
+    (void)cudaMemcpy(a, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}
+
+// 1 if this library has the tcgen05 kernel for long portions (head size 128).
+ATOM_EXPORT int atom_flash_has_tc() {
+#if ATOM_HD == 128
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 #define ATOM_CAT_(a, b) a##b
 #define ATOM_CAT(a, b) ATOM_CAT_(a, b)
 
@@ -580,15 +624,18 @@ ATOM_EXPORT int64_t atom_flash_scratch_bytes(int T, int nh, int num_splits) {
   return num_splits <= 1 ? 0 : (int64_t)T * nh * num_splits * (atom::flash::HD + 2) * (int64_t)sizeof(float);
 }
 
-// prefill_tiles: sum over requests with more than 16 packed rows of ceil(rows / 64); 0: none.
+// long_tiles > 0: requests with at least long_rows packed rows run on the tcgen05 kernel
+// (long_tiles = sum over them of ceil(rows / 128); needs atom_flash_has_tc() and window <= 0).
+// prefill_tiles: sum over the other requests with more than 16 packed rows of ceil(rows / 64); 0: none.
 // has_short: some request has at most 16 packed rows.  scratch: atom_flash_scratch_bytes bytes
 // when num_splits > 1.
 ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride, const void* k_pages,
                                      const void* v_pages, const int* block_table, int max_pages,
                                      int page_size, const int* cu_q, const int* ctx_len,
                                      const int* seq_of_token, int T, int num_seqs, int nh, int nkv,
-                                     int hd, float scale, int window, int prefill_tiles, int has_short,
-                                     int num_splits, void* scratch, cudaStream_t stream) {
+                                     int hd, float scale, int window, int long_tiles, int long_rows,
+                                     int prefill_tiles, int has_short, int num_splits, void* scratch,
+                                     cudaStream_t stream) {
   using namespace atom::flash;
   if (T <= 0 || num_seqs <= 0) return ATOM_OK;
   if (hd != HD || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || num_splits < 1 ||
@@ -619,6 +666,9 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   p.num_splits = num_splits;
+  p.error = atom::flash::error_flag_address();
+  p.long_rows = long_tiles > 0 ? long_rows : 0x7fffffff;
+  if (long_tiles > 0 && (!atom_flash_has_tc() || window > 0 || long_rows < 17 || p.error == nullptr)) return ATOM_ERR_ARG;
   p.part_o = (float*)scratch;
   p.part_ml = p.part_o ? p.part_o + (int64_t)T * nh * num_splits * HD : nullptr;
 
@@ -631,6 +681,19 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
       return ATOM_ERR_LAUNCH;
     attr_set = true;
   }
+#if ATOM_HD == 128
+  if (long_tiles > 0) {
+    static bool tc_attr = false;
+    if (!tc_attr) {
+      if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)tc::smem_bytes()) != cudaSuccess)
+        return ATOM_ERR_LAUNCH;
+      tc_attr = true;
+    }
+    atom::launch_pdl(tc::flash_prefill_tc_kernel, dim3(long_tiles, nkv), dim3(tc::NTHREADS), tc::smem_bytes(), stream, p,
+                     long_rows);
+  }
+#endif
   if (prefill_tiles > 0) {
     dim3 grid(prefill_tiles, nkv);
     atom::launch_pdl(flash_prefill_kernel, dim3(grid), dim3(NT), prefill_smem_bytes(), stream, p);
@@ -698,5 +761,5 @@ ATOM_EXPORT int atom_flash_attention_static(void* out, const void* q, int64_t q_
   }
   return atom_flash_attention(out, q, q_stride, k_pages, v_pages, block_table, max_pages, page_size,
                               cu_q, ctx_len, seq_of_token, T, num_seqs, nh, nkv, hd, scale, window,
-                              prefill_tiles, has_short, num_splits, scratch, stream);
+                              0, 0, prefill_tiles, has_short, num_splits, scratch, stream);
 }

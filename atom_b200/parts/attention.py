@@ -87,7 +87,9 @@ class PagedAttention(Mixer):
             T = o.shape[0]
             plan = step.plans.get(("flash", self.nh, self.nkv))
             if plan is None:
-                plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len)
+                long_rows = native.LONG_ROWS if (not self.window and native.flash_has_tc(self.hd)) else 0
+                plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
+                                         long_rows=long_rows)
                 step.plans[("flash", self.nh, self.nkv)] = plan
             scratch = None
             if plan[2] > 1:

@@ -227,9 +227,12 @@ def _run_attention(native, kind, q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, s
     if kind == "generic":
         native.paged_attention_generic(out, qd, nh * hd, kpd, vpd, btd, pos, sot, T, nh, nkv, hd, scale, window)
     else:
-        plan = native.flash_plan(q_lens, nh // nkv, nkv, max(ctx_lens))
+        long_rows = native.LONG_ROWS if (kind == "flash_tc" and native.flash_has_tc(hd)) else 0
+        plan = native.flash_plan(q_lens, nh // nkv, nkv, max(ctx_lens), long_rows=long_rows)
+        if kind == "flash_tc":
+            assert plan[3] > 0, "the case has no request long enough for the tcgen05 kernel"
         if force_splits:
-            plan = (plan[0], plan[1], force_splits)
+            plan = (plan[0], plan[1], force_splits) + tuple(plan[3:])
         scratch = None
         if plan[2] > 1:
             scratch = torch.empty(native.flash_scratch_elems(T, nh, hd, plan[2]), dtype=torch.float32, device=DEV)
@@ -264,6 +267,50 @@ def test_paged_attention(native, case, kind, dtype):
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     err = (got - want).abs().max().item()
     assert err <= tol, f"max abs error {err:.3e}"
+
+
+TC_CASES = [
+    # nh, nkv, page, q_lens, ctx_lens  (head size 128; at least one request with >= 128 packed rows)
+    (32, 8, 16, [1, 1, 200, 5], [700, 129, 333, 64]),
+    (4, 4, 16, [300], [500]),                 # group 1, a portion that continues a cached prefix
+    (8, 1, 24, [33, 64], [33, 200]),          # group 8, pages of 24 tokens
+    (6, 2, 16, [129, 1, 43, 2048 // 16], [129, 1000, 300, 128]),
+    (16, 4, 8, [520], [520]),                 # several key tiles, rows not a multiple of 128
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: f"nh{c[0]}kv{c[1]}pg{c[2]}")
+def test_tcgen05_attention(native, case):
+    nh, nkv, page, q_lens, ctx_lens = case
+    hd = 128
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=nh + page)
+    scale = hd ** -0.5
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, scale, 0)
+    got = _run_attention(native, "flash_tc", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, scale, 0)
+    native.check_error_flags()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs().max().item()
+    assert err <= 2e-2, f"max abs error {err:.3e}"
+
+
+@pytest.mark.parametrize("far", [0, 127, 128, 300, 511])
+def test_tcgen05_one_far_key_decides(native, far):
+    """As test_one_far_key_decides, for a long portion on the tcgen05 kernel: the key that
+    stands out lies at a tile's edge, in the first tile, in a middle one."""
+    nh, nkv, hd, page = 8, 2, 128, 16
+    q_lens, ctx_lens = [80], [592]
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=far)
+    row = 37                                    # a token in the middle of the portion
+    qv = q[row, 5].float()
+    key = (qv / qv.norm() * 6.0).to(torch.bfloat16)
+    k0, v0 = dense[0]
+    k0[far, 1] = key                            # query head 5 reads kv head 1
+    kp[int(bt[0, far // page]), 1, far % page] = key
+    got = _run_attention(native, "flash_tc", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, 1.0, 0)
+    native.check_error_flags()
+    torch.testing.assert_close(got[row, 5], v0[far, 1].float(), rtol=2e-2, atol=2e-2)
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, 1.0, 0)
+    assert (got - want).abs().max().item() <= 3e-2
 
 
 @pytest.mark.parametrize("splits", [2, 3, 7])
