@@ -133,6 +133,28 @@ def model_numbers(cfg, n_layers):
     return weight_bytes, kv_bytes_per_token, flops
 
 
+def reference_arm() -> dict:
+    """The unmodified reference, installed without its dependencies under baseline/_ref.  Its
+    engine imports the AMD-only ``aiter`` kernel package at module level, which exists in no
+    wheel here and has no NVIDIA build, so the arm reports why it cannot run."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "atom")):
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --no-deps --target baseline/_ref)"}
+    sys.path.insert(0, ref)
+    try:
+        import importlib
+
+        importlib.import_module("atom.model_engine.model_runner")
+    except Exception as e:      # the expected outcome on this platform
+        why = f"{type(e).__name__}: {e}".splitlines()[0][:160]
+        return {"impl": "reference", "unavailable":
+                f"ROCm/ATOM's engine cannot be imported here ({why}); every kernel it calls lives in the AMD-only aiter package"}
+    finally:
+        sys.path.remove(ref)
+    return {"impl": "reference", "unavailable":
+            "ROCm/ATOM imported, but its kernels (aiter: ROCm ASM/CK/Triton) have no NVIDIA build to run"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,9 +169,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "ROCm/ATOM's model code needs the AMD-only aiter package (ROCm kernels); "
-                          "it cannot be installed or run on an NVIDIA GPU"}))
+        print(json.dumps(reference_arm()))
         return 0
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
