@@ -317,7 +317,7 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- tensor-core attention
 
 _flash_libs = {}
-_FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
+_FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
               _i, _vp, _vp]
 LONG_ROWS = 128    # packed rows from which a request runs on the tcgen05 attention kernel
 
@@ -416,7 +416,7 @@ def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: 
         assert scratch.numel() >= flash_scratch_elems(T, nh, hd, splits)
     l = flash_lib(hd)
     _check(l.atom_flash_attention(
-        out.data_ptr(), q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
+        out.data_ptr(), q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
         block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
         seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(long_tiles),
         LONG_ROWS, int(tiles), int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")

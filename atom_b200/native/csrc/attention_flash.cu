@@ -17,6 +17,8 @@
 // Keys of a tile come into shared memory with cp.async (rows beyond the request's length, or
 // on pages a window has given back, are zero-filled), in a ring of stages; S = Q K^T and
 // O += P V run on mma.sync.m16n8k16 with P rounded to bf16.
+#include <string.h>
+
 #include "common.cuh"
 
 #ifndef ATOM_HD
@@ -624,13 +626,14 @@ ATOM_EXPORT int64_t atom_flash_scratch_bytes(int T, int nh, int num_splits) {
   return num_splits <= 1 ? 0 : (int64_t)T * nh * num_splits * (atom::flash::HD + 2) * (int64_t)sizeof(float);
 }
 
+// num_pages: pages of k_pages / v_pages (used to bound the TMA maps; 0: unknown, no TMA loading).
 // long_tiles > 0: requests with at least long_rows packed rows run on the tcgen05 kernel
 // (long_tiles = sum over them of ceil(rows / 128); needs atom_flash_has_tc() and window <= 0).
 // prefill_tiles: sum over the other requests with more than 16 packed rows of ceil(rows / 64); 0: none.
 // has_short: some request has at most 16 packed rows.  scratch: atom_flash_scratch_bytes bytes
 // when num_splits > 1.
 ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride, const void* k_pages,
-                                     const void* v_pages, const int* block_table, int max_pages,
+                                     const void* v_pages, int64_t num_pages, const int* block_table, int max_pages,
                                      int page_size, const int* cu_q, const int* ctx_len,
                                      const int* seq_of_token, int T, int num_seqs, int nh, int nkv,
                                      int hd, float scale, int window, int long_tiles, int long_rows,
@@ -683,15 +686,39 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   }
 #if ATOM_HD == 128
   if (long_tiles > 0) {
+    // TMA loading needs pages of 8, 16, ..., 128 (or more, a power of two) tokens and a group size that
+    // divides 128; otherwise the cp.async loaders take any sizes.
+    const int ps = page_size, G = p.group;
+    const bool ps_ok = (ps & (ps - 1)) == 0 && ps >= 8;
+    bool use_tma = ps_ok && G <= 128 && 128 % G == 0 && num_pages > 0 && (uint64_t)num_pages * nkv * ps < 0x7fffffffull && atom::tma::encode_fn() != nullptr && (q_stride % 8) == 0;
+    tc::Maps maps;
+    memset(&maps, 0, sizeof(maps));
+    if (use_tma) {
+      const uint64_t rows = (uint64_t)num_pages * nkv * ps;     // the page matrices [pages * nkv * page][128]
+      const uint32_t box_rows = ps < tc::TN ? ps : tc::TN;
+      uint64_t d2[2] = {128, rows}, s2[1] = {256};
+      uint32_t b2[2] = {64, box_rows};
+      uint64_t d3[3] = {128, (uint64_t)(nh + 2 * nkv), (uint64_t)T}, s3[2] = {256, (uint64_t)q_stride * 2};
+      uint32_t b3[3] = {64, (uint32_t)G, (uint32_t)(128 / G)};
+      use_tma = atom::tma::make_map_raw(&maps.k, k_pages, 2, d2, s2, b2) &&
+                atom::tma::make_map_raw(&maps.v, v_pages, 2, d2, s2, b2) &&
+                atom::tma::make_map_raw(&maps.q, q, 3, d3, s3, b3);
+    }
     static bool tc_attr = false;
     if (!tc_attr) {
-      if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)tc::smem_bytes()) != cudaSuccess ||
+          cudaFuncSetAttribute(tc::flash_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)tc::smem_bytes()) != cudaSuccess)
         return ATOM_ERR_LAUNCH;
       tc_attr = true;
     }
-    atom::launch_pdl(tc::flash_prefill_tc_kernel, dim3(long_tiles, nkv), dim3(tc::NTHREADS), tc::smem_bytes(), stream, p,
-                     long_rows);
+    if (use_tma)
+      atom::launch_pdl(tc::flash_prefill_tc_kernel<true>, dim3(long_tiles, nkv), dim3(tc::Roles<true>::NTHREADS),
+                       tc::smem_bytes(), stream, p, long_rows, maps);
+    else
+      atom::launch_pdl(tc::flash_prefill_tc_kernel<false>, dim3(long_tiles, nkv), dim3(tc::Roles<false>::NTHREADS),
+                       tc::smem_bytes(), stream, p, long_rows, maps);
   }
 #endif
   if (prefill_tiles > 0) {
@@ -759,7 +786,7 @@ ATOM_EXPORT int atom_flash_attention_static(void* out, const void* q, int64_t q_
     scratch = static_scratch_for_current_device();
     if (scratch == nullptr) return ATOM_ERR_SETUP;
   }
-  return atom_flash_attention(out, q, q_stride, k_pages, v_pages, block_table, max_pages, page_size,
+  return atom_flash_attention(out, q, q_stride, k_pages, v_pages, 0, block_table, max_pages, page_size,
                               cu_q, ctx_len, seq_of_token, T, num_seqs, nh, nkv, hd, scale, window,
                               0, 0, prefill_tiles, has_short, num_splits, scratch, stream);
 }

@@ -30,9 +30,17 @@ using atom::tma::smem_u32;
 
 constexpr int TM = 128;          // packed query rows per CTA
 constexpr int TN = 128;          // keys per tile
-constexpr int LOADERS = 256;     // loader threads: what a warp can keep in flight is limited, so many of them
-constexpr int NTHREADS = 128 + LOADERS + 32;   // 4 softmax warps, 8 loader warps, 1 MMA warp
-constexpr int MMA_WARP = (128 + LOADERS) / 32;
+// Two ways to bring K and V (and Q) into shared memory:
+//   TMA   one warp issues tensor-map boxes, one per page and 64-element half of the head (pages of a
+//         power of two of 8 to 128 tokens, a group size that divides 128).  Measured: ~88 cycles per
+//         2 KB box with 16 issuing lanes, 23 B/clk/SM, far above what cp.async can carry.
+//   else  eight warps copy with cp.async (any page size, any group size): ~2.5 B/clk per warp.
+template <bool TMA> struct Roles {
+  static constexpr int LOADERS = TMA ? 32 : 256;            // loader threads
+  static constexpr int NTHREADS = 128 + LOADERS + 32;       // 4 softmax warps, the loaders, 1 MMA warp
+  static constexpr int MMA_WARP = (128 + LOADERS) / 32;
+  static constexpr int FULL_ARRIVALS = TMA ? 1 : LOADERS;   // arrivals that complete a K or V stage
+};
 constexpr int BLOCK = 128 * 128; // bytes of one [128 rows][64 elements] swizzled block
 constexpr int K_STAGES = 3, V_STAGES = 2;   // K is wanted one tile ahead of V and is free again sooner
 constexpr uint32_t TMEM_COLS = 512;
@@ -142,13 +150,23 @@ __device__ __forceinline__ uint32_t sw_addr(uint32_t base, int row, int ch) {
 #endif
 
 struct Bars {
-  uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES], s_full[2], p_full, o_full;
+  uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES], s_full[2], p_full, o_full, q_full;
   uint32_t tmem_base;
   int aborted;
 };
 
-__global__ void __launch_bounds__(NTHREADS, 1) flash_prefill_tc_kernel(const Params p, int min_rows) {
+// Tensor maps of the TMA path: the K and V pages as matrices [pages * nkv * page_size, 128] with boxes of
+// 64 x min(page_size, 128), and the packed projection output as [tokens][heads][128] with boxes of
+// 64 x group x (128 / group), which lands as the CTA's 128 packed rows.
+struct Maps {
+  CUtensorMap k, v, q;
+};
+
+template <bool TMA>
+__global__ void __launch_bounds__(Roles<TMA>::NTHREADS, 1)
+flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Maps maps) {
   static_assert(HD == 128, "the tcgen05 attention kernel is written for head size 128");
+  constexpr int LOADERS = Roles<TMA>::LOADERS, MMA_WARP = Roles<TMA>::MMA_WARP;
   atom::pdl_wait();
   atom::pdl_trigger();
   extern __shared__ unsigned char smem_raw[];
@@ -184,17 +202,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_prefill_tc_kernel(const Par
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < K_STAGES; ++i) {
-      mbar_init(&bars->k_full[i], LOADERS);
+      mbar_init(&bars->k_full[i], Roles<TMA>::FULL_ARRIVALS);
       mbar_init(&bars->k_empty[i], 1);
     }
     for (int i = 0; i < V_STAGES; ++i) {
-      mbar_init(&bars->v_full[i], LOADERS);
+      mbar_init(&bars->v_full[i], Roles<TMA>::FULL_ARRIVALS);
       mbar_init(&bars->v_empty[i], 1);
     }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_full, 128);
     mbar_init(&bars->o_full, 1);
+    mbar_init(&bars->q_full, 1);
     bars->aborted = 0;
     mbar_fence_init();
   }
@@ -206,6 +225,57 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_prefill_tc_kernel(const Par
   volatile int* aborted = &bars->aborted;
 
   if (warp >= 4 && warp < MMA_WARP) {
+   if constexpr (TMA) {
+    // ------------------------------------------------------------------ loader, TMA: one warp
+    // A tile of 128 keys is 128 / page_size pages (or part of one page when pages are larger);
+    // every page gives two boxes, one per 64-element half of the head.  Lane l issues box l.
+    const int ps = p.page_size;
+    const int box_rows = ps < TN ? ps : TN;
+    const int ppt = TN / box_rows;                   // pages (boxes per half) of a tile
+    const int n_ops = 2 * ppt;
+    const int my_pg = lane >> 1, my_half = lane & 1;
+    const bool active = lane < n_ops;
+    // Row of the page matrix where this lane's box of tile j starts.  Pages beyond the last key
+    // are replaced by the request's first page: finite values that the causal mask removes.
+    auto box_row = [&](int j) -> int {
+      const int key = j * TN + my_pg * box_rows;
+      int lp = p.page_shift >= 0 ? (key >> p.page_shift) : (key / ps);
+      int in_page = key - lp * ps;
+      if (key >= key_end) { lp = 0; in_page = 0; }
+      const int page = active ? __ldg(w.bt + lp) : 0;
+      return (page * p.nkv + w.kvh) * ps + in_page;
+    };
+    if (lane < 2) {   // Q: the CTA's 128 packed rows are 128 / group tokens of the group's heads
+      if (lane == 0) atom::tma::mbar_expect_tx(&bars->q_full, 2 * BLOCK);
+      __syncwarp(0x3u);
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::
+              "r"(sbase + SMEM_Q + lane * BLOCK),
+          "l"(&maps.q), "r"(lane * 64), "r"(w.kvh * p.group), "r"(w.q_begin + w.row0 / p.group), "r"(smem_u32(&bars->q_full))
+          : "memory");
+    }
+    int row_k = box_row(0), row_v = row_k;
+    const int n_groups = 2 * n_tiles;     // K0, V0, K1, V1, ...
+#pragma unroll 1
+    for (int g = 0; g < n_groups; ++g) {
+      const bool is_k = (g & 1) == 0;
+      const int j = g >> 1;
+      uint64_t* full = is_k ? &bars->k_full[j % K_STAGES] : &bars->v_full[j % V_STAGES];
+      if (is_k) {
+        if (j >= K_STAGES) mbar_wait(&bars->k_empty[j % K_STAGES], ((j / K_STAGES) & 1) ^ 1, aborted, p.error);
+      } else {
+        if (j >= V_STAGES) mbar_wait(&bars->v_empty[j % V_STAGES], ((j / V_STAGES) & 1) ^ 1, aborted, p.error);
+      }
+      if (lane == 0) atom::tma::mbar_expect_tx(full, 2 * BLOCK);
+      __syncwarp();
+      if (active) {
+        const uint32_t dst = (is_k ? sbase + SMEM_K + (j % K_STAGES) * 2 * BLOCK : sbase + SMEM_V + (j % V_STAGES) * 2 * BLOCK) +
+                             my_half * BLOCK + my_pg * box_rows * 128;
+        atom::tma::load_box(reinterpret_cast<void*>(0), is_k ? &maps.k : &maps.v, my_half * 64, is_k ? row_k : row_v, full, dst);
+      }
+      if (is_k) row_k = box_row(j + 1); else row_v = box_row(j + 1);   // looked up a tile ahead
+    }
+   } else {
     // ------------------------------------------------------------------ loaders
     constexpr int RSTEP = LOADERS / 16, RPT = 128 / RSTEP;   // a thread's rows are r0, r0 + RSTEP, ...: RPT of them
     const int t = threadIdx.x - 128;               // 0 .. LOADERS - 1
@@ -288,6 +358,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_prefill_tc_kernel(const Par
       }
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // nothing of this thread is in flight when it leaves
+   }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -307,6 +378,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) flash_prefill_tc_kernel(const Par
         umma_commit(&bars->s_full[j & 1]);
         umma_commit(&bars->k_empty[st]);
       };
+      if constexpr (TMA) {
+        mbar_wait(&bars->q_full, 0, aborted, p.error);
+      }
       if (n_tiles > 0) issue_s(0);
       for (int j = 0; j < n_tiles; ++j) {
         if (j + 1 < n_tiles) issue_s(j + 1);

@@ -79,6 +79,28 @@ inline bool make_map_chunked(CUtensorMap* map, const void* base, uint64_t rows, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A bf16 map of rank 2 or 3 given outright: sizes (innermost first), byte strides of the outer
+// dimensions, box sizes; 128-byte swizzle (box[0] must be 64).
+inline bool make_map_raw(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                         const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || rank < 2 || rank > 3 || ((uintptr_t)base % 16) != 0 || box[0] != (uint32_t)BOX_COLS) return false;
+  cuuint64_t d[3], st[2];
+  cuuint32_t b[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] == 0 || box[i] == 0 || box[i] > 256) return false;
+    d[i] = dims[i];
+    b[i] = box[i];
+  }
+  for (int i = 0; i < rank - 1; ++i) {
+    if (strides[i] % 16 != 0) return false;
+    st[i] = strides[i];
+  }
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, st, b, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Maps are cached by what they describe: encoding costs a few microseconds on the host.
 struct MapKey {
   const void* base;
@@ -165,6 +187,17 @@ __device__ __forceinline__ void load_box(void* smem_dst, const CUtensorMap* map,
       "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// The same with the destination given as a 32-bit shared-memory address (`smem_dst` is ignored).
+__device__ __forceinline__ void load_box(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar,
+                                         uint32_t smem_addr) {
+  (void)smem_dst;
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+          "r"(smem_addr),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // Chunked map: loads chunks [chunk, chunk + box_chunks) of rows [row, row + box_rows).
 __device__ __forceinline__ void load_chunks(void* smem_dst, const CUtensorMap* map, int row, int chunk,
                                             uint64_t* bar) {
