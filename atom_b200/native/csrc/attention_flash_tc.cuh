@@ -414,6 +414,77 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
       mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, aborted, p.error);
       tc_fence_after();
       if (threadIdx.x == 0) TC_TRACE(1, j);
+     if constexpr (TMA) {
+      const uint32_t scol = tmem + lane_base + ((j & 1) ? S_COL1 : S_COL0);
+      const int key0 = j * TN;
+      const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
+      // The whole row in registers (the TMA variant has few threads, so many registers each): one
+      // round trip to tensor memory per tile.
+      float s[TN];
+#pragma unroll
+      for (int q = 0; q < TN / 32; ++q) tmem_ld32(scol + q * 32, s + q * 32);
+      tmem_wait_ld();
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < TN; ++i)
+          if (key0 + i > pos) s[i] = -INFINITY;
+      }
+      float mx8[8] = {m, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < TN; i += 8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = ex2((m - m_use) * c);
+      const float mc = m_use * c;
+      if (threadIdx.x == 0) TC_TRACE(2, j);
+      // the exponentials do not depend on the tile before; only O and the P buffer do
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < TN; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[i + e] = ex2(fmaf(s[i + e], c, -mc));
+          sum4[e] += s[i + e];
+        }
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      if (threadIdx.x == 0) TC_TRACE(3, j);
+      if (j > 0) {
+        mbar_wait(&bars->o_full, (j - 1) & 1, aborted, p.error);
+        tc_fence_after();
+        if (threadIdx.x == 0) TC_TRACE(4, j);
+        if (__any_sync(0xffffffffu, mx > m)) {      // some row of this warp has a new maximum: rescale O
+#pragma unroll
+          for (int q = 0; q < HD / 32; ++q) {
+            float o[32];
+            tmem_ld32(tmem + lane_base + O_COL + q * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(tmem + lane_base + O_COL + q * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      m = mx;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[8 * k + 2 * e], s[8 * k + 2 * e + 1]);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        const uint32_t a = sw_addr(sbase + SMEM_P, r, k);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(a), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                     "r"(pk[3])
+                     : "memory");
+      }
+     } else {
       // Two passes over the row in tensor memory, 32 columns at a time (few live registers, the
       // next chunk's load in flight while this one is worked on): first the maximum, then P.
       const uint32_t scol = tmem + lane_base + ((j & 1) ? S_COL1 : S_COL0);
@@ -501,6 +572,7 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
         }
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+     }
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->p_full);
