@@ -17,7 +17,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import ScheduledStep, Scheduler
+from .scheduler import ScheduledEntry, ScheduledStep, Scheduler
 from .sequence import Sequence
 
 
@@ -31,6 +31,14 @@ def _load_tokenizer(model_dir: str):
         return AutoTokenizer.from_pretrained(model_dir)
     except Exception:  # pragma: no cover - depends on the folder
         return None
+
+
+class _Pending:
+    """A launched step: its schedule, the sampled ids on the device, their pinned host copy
+    (in flight) and the event that marks the copy's end."""
+
+    def __init__(self, sched, ids, host, event):
+        self.sched, self.ids, self.host, self.event = sched, ids, host, event
 
 
 class LLMEngine:
@@ -57,6 +65,15 @@ class LLMEngine:
         self.num_prompt_tokens = 0
         self.num_generated_tokens = 0
         self.d2h_bytes = 0      # bytes of sampled token ids read back to the host so far
+        # A decode step that has been launched but whose tokens the host has not read yet.  The
+        # next decode step is launched before they are read (its tokens stay on the device), so
+        # the host's work for a step overlaps the device's work for the one before: the
+        # reference's deferred output (atom/model_engine/model_runner.py:204-223, :358-392).
+        self._pending: Optional[_Pending] = None
+        self.overlap_steps = not self.config.enforce_eager
+        self.num_overlapped = 0
+        self._pin_ring = None
+        self._pin_next = 0
 
     # ------------------------------------------------------------------ requests
 
@@ -81,9 +98,6 @@ class LLMEngine:
     def abort(self, seq_id: int) -> None:
         self.scheduler.abort(seq_id)
 
-    def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
-
     def _seed_of(self, seq: Sequence) -> int:
         if seq.params.seed is not None:
             return seq.params.seed
@@ -91,8 +105,81 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ one step
 
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished() and self._pending is None
+
+    def _sample(self, logits, sampling: List[Sequence], ahead: int = 0) -> torch.Tensor:
+        return self.sampler.sample(
+            logits, [s.params for s in sampling], [self._seed_of(s) for s in sampling],
+            [s.num_output_tokens + ahead for s in sampling])
+
+    def _read_later(self, sched: ScheduledStep, ids: torch.Tensor) -> "_Pending":
+        """Starts the copy of the sampled ids to pinned host memory; the host waits for it later."""
+        if self._pin_ring is None or self._pin_ring[0].numel() < ids.numel():
+            self._pin_ring = [torch.empty(max(ids.numel(), 64), dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._pin_next = (self._pin_next + 1) % 4      # a buffer is read two calls later at most
+        host = self._pin_ring[self._pin_next][: ids.numel()]
+        host.copy_(ids, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return _Pending(sched, ids, host, ev)
+
+    def _resolve(self, pending: "_Pending") -> List[Sequence]:
+        """Waits for a launched step's tokens and does its bookkeeping."""
+        pending.event.synchronize()
+        tokens = pending.host.tolist()
+        self.d2h_bytes += 4 * len(tokens)
+        self.num_generated_tokens += len(tokens)
+        return self.scheduler.postprocess(pending.sched, tokens)
+
+    def _look_ahead(self, pending: "_Pending") -> Optional["_Pending"]:
+        """Launches the decode step after ``pending`` without knowing its tokens, if nothing but
+        one more token per running request can happen: nobody waits, the running requests are
+        exactly those of the pending step, none of them ends with the pending token for a reason
+        the host can foresee (token count, length), and their next positions have pages."""
+        sch = self.scheduler
+        seqs = [e.seq for e in pending.sched.entries]
+        if sch.waiting or len(seqs) != len(sch.running) or any(a is not b for a, b in zip(seqs, sch.running)):
+            return None
+        if len(seqs) > sch.max_num_batched_tokens:
+            return None
+        entries, sched = [], ScheduledStep()
+        for e in pending.sched.entries:
+            s = e.seq
+            if not e.samples or e.num_tokens != 1:
+                return None
+            if s.num_output_tokens + 1 >= s.params.max_tokens or s.num_tokens + 1 >= sch.max_model_len:
+                return None
+            start = e.start + 1                      # position of the token the pending step produces
+            if not self.runner.cache.can_extend(s.seq_id, start + 1):
+                return None
+            entries.append(StepEntry(s.seq_id, [0], (0,)))
+            sched.entries.append(ScheduledEntry(s, start, 1, True))
+        if not self.runner._graph_size(entries):
+            return None
+        logits = self.runner.step(entries, device_tokens=pending.ids)
+        ids = self._sample(logits, seqs, ahead=1)
+        self.num_steps += 1
+        self.num_overlapped += 1
+        return self._read_later(sched, ids)
+
     def step(self) -> List[Sequence]:
-        """schedule -> run the batch -> sample -> bookkeeping; returns what finished."""
+        """schedule -> run the batch -> sample -> bookkeeping; returns what finished.
+
+        A pure decode step is left pending (launched, tokens unread); the next call first tries
+        to launch the following decode step and only then reads the pending tokens, so a
+        request's tokens reach the host one call later than they were computed."""
+        if self._pending is not None:
+            pending, self._pending = self._pending, None
+            ahead = self._look_ahead(pending) if self.overlap_steps else None
+            finished = self._resolve(pending)
+            if ahead is not None:
+                self._pending = ahead
+                return finished
+            return finished + self._step_now()
+        return self._step_now()
+
+    def _step_now(self) -> List[Sequence]:
         sched: ScheduledStep = self.scheduler.schedule()
         finished = list(sched.rejected)
         if not sched.entries:
@@ -104,18 +191,19 @@ class LLMEngine:
             if e.samples:
                 sampling.append(e.seq)
         logits = self.runner.step(entries)
-        tokens: List[int] = []
-        if sampling:
-            ids = self.sampler.sample(
-                logits, [s.params for s in sampling], [self._seed_of(s) for s in sampling],
-                [s.num_output_tokens for s in sampling])
-            tokens = ids.tolist()
-            self.d2h_bytes += 4 * len(tokens)
         self.num_steps += 1
         self.num_prompt_tokens += sum(e.num_tokens for e in sched.entries if not (e.samples and e.num_tokens == 1))
+        if not sampling:
+            return finished + self.scheduler.postprocess(sched, [])
+        ids = self._sample(logits, sampling)
+        pure_decode = all(e.samples and e.num_tokens == 1 for e in sched.entries)
+        if self.overlap_steps and pure_decode and self.runner._graph_size(entries):
+            self._pending = self._read_later(sched, ids)
+            return finished
+        tokens = ids.tolist()
+        self.d2h_bytes += 4 * len(tokens)
         self.num_generated_tokens += len(tokens)
-        finished += self.scheduler.postprocess(sched, tokens)
-        return finished
+        return finished + self.scheduler.postprocess(sched, tokens)
 
     # ------------------------------------------------------------------ whole requests
 

@@ -141,14 +141,23 @@ class ModelRunner:
         return targets
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch; returns logits [R, vocab] float32 on the device, rows in the order
-        of the entries and of their ``want`` lists.  The cache then holds the new tokens."""
+        of the entries and of their ``want`` lists.  The cache then holds the new tokens.
+
+        device_tokens: for a batch of single-token requests whose tokens are still on the device
+        (the sampler's output of the step before, int32 [len(entries)], in the entries' order):
+        they replace the entries' token values, which are then placeholders.  The host never
+        has to see them before this step is launched."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         targets = self._reserve(entries)
         size = self._graph_size(entries)
-        if size:
+        if device_tokens is not None:
+            if not size or device_tokens.dtype != torch.int32 or device_tokens.numel() != len(entries):
+                raise StepError("device_tokens needs a captured decode step and one int32 token per entry")
+            logits = self._step_graph(entries, targets, size, device_tokens)
+        elif size:
             logits = self._step_graph(entries, targets, size)
         else:
             ctx = self.builder.build(entries, targets)
@@ -207,11 +216,14 @@ class ModelRunner:
             self.rt.workspace = saved
         return g
 
-    def _step_graph(self, entries: Sequence[StepEntry], targets: List[int], size: int) -> torch.Tensor:
+    def _step_graph(self, entries: Sequence[StepEntry], targets: List[int], size: int,
+                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = self._graphs.get(size)
         if g is None:
             g = self._graphs[size] = self._capture(size)
-        self.builder.build_fixed(entries, targets, size, self._table_width)
+        ctx = self.builder.build_fixed(entries, targets, size, self._table_width)
+        if device_tokens is not None:
+            ctx.token_ids[: len(entries)].copy_(device_tokens)     # on the stream, after the arrays' copy
         g.graph.replay()
         native.add_launches(g.num_launches)
         self.graph_replays += 1

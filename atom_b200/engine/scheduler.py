@@ -191,6 +191,9 @@ class Scheduler:
         it = iter(sampled)
         for e in step.entries:
             seq = e.seq
+            if seq.is_finished:      # ended while this (look-ahead) step was in flight: its token is dropped
+                next(it, None) if e.samples else None
+                continue
             seq.num_computed = e.start + e.num_tokens
             if not e.samples:
                 continue

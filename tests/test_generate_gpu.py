@@ -160,3 +160,42 @@ def test_command_line(model_dirs, capsys):
     text = capsys.readouterr().out
     cfg, w = _plain(model_dirs["A"])
     assert "Prompt: [5, 17, 3]" in text and f"Completion: {plain.generate_greedy(cfg, w, [5, 17, 3], 5)!r}" in text
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_decode_steps_give_the_same_tokens(model_dirs, dtype):
+    """With CUDA graphs on, a decode step is launched before the tokens of the step before it
+    have reached the host.  The tokens are those of the plain implementation all the same,
+    also when a request stops on a token value (seen one step late) while others go on, and
+    with seeded temperature sampling."""
+    from atom_b200 import SamplingParams
+    name = "B"
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [3, 12, 29, 40], seed=3)
+    ref = [plain.generate_greedy(cfg, w, p, 24) for p in prompts]
+    eng = _engine(model_dirs[name], dtype, pages=64, page=8, enforce_eager=False, cudagraph_capture_sizes=[1, 2, 4],
+                  max_model_len=256)
+    stop = ref[1][9]                                   # request 1 stops at the first occurrence of this token
+    sps = [SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True),
+           SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, stop_token_ids=[stop]),
+           SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True),
+           SamplingParams(temperature=0.8, max_tokens=24, ignore_eos=True, seed=11)]
+    outs = eng.generate(prompts, sps)
+    assert eng.num_overlapped > 10
+    margin = 0 if dtype == "float32" else 0.08
+    if dtype == "float32":
+        assert outs[0]["token_ids"] == ref[0]
+        assert outs[1]["token_ids"] == ref[1][: ref[1].index(stop) + 1] and outs[1]["finish_reason"] == f"stop_{stop}"
+        assert outs[2]["token_ids"] == ref[2][:7] and outs[2]["finish_reason"] == "max_tokens"
+        ids = list(prompts[3])
+        for j, tok in enumerate(outs[3]["token_ids"]):
+            assert tok == plain.sample_temperature(plain.forward(cfg, w, ids)[-1], 0.8, 11, j)
+            ids.append(tok)
+    else:
+        for i in (0, 2):
+            _check_greedy_against_plain(cfg, w, prompts[i], outs[i]["token_ids"], margin)
+    assert all(g.pool.num_used == 0 for g in eng.runner.cache.groups)
+    # the same engine without overlap gives the same tokens
+    eng.overlap_steps = False
+    again = eng.generate(prompts, sps)
+    assert [o["token_ids"] for o in again] == [o["token_ids"] for o in outs]
