@@ -364,8 +364,9 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = 
 
     Short requests (at most 16 packed rows) are split along their keys.  Two CTAs fit an SM.
     Measured on B200: one wave of CTAs (at most 2 per SM) is best, with splits no shorter than
-    256 keys; when even one split per (request, kv head) is more than a wave, the split count
-    (up to 8) that fills whole waves best."""
+    256 keys; when even one split per (request, kv head) is more than a wave, a larger split
+    count (up to 8) only where it fills whole waves at least 15 % better (every split costs a
+    pass of the merge kernel over its partial sums)."""
     sms = sms or sm_count()
     tiles, short, long_tiles = 0, 0, 0
     for n in q_lens:
@@ -388,7 +389,7 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = 
             for s in range(1, min(8, longest) + 1):
                 ctas = pairs * s
                 eff = ctas / (-(-ctas // slots) * slots)
-                if eff > best + 1e-9:
+                if eff > best * 1.15:
                     best, splits = eff, s
     if long_rows:
         return tiles, short > 0, splits, long_tiles

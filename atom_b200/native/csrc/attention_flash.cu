@@ -17,9 +17,17 @@
 // Keys of a tile come into shared memory with cp.async (rows beyond the request's length, or
 // on pages a window has given back, are zero-filled), in a ring of stages; S = Q K^T and
 // O += P V run on mma.sync.m16n8k16 with P rounded to bf16.
+//
+// Where the head size is a multiple of 64 and a page holds a power of two >= 8 of tokens, short
+// requests run on another kernel (flash_decode_tma_kernel): pages come as TMA boxes (a warp's
+// own cp.async stream carries ~2.5 bytes a clock, far less than the memory system gives a CTA),
+// and the products are transposed, S^T = K Q^T and O^T = V^T P^T, so that the 16-wide side of
+// the instruction runs over keys and the 8-wide side over the few query rows.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 #ifndef ATOM_HD
 #error "compile with -DATOM_HD=<head size>"
@@ -395,6 +403,39 @@ __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
 
 // ------------------------------------------------------------------ short requests (decode)
 
+// Combines the four warps' partial results (each saw other keys) that lie in shared memory,
+// mo[warp][16 rows][MLD], mm / ml [warp][16], and writes the result or this split's partial sums.
+constexpr int MLD = HD + 8;   // padded row: conflict-free fragment stores
+__device__ __forceinline__ void decode_combine(const Params& p, const Work& w, int split, const float* mo,
+                                               const float* mm, const float* ml) {
+  for (int idx = threadIdx.x; idx < w.rows_total * HD; idx += NT) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) M = fmaxf(M, mm[k * 16 + row]);
+    const float Mu = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float f = exp2f((mm[k * 16 + row] - Mu) * p.scale_log2);
+      L += ml[k * 16 + row] * f;
+      O += mo[(k * 16 + row) * MLD + d] * f;
+    }
+    const int tok = row / p.group, hig = row - tok * p.group;
+    const int64_t th = (int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig);
+    if (p.num_splits == 1) {
+      p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+    } else {
+      p.part_o[(th * p.num_splits + split) * HD + d] = O;
+      if (d == 0) {
+        p.part_ml[(th * p.num_splits + split) * 2] = M;
+        p.part_ml[(th * p.num_splits + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+
 constexpr int DECODE_STAGES = 3;
 constexpr size_t decode_smem_bytes() {
   const size_t ring = sizeof(__nv_bfloat16) * (size_t)(16 * LDS + DECODE_STAGES * 2 * BN * LDS);
@@ -473,7 +514,6 @@ __global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
   __syncthreads();   // the ring is free: it becomes the merge buffer
 
   // Merge the four warps (each saw other keys).
-  constexpr int MLD = HD + 8;                            // padded row: conflict-free fragment stores
   float* mo = reinterpret_cast<float*>(smem_raw);       // [4][16][MLD]
   float* mm = mo + 4 * 16 * MLD;                         // [4][16]
   float* ml = mm + 4 * 16;                               // [4][16]
@@ -494,32 +534,405 @@ __global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < w.rows_total * HD; idx += NT) {
-    const int row = idx / HD, d = idx - row * HD;
-    float M = -INFINITY;
+  decode_combine(p, w, split, mo, mm, ml);
+}
+
+#if ATOM_HD % 64 == 0
+// ------------------------------------------------------------------ short requests, TMA and transposed products
+//
+// Every warp works alone: it takes tiles w, w + 4, ... (KTW keys each) of the CTA's keys through a
+// ring of its own (RING stages, one mbarrier each), and refills a stage itself as soon as it has
+// left it, so there is no CTA-wide barrier in the loop and a warp only ever waits for a phase
+// that it started itself.  (With a ring shared by the warps a warp could run two phases ahead of
+// a stage whose earlier tile belongs to another warp, which a parity wait cannot tell apart.)
+// A stage holds its keys as boxes of min(page, KTW) keys (one page, or a piece of a larger one),
+// each box laid out [64-column half][key][64 columns] with the 128-byte swizzle.  Lane
+// l < 2 * boxes issues box l / 2 of K (l even) or V (l odd), with the page looked up one tile
+// ahead.  Every box is always issued, so a stage always receives the same number of bytes: a box
+// past the request's end, or on a page that a window gave back, is read from the request's last
+// page instead and masked like any key outside the causal range (the cache holds finite numbers
+// everywhere, so 0 * V is 0).
+//
+// A warp's tile: S^T[KTW keys, 8 NQ rows] = K Q^T (A = K from ldmatrix, B = Q^T held in
+// registers; two accumulators over the head size to shorten the dependent chain), softmax down
+// the key axis (a thread holds keys g, g + 8 of each 16 for columns 2 t4, 2 t4 + 1; the maximum
+// goes over the lanes of equal t4, the denominator stays a per-thread partial sum until the
+// end), P^T to bf16 and through movmatrix into B fragments, and O^T[HD, 8 NQ] += V^T P^T
+// (A = V^T from ldmatrix.trans).
+//
+// KTW, the keys of a warp's tile, is 16 or 32: with 16 two CTAs share an SM, which overlaps one
+// CTA's start and end with the other's loads (better for grids of several waves); with 32 the
+// per-tile costs are spread over more keys (better where every CTA has an SM to itself).
+constexpr int RING = 3;                    // stages of a warp's ring
+__host__ __device__ constexpr int tma_stage_bytes(int ktw) { return 2 * ktw * HD * 2; }
+constexpr size_t decode_tma_smem_bytes(int ktw) {
+  const size_t ring = 1024 + (size_t)4 * RING * tma_stage_bytes(ktw) + sizeof(__nv_bfloat16) * 16 * LDS +
+                      sizeof(uint64_t) * 4 * RING;
+  const size_t merge = sizeof(float) * (size_t)(4 * 16 * (MLD + 2));
+  return ring > merge ? ring : merge;
+}
+constexpr bool decode_tma_fits(int ktw) { return decode_tma_smem_bytes(ktw) <= 227 * 1024; }
+// CTAs that share an SM
+constexpr int decode_tma_ctas(int ktw) { return decode_tma_smem_bytes(ktw) + 1024 <= (227 * 1024) / 2 ? 2 : 1; }
+static_assert(decode_tma_fits(16), "the rings must fit an SM");
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+
+// Running state of a warp over NQ * 8 query rows, transposed: o[dm][nq] is the C fragment of
+// O^T rows dm * 16 + {g, g + 8}, columns nq * 8 + {2 t4, 2 t4 + 1}.
+template <int NQ>
+struct AccT {
+  float o[HD / 16][NQ][4];
+  float m[NQ][2], l[NQ][2];
+  __device__ __forceinline__ void init() {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) M = fmaxf(M, mm[k * 16 + row]);
-    const float Mu = (M == -INFINITY) ? 0.f : M;
-    float L = 0.f, O = 0.f;
+    for (int i = 0; i < HD / 16; ++i)
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float f = exp2f((mm[k * 16 + row] - Mu) * p.scale_log2);
-      L += ml[k * 16 + row] * f;
-      O += mo[(k * 16 + row) * MLD + d] * f;
+      for (int n = 0; n < NQ; ++n) o[i][n][0] = o[i][n][1] = o[i][n][2] = o[i][n][3] = 0.f;
+#pragma unroll
+    for (int n = 0; n < NQ; ++n) {
+      m[n][0] = m[n][1] = -INFINITY;
+      l[n][0] = l[n][1] = 0.f;
     }
-    const int tok = row / p.group, hig = row - tok * p.group;
-    const int64_t th = (int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig);
-    if (p.num_splits == 1) {
-      p.out[th * HD + d] = __float2bfloat16_rn(O / L);
-    } else {
-      p.part_o[(th * p.num_splits + split) * HD + d] = O;
-      if (d == 0) {
-        p.part_ml[(th * p.num_splits + split) * 2] = M;
-        p.part_ml[(th * p.num_splits + split) * 2 + 1] = L;
+  }
+};
+
+// One KTW-key tile of a warp.  sK / sV: the stage's K and V; qf: B fragments of Q^T (or read from
+// sQ when they do not fit in registers); pos[nq][j]: position of query row nq * 8 + 2 t4 + j (-1: none).
+template <int NQ, int KTW>
+__device__ __forceinline__ void warp_tile_t(AccT<NQ>& acc, const uint32_t (*qf)[NQ][2], const __nv_bfloat16* sQ,
+                                            const unsigned char* sK, const unsigned char* sV, int key0,
+                                            const int (*pos)[2], int window, float c, bool mask, int box_shift) {
+  constexpr int MT = KTW / 16;
+  const int lane = threadIdx.x & 31;
+  const int mat = lane >> 3, r8 = lane & 7, g = lane >> 2;
+  const int half_stride = 128 << box_shift;
+  // byte offset of key row kr (first half, chunk 0) in a stage
+  auto sw_row = [&](int kr) {
+    return (((kr >> box_shift) * HD) << (box_shift + 1)) + (kr & ((1 << box_shift) - 1)) * 128;
+  };
+  float s[MT][NQ][4];
+
+  // S^T = K Q^T, even and odd 16-column steps in accumulators of their own
+  {
+    float s2[MT][NQ][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[mt][n][e] = s2[mt][n][e] = 0.f;
+    int krow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) krow[mt] = sw_row(mt * 16 + (mat & 1) * 8 + r8);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      uint32_t b[NQ][2];
+      if (Q_IN_REGS) {
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) b[n][0] = qf[ks][n][0], b[n][1] = qf[ks][n][1];
+      } else {
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) {
+          const __nv_bfloat16* qrow = sQ + (n * 8 + g) * LDS + ks * 16 + 2 * (lane & 3);
+          b[n][0] = *reinterpret_cast<const uint32_t*>(qrow);
+          b[n][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
+        }
+      }
+      const int koff = (ks >> 2) * half_stride + ((((ks * 2) & 7) + (mat >> 1)) ^ r8) * 16;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4(a, sK + krow[mt] + koff);
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) {
+          if (ks & 1)
+            mma_bf16(s2[mt][n], a, b[n][0], b[n][1]);
+          else
+            mma_bf16(s[mt][n], a, b[n][0], b[n][1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[mt][n][e] += s2[mt][n][e];
+  }
+
+  if (mask) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + mt * 16 + g + (e >> 1) * 8;
+          const int ps = pos[n][e & 1];
+          bool ok = j <= ps;
+          if (window > 0) ok = ok && (j > ps - window);
+          if (!ok) s[mt][n][e] = -INFINITY;
+        }
+  }
+
+  // online softmax down the keys
+  bool changed = false;
+  float corr[NQ][2];
+#pragma unroll
+  for (int n = 0; n < NQ; ++n)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mx = fmaxf(mx, fmaxf(s[mt][n][j], s[mt][n][j + 2]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(acc.m[n][j], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      changed = changed || (m_new > acc.m[n][j]);
+      corr[n][j] = exp2f((acc.m[n][j] - m_use) * c);
+      acc.m[n][j] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float p0 = exp2f((s[mt][n][j] - m_use) * c);
+        const float p1 = exp2f((s[mt][n][j + 2] - m_use) * c);
+        s[mt][n][j] = p0;
+        s[mt][n][j + 2] = p1;
+        sum += p0 + p1;
+      }
+      acc.l[n][j] = acc.l[n][j] * corr[n][j] + sum;
+    }
+  if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll
+    for (int dm = 0; dm < HD / 16; ++dm)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n) {
+        acc.o[dm][n][0] *= corr[n][0];
+        acc.o[dm][n][1] *= corr[n][1];
+        acc.o[dm][n][2] *= corr[n][0];
+        acc.o[dm][n][3] *= corr[n][1];
+      }
+  }
+
+  // O^T += V^T P^T
+  {
+    uint32_t pb[MT][NQ][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n) {
+        pb[mt][n][0] = movmatrix_trans(pack_bf16(s[mt][n][0], s[mt][n][1]));
+        pb[mt][n][1] = movmatrix_trans(pack_bf16(s[mt][n][2], s[mt][n][3]));
+      }
+    int vrow[MT];
+#pragma unroll
+    for (int kk = 0; kk < MT; ++kk) vrow[kk] = sw_row(kk * 16 + (mat >> 1) * 8 + r8);
+#pragma unroll
+    for (int dm = 0; dm < HD / 16; ++dm) {
+      const int voff = (dm >> 2) * half_stride + ((((dm * 2) & 7) + (mat & 1)) ^ r8) * 16;
+#pragma unroll
+      for (int kk = 0; kk < MT; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, sV + vrow[kk] + voff);
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) mma_bf16(acc.o[dm][n], a, pb[kk][n][0], pb[kk][n][1]);
       }
     }
   }
 }
+
+// The work of one warp of a short-request CTA over KTW-key tiles [tile_begin, tile_end) of the
+// request.  ring / full: this warp's stages and their barriers.
+template <int NQ, int KTW>
+__device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, unsigned char* ring, uint64_t* full,
+                                                const CUtensorMap* kmap, const CUtensorMap* vmap, int* aborted,
+                                                const __nv_bfloat16* sQ, int tile_begin, int tile_end,
+                                                int key_end, int split, unsigned char* smem_raw) {
+  constexpr int TMA_STAGE_BYTES = tma_stage_bytes(KTW);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  int box_shift = p.page_shift, kt_shift = 0;
+  while ((1 << kt_shift) < KTW) ++kt_shift;
+  box_shift = min(box_shift, kt_shift);
+  const int boxes = KTW >> box_shift;
+  const bool issuer = lane < 2 * boxes;
+  const int my_box = lane >> 1;
+  const CUtensorMap* my_map = (lane & 1) ? vmap : kmap;
+  const uint32_t my_dst = ((lane & 1) ? KTW * HD * 2 : 0) + ((my_box * HD) << (box_shift + 1));
+  const int safe_page = (issuer && key_end > 0) ? max(w.bt[(key_end - 1) >> p.page_shift], 0) : 0;
+  // Row of this lane's box of tile t in the page matrix [pages * nkv * page][HD].
+  auto box_row = [&](int t) -> int {
+    if (!issuer || t >= tile_end) return 0;
+    const int j0 = t * KTW + (my_box << box_shift);
+    int page = safe_page, in_page = 0;
+    if (j0 < key_end) {
+      const int pg = w.bt[j0 >> p.page_shift];
+      if (pg >= 0) {
+        page = pg;
+        in_page = j0 & (p.page_size - 1);
+      }
+    }
+    return (page * p.nkv + w.kvh) * p.page_size + in_page;
+  };
+  auto issue = [&](int st, int row) {
+    if (lane == 0) atom::tma::mbar_expect_tx(&full[st], TMA_STAGE_BYTES);
+    __syncwarp();
+    if (issuer) atom::tma::load_chunks(ring + st * TMA_STAGE_BYTES + my_dst, my_map, row, 0, &full[st]);
+  };
+
+  // The warp's first RING tiles.
+  int row_next;
+  {
+    int rows[RING + 1];
+#pragma unroll
+    for (int i = 0; i <= RING; ++i) rows[i] = box_row(tile_begin + warp + 4 * i);
+#pragma unroll
+    for (int i = 0; i < RING; ++i)
+      if (tile_begin + warp + 4 * i < tile_end) issue(i, rows[i]);
+    row_next = rows[RING];
+  }
+
+  int pos[NQ][2];
+#pragma unroll
+  for (int n = 0; n < NQ; ++n)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int R = n * 8 + 2 * t4 + j;
+      pos[n][j] = R < w.rows_total ? w.q_start + R / p.group : -1;
+    }
+  uint32_t qf[Q_IN_REGS ? HD / 16 : 1][NQ][2];
+  if (Q_IN_REGS) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+#pragma unroll
+      for (int n = 0; n < NQ; ++n) {
+        const __nv_bfloat16* qrow = sQ + (n * 8 + g) * LDS + ks * 16 + 2 * t4;
+        qf[ks][n][0] = *reinterpret_cast<const uint32_t*>(qrow);
+        qf[ks][n][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
+      }
+  }
+
+  AccT<NQ> acc;
+  acc.init();
+  int st = 0;
+  uint32_t phase = 0;
+  for (int t = tile_begin + warp; t < tile_end; t += 4) {
+    const int refill = t + 4 * RING;
+    const int row_after = box_row(refill + 4);   // in flight during the tile's arithmetic
+    atom::tma::mbar_wait(&full[st], phase, aborted, p.error);
+    const unsigned char* sK = ring + st * TMA_STAGE_BYTES;
+    const int key0 = t * KTW;
+    bool mask = key0 + KTW - 1 > w.q_start;
+    if (p.window > 0) mask = mask || (key0 <= w.ctx - 1 - p.window);
+    warp_tile_t<NQ, KTW>(acc, qf, sQ, sK, sK + KTW * HD * 2, key0, pos, p.window, p.scale_log2, mask, box_shift);
+    if (refill < tile_end) {
+      __syncwarp();
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // this warp's reads before the refill's writes
+      issue(st, row_next);
+    }
+    row_next = row_after;
+    if (++st == RING) {
+      st = 0;
+      phase ^= 1;
+    }
+  }
+  __syncthreads();   // every warp has consumed all it asked for: the rings become the merge buffer
+
+  float* mo = reinterpret_cast<float*>(smem_raw);       // [4][16][MLD]
+  float* mm = mo + 4 * 16 * MLD;                         // [4][16]
+  float* ml = mm + 4 * 16;                               // [4][16]
+#pragma unroll
+  for (int n = 0; n < NQ; ++n)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float l = acc.l[n][j];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      const int row = n * 8 + 2 * t4 + j;
+      if (g == 0) {
+        mm[warp * 16 + row] = acc.m[n][j];
+        ml[warp * 16 + row] = l;
+      }
+#pragma unroll
+      for (int dm = 0; dm < HD / 16; ++dm) {
+        mo[(warp * 16 + row) * MLD + dm * 16 + g] = acc.o[dm][n][j];
+        mo[(warp * 16 + row) * MLD + dm * 16 + g + 8] = acc.o[dm][n][j + 2];
+      }
+    }
+  __syncthreads();
+  decode_combine(p, w, split, mo, mm, ml);
+}
+
+template <int KTW>
+__global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_kernel(const Params p,
+                                                                 const __grid_constant__ CUtensorMap kmap,
+                                                                 const __grid_constant__ CUtensorMap vmap) {
+  constexpr int TMA_STAGE_BYTES = tma_stage_bytes(KTW);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int aborted;
+  unsigned char* rings = smem_raw + ((1024 - (atom::tma::smem_u32(smem_raw) & 1023)) & 1023);
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(rings + 4 * RING * TMA_STAGE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sQ + 16 * LDS);
+  if (threadIdx.x == 0) {
+    aborted = 0;
+#pragma unroll
+    for (int i = 0; i < 4 * RING; ++i) atom::tma::mbar_init(&full[i], 1);
+    atom::tma::mbar_fence_init();
+    atom::tma::prefetch_map(&kmap);
+    atom::tma::prefetch_map(&vmap);
+  }
+  __syncthreads();
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+
+  Work w;
+  w.seq = blockIdx.x;
+  w.kvh = blockIdx.y;
+  const int split = blockIdx.z;
+  w.q_begin = p.cu_q[w.seq];
+  const int q_len = p.cu_q[w.seq + 1] - w.q_begin;
+  w.rows_total = q_len * p.group;
+  if (w.rows_total <= 0 || w.rows_total > 16) return;
+  w.ctx = p.ctx_len[w.seq];
+  w.q_start = w.ctx - q_len;
+  w.row0 = 0;
+  w.bt = p.block_table + (int64_t)w.seq * p.max_pages;
+
+  // The splits are cut in units of BN keys, as in the kernel above; tiles are counted in KTW keys.
+  const int key_end = w.ctx;
+  int key_lo = 0;
+  if (p.window > 0) key_lo = max(0, w.q_start - p.window + 1);
+  const int first_tile = key_lo / BN, n_tiles = (key_end + BN - 1) / BN - first_tile;
+  const int per_split = (n_tiles + p.num_splits - 1) / p.num_splits;
+  const int big_begin = first_tile + split * per_split;
+  const int big_end = max(big_begin, min(big_begin + per_split, first_tile + n_tiles));
+  const int tile_begin = big_begin * (BN / KTW);
+  const int tile_end = min(big_end * (BN / KTW), (key_end + KTW - 1) / KTW);
+
+  if (tile_begin < tile_end) {
+    load_q_tile<16>(p, w, sQ);
+    cp_async_commit();
+    cp_async_wait<0>();
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  unsigned char* ring = rings + warp * RING * TMA_STAGE_BYTES;
+  if (w.rows_total <= 8)
+    decode_tma_body<1, KTW>(p, w, ring, full + warp * RING, &kmap, &vmap, &aborted, sQ, tile_begin, tile_end, key_end,
+                       split, smem_raw);
+  else
+    decode_tma_body<2, KTW>(p, w, ring, full + warp * RING, &kmap, &vmap, &aborted, sQ, tile_begin, tile_end, key_end,
+                       split, smem_raw);
+}
+#endif
 
 // Merges the splits of every (token, head) of the short requests: one warp each.  Lanes
 // first take one split each to find the common maximum and the weights, then one output
@@ -727,7 +1140,49 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   }
   if (has_short) {
     dim3 grid(num_seqs, nkv, num_splits);
-    atom::launch_pdl(flash_decode_kernel, dim3(grid), dim3(NT), decode_smem_bytes(), stream, p);
+    bool tma_done = false;
+#if ATOM_HD % 64 == 0
+    // One TMA box per page needs pages of a power of two >= 8 tokens and the size of the page matrices.
+    static const bool tma_off = [] { const char* e = getenv("ATOM_DECODE_TMA"); return e != nullptr && e[0] == '0'; }();
+    const uint64_t page_rows = (uint64_t)num_pages * nkv * page_size;
+    if (!tma_off && p.page_shift >= 3 && num_pages > 0 && page_rows < 0x7fffffffull && p.error != nullptr) {
+      // 32-key warp tiles where every CTA has an SM to itself (and they fit), else 16-key tiles and two CTAs an SM.
+      static int sms = 0;
+      if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+          return ATOM_ERR_LAUNCH;
+      }
+      static const int forced = [] { const char* e = getenv("ATOM_DECODE_KTW"); return e ? atoi(e) : 0; }();
+      const bool wide = decode_tma_fits(32) && (forced == 32 || (forced != 16 && (int64_t)num_seqs * nkv * num_splits <= sms));
+      const int ktw = wide ? 32 : 16;
+      const uint32_t box_rows = page_size < ktw ? page_size : ktw;
+      CUtensorMap kmap, vmap;
+      if (atom::tma::cached_map(&kmap, k_pages, page_rows, HD, HD, box_rows, HD / 64) &&
+          atom::tma::cached_map(&vmap, v_pages, page_rows, HD, HD, box_rows, HD / 64)) {
+        static bool tma_attr = false;
+        if (!tma_attr) {
+          if (cudaFuncSetAttribute(flash_decode_tma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)decode_tma_smem_bytes(16)) != cudaSuccess)
+            return ATOM_ERR_LAUNCH;
+          if (decode_tma_fits(32) &&
+              cudaFuncSetAttribute(flash_decode_tma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)decode_tma_smem_bytes(32)) != cudaSuccess)
+            return ATOM_ERR_LAUNCH;
+          tma_attr = true;
+        }
+        if (wide)
+          atom::launch_pdl(flash_decode_tma_kernel<32>, dim3(grid), dim3(NT), decode_tma_smem_bytes(32), stream, p, kmap,
+                           vmap);
+        else
+          atom::launch_pdl(flash_decode_tma_kernel<16>, dim3(grid), dim3(NT), decode_tma_smem_bytes(16), stream, p, kmap,
+                           vmap);
+        tma_done = true;
+      }
+    }
+#endif
+    if (!tma_done) atom::launch_pdl(flash_decode_kernel, dim3(grid), dim3(NT), decode_smem_bytes(), stream, p);
     if (num_splits > 1) {
       const int warps = T * nh;
       atom::launch_pdl(flash_merge_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, p, seq_of_token, T);

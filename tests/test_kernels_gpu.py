@@ -313,6 +313,53 @@ def test_tcgen05_one_far_key_decides(native, far):
     assert (got - want).abs().max().item() <= 3e-2
 
 
+TMA_DECODE_CASES = [
+    # nh, nkv, hd, page, window, q_lens, ctx_lens, splits  (head size a multiple of 64, pages of 8, 16, ... tokens:
+    # short requests take their pages as TMA boxes)
+    (32, 8, 128, 16, 0, [1] * 6, [2100, 1, 63, 64, 65, 1000], 1),
+    (32, 8, 128, 16, 0, [1] * 6, [2100, 1, 63, 64, 65, 1000], 5),
+    (8, 4, 64, 8, 100, [1, 2, 4, 8, 3], [300, 130, 77, 8, 259], 3),      # 2 to 16 packed rows, a window
+    (4, 2, 256, 32, 0, [1, 3, 8], [500, 35, 260], 2),                    # pieces of 16 keys of 32-token pages
+    (6, 2, 192, 64, 0, [1, 5, 2], [333, 70, 129], 1),                    # three 64-column halves
+    (8, 2, 128, 128, 0, [1, 4, 1], [700, 300, 129], 4),                  # pages larger than a tile
+    (8, 4, 128, 16, 0, [1] * 40, [40 + 13 * i for i in range(40)], 1),   # more CTAs than SMs: two CTAs an SM
+    (8, 4, 128, 16, 0, [1] * 40, [40 + 13 * i for i in range(40)], 3),
+]
+
+
+@pytest.mark.parametrize("case", TMA_DECODE_CASES, ids=lambda c: f"nh{c[0]}kv{c[1]}hd{c[2]}pg{c[3]}w{c[4]}s{c[7]}n{len(c[5])}")
+def test_flash_decode_tma(native, case):
+    nh, nkv, hd, page, window, q_lens, ctx_lens, splits = case
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=hd + page + splits)
+    scale = hd ** -0.5
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, scale, window)
+    got = _run_attention(native, "flash", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, scale, window,
+                         force_splits=splits)
+    native.check_error_flags()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs().max().item()
+    assert err <= 2e-2, f"max abs error {err:.3e}"
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 31, 32, 63, 64, 1023, 1024, 1999])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_flash_decode_tma_one_far_key_decides(native, far, splits):
+    """One key among two thousand decides the output: at a box's, a tile's, a ring's and a split's edge."""
+    nh, nkv, hd, page = 8, 2, 128, 16
+    q_lens, ctx_lens = [1, 1], [2000, 700]
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=far)
+    qv = q[0, 5].float()
+    key = (qv / qv.norm() * 6.0).to(torch.bfloat16)
+    k0, v0 = dense[0]
+    k0[far, 1] = key                            # query head 5 reads kv head 1
+    kp[int(bt[0, far // page]), 1, far % page] = key
+    got = _run_attention(native, "flash", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, 1.0, 0, force_splits=splits)
+    native.check_error_flags()
+    torch.testing.assert_close(got[0, 5], v0[far, 1].float(), rtol=2e-2, atol=2e-2)
+    want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, 1.0, 0)
+    assert (got - want).abs().max().item() <= 3e-2
+
+
 @pytest.mark.parametrize("splits", [2, 3, 7])
 def test_flash_decode_splits_agree(native, splits):
     nh, nkv, hd, page = 8, 2, 64, 16
