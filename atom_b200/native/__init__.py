@@ -68,7 +68,8 @@ _SIGNATURES = {
     "atom_gemm_f32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _vp],
     "atom_gemm_bf16": [_vp, _i, _vp, _vp, _i, _i, _i, _i64, _vp, _sz, _vp],
     "atom_add_bias": [_vp, _i, _vp, _i, _i, _i, _vp],
-    "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i64, _vp],
+    "atom_gemm_smallm_scratch_bytes": [_i],
     "atom_gemm_smallm_supports": [_i, _i, _i, _i64],
 }
 
@@ -79,7 +80,7 @@ def _declare(l) -> None:
             continue  # optional kernels are declared by the module that owns them
         fn = getattr(l, name)
         fn.argtypes = args
-        fn.restype = ctypes.c_int
+        fn.restype = ctypes.c_int64 if name.endswith("_bytes") else ctypes.c_int
 
 
 def declare(name: str, args) -> None:
@@ -290,6 +291,21 @@ def gemm_smallm_supports(M: int, N: int, K: int, lda: int) -> bool:
     return bool(lib().atom_gemm_smallm_supports(M, N, K, lda))
 
 
+_smallm_scratch = {}
+
+
+def _smallm_scratch_for(device: torch.device, n_rows: int) -> torch.Tensor:
+    """Zeroed device memory for the partial sums of W slabs that several CTAs share: one buffer
+    per device, grown (outside graph capture only) when a taller matrix comes."""
+    need = int(lib().atom_gemm_smallm_scratch_bytes(n_rows))
+    buf = _smallm_scratch.get(device)
+    if buf is None or buf.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("gemm_smallm: first call for this size inside a graph capture; run the step once before")
+        buf = _smallm_scratch[device] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+    return buf
+
+
 def gemm_smallm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 gated: bool = False) -> None:
     """out[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T (+ bias) for M <= 16: the weight-streaming
@@ -300,10 +316,11 @@ def gemm_smallm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optio
     assert a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous()
     assert w.shape[0] == (2 * N if gated else N) and out.shape[0] == M
     assert a.stride(1) == 1 and out.stride(1) == 1
+    scratch = _smallm_scratch_for(out.device, w.shape[0])
     _check(lib().atom_gemm_smallm(
         out.data_ptr(), dtype_code(out.dtype), out.stride(0), a.data_ptr(), a.stride(0), w.data_ptr(),
         _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, M, N, K, int(gated),
-        error_flag(out.device).data_ptr(), _stream()), "gemm_smallm")
+        error_flag(out.device).data_ptr(), scratch.data_ptr(), scratch.numel(), _stream()), "gemm_smallm")
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

@@ -15,9 +15,19 @@
 // W = [gate rows ; up rows]: the feed-forward's activation never travels through memory.
 // Meanwhile the producer is already streaming the next slab.
 //
+// Work is the sequence of all (slab, 256-k stage) pairs, slab-major, cut into one contiguous
+// range per CTA of equal length (+-1 stage), so every CTA streams the same number of bytes
+// whatever the number of slabs.  A range may begin and end inside a slab.  Such a slab has
+// several contributors: each writes its partial sums to its own slot of a scratch buffer and
+// counts itself in; the one that arrives last adds the slots in the order of the ranges (so
+// the sum does not depend on who was last), applies the epilogue and clears the counter.
+// Nobody waits for anybody.  Without scratch the ranges are rounded to whole slabs.
+//
 // Takes K that is a multiple of 64 and leading dimensions that are multiples of 8 elements;
 // the caller uses the library product for other sizes.  Every mbarrier wait is bounded: when one runs
 // out the kernel raises the device error flag and finishes without hanging.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -29,6 +39,7 @@ using namespace atom::tma;
 constexpr int NCONS = 4;                 // consumer warps, one 64-element box of a stage each
 constexpr int NTHREADS = (NCONS + 1) * 32;
 constexpr int BK = NCONS * BOX_COLS;     // k elements per stage
+constexpr int MAX_GRID = 256;            // most CTAs of a launch whose ranges may share slabs
 
 struct Params {
   void* out;
@@ -39,7 +50,18 @@ struct Params {
   int M, N, K;
   int gated;
   int* error;
+  int num_slabs;
+  long long total;      // stages of all slabs
+  float* slots;         // [CTAs][2][8 MT][ROWS] partial sums of ranges that begin or end inside a slab
+  int* counters;        // [num_slabs] contributors that have arrived; zero between launches
+  int whole_slabs;      // 1: ranges are rounded to whole slabs (no scratch)
 };
+
+// First stage of CTA c's range.
+__device__ __forceinline__ long long range_begin(const Params& p, int c, int num_kt) {
+  if (p.whole_slabs) return ((long long)p.num_slabs * c / gridDim.x) * num_kt;
+  return p.total * c / gridDim.x;
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -56,6 +78,57 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+
+// The order in which a CTA walks the stages [b, e) of its range: first the piece of the slab
+// that its range ends in, then the piece of the slab that it begins in, then the whole slabs
+// between them.  The shared slabs are thus settled early, while the stream of the whole slabs
+// is already on its way, and the kernel's end is a plain slab's.
+struct Walk {
+  long long pb[3], pe[3];
+  int n, pi, num_kt;
+  long long g;
+  int slab, kt;
+  __device__ __forceinline__ void seek() {
+    if (pi < n) {
+      g = pb[pi];
+      slab = (int)(g / num_kt);
+      kt = (int)(g - (long long)slab * num_kt);
+    }
+  }
+  __device__ __forceinline__ Walk(long long b, long long e, int nkt) : n(0), pi(0), num_kt(nkt), g(0), slab(0), kt(0) {
+    const long long head_end = (b / nkt + 1) * nkt;        // end of the slab that b lies in
+    const long long tail_begin = (e / nkt) * nkt;          // begin of the slab that e lies in
+    const bool head_cut = b % nkt != 0, tail_cut = e % nkt != 0;
+    if (b >= e) {
+    } else if (head_end >= e || (!head_cut && tail_begin <= b)) {
+      // at most one slab is touched, or the range is one run: whole slabs, then a cut tail
+      if (tail_cut && tail_begin > b) {
+        pb[n] = tail_begin, pe[n] = e, ++n;
+        pb[n] = b, pe[n] = tail_begin, ++n;
+      } else {
+        pb[n] = b, pe[n] = e, ++n;
+      }
+    } else {
+      long long wb = b, we = e;
+      if (tail_cut) pb[n] = tail_begin, pe[n] = e, ++n, we = tail_begin;
+      if (head_cut) pb[n] = b, pe[n] = head_end, ++n, wb = head_end;
+      if (wb < we) pb[n] = wb, pe[n] = we, ++n;
+    }
+    seek();
+  }
+  __device__ __forceinline__ bool valid() const { return pi < n; }
+  __device__ __forceinline__ void advance() {
+    ++g;
+    if (++kt == num_kt) {
+      kt = 0;
+      ++slab;
+    }
+    if (g == pe[pi]) {
+      ++pi;
+      seek();
+    }
+  }
+};
 
 // MT: 8-token column tiles (tokens padded to 8 * MT).  RT: 16-row tiles of W per slab.  NS: stages.
 template <int MT, int RT, int NS>
@@ -74,7 +147,7 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\
 template <int MT, int RT, int NS>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   const Params p, int num_slabs) {
+                   const Params p) {
   atom::pdl_trigger();   // the next kernel may be scheduled; this one waits below, after its first loads of W
   using C = Cfg<MT, RT, NS>;
   constexpr int ROWS = C::ROWS, MP = C::MP, RLD = C::RLD;
@@ -100,6 +173,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   // Rows of W in a slab.  Gated: the first half are gate rows, the second the matching up rows.
   const int out_per_slab = p.gated ? ROWS / 2 : ROWS;
   const int num_kt = (p.K + BK - 1) / BK;
+  const long long g_begin = range_begin(p, blockIdx.x, num_kt), g_end = range_begin(p, blockIdx.x + 1, num_kt);
 
   if (warp == NCONS) {
     // ---------------------------------------------------------------- producer
@@ -112,32 +186,27 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     // One operation per operand and stage: W rows (gate rows when gated), X, and the up rows
     // when gated.  A gated stage is [gate: 4 blocks of ROWS/2 rows][up: the same][X].
     {
-      int it = 0;
-      for (int slab = blockIdx.x; slab < num_slabs && it < NS; slab += gridDim.x) {
-        const int n0 = slab * out_per_slab;
-        for (int kt = 0; kt < num_kt && it < NS; ++kt, ++it) {
-          unsigned char* stage = ring + (size_t)it * C::STAGE;
-          if (lane == 0) {
-            mbar_expect_tx(&full[it], (uint32_t)C::STAGE);
-            load_chunks(stage, &wmap, n0, kt * NCONS, &full[it]);
-          } else if (lane == 2 && p.gated) {
-            load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, kt * NCONS, &full[it]);
-          }
+      Walk w(g_begin, g_end, num_kt);
+      for (int it = 0; it < NS && w.valid(); ++it, w.advance()) {
+        const int n0 = w.slab * out_per_slab;
+        unsigned char* stage = ring + (size_t)it * C::STAGE;
+        if (lane == 0) {
+          mbar_expect_tx(&full[it], (uint32_t)C::STAGE);
+          load_chunks(stage, &wmap, n0, w.kt * NCONS, &full[it]);
+        } else if (lane == 2 && p.gated) {
+          load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, w.kt * NCONS, &full[it]);
         }
       }
     }
     atom::pdl_wait();
-    int it = 0;   // stages issued so far, over all slabs
-    for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
-      const int n0 = slab * out_per_slab;
-      for (int kt = 0; kt < num_kt; ++kt, ++it) {
-        const int s = it % NS, u = it / NS;
-        unsigned char* stage = ring + (size_t)s * C::STAGE;
-        const int kc = kt * NCONS;
-        if (it < NS) {   // W of the first ring is on its way already
-          if (lane == 1) load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
-          continue;
-        }
+    int s = 0, u = 0, it = 0;   // stage s of the ring, in its u-th use
+    for (Walk w(g_begin, g_end, num_kt); w.valid(); w.advance(), ++it) {
+      const int n0 = w.slab * out_per_slab;
+      unsigned char* stage = ring + (size_t)s * C::STAGE;
+      const int kc = w.kt * NCONS;
+      if (it < NS) {   // W of the first ring is on its way already
+        if (lane == 1) load_chunks(stage + NCONS * C::W_BOX, &xmap, 0, kc, &full[s]);
+      } else {
         mbar_wait(&empty[s], (u & 1) ^ 1, &aborted, p.error);
         if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)C::STAGE);
         __syncwarp();
@@ -149,6 +218,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
           load_chunks(stage + NCONS * C::W_BOX / 2, &wmap, p.N + n0, kc, &full[s]);
         }
       }
+      if (++s == NS) {
+        s = 0;
+        ++u;
+      }
     }
     return;
   }
@@ -158,8 +231,13 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   // are written after the kernels before this one have completed)
   const int mat = lane >> 3, r8 = lane & 7;
   const int tid = threadIdx.x;   // 0 .. NCONS * 32 - 1
-  int it = 0;
-  for (int slab = blockIdx.x; slab < num_slabs; slab += gridDim.x) {
+  __shared__ int is_last;
+  __shared__ int part_slot[MAX_GRID];   // for the contributors of a shared slab: index of the slot each wrote
+  const int head_slab = (int)(g_begin / num_kt);
+  int s = 0, u = 0;   // stage s of the ring, in its u-th use
+  Walk walk(g_begin, g_end, num_kt);
+  while (walk.valid()) {
+    const int slab = walk.slab, kt_first = walk.kt;
     const int n0 = slab * out_per_slab;
     float acc[RT][MT][4];
 #pragma unroll
@@ -167,8 +245,9 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
       for (int j = 0; j < MT; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
 
-    for (int kt = 0; kt < num_kt; ++kt, ++it) {
-      const int s = it % NS, u = it / NS;
+    int kt_last = kt_first;   // exclusive
+    for (; walk.valid() && walk.slab == slab && walk.kt == kt_last; walk.advance()) {
+      const int kt = kt_last++;
       mbar_wait(&full[s], u & 1, &aborted, p.error);
       const unsigned char* stage = ring + (size_t)s * C::STAGE;
       // this warp's block of W rows; gated: its block of gate rows, the up rows half a W region on
@@ -210,15 +289,19 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
+      if (++s == NS) {
+        s = 0;
+        ++u;
+      }
     }
-    // Add the four warps' partial sums in a fixed order and write the slab's outputs.
+    // The four warps' partial sums go to shared memory; they are added in a fixed order below.
     {
-      const int g = lane >> 2, t4 = lane & 3;
+      const int g4 = lane >> 2, t4 = lane & 3;
 #pragma unroll
       for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          float* base = red + ((size_t)warp * MP + j * 8 + 2 * t4) * RLD + i * 16 + g;
+          float* base = red + ((size_t)warp * MP + j * 8 + 2 * t4) * RLD + i * 16 + g4;
           base[0] = acc[i][j][0];
           base[RLD] = acc[i][j][1];
           base[8] = acc[i][j][2];
@@ -226,25 +309,87 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         }
     }
     consumer_sync();
-    for (int idx = tid; idx < out_per_slab * p.M; idx += NCONS * 32) {
-      const int m = idx / out_per_slab, r = idx - m * out_per_slab;
-      const int col = n0 + r;
-      if (col >= p.N) continue;
-      float v = 0.f;
+
+    // Does this range hold the whole slab?  If not: which CTAs share it, and which of them is this one.
+    const bool whole = kt_first == 0 && kt_last == num_kt;
+    int c_first = blockIdx.x, nparts = 1;
+    bool finish = true;
+    if (!whole) {
+      const long long s_begin = (long long)slab * num_kt, s_end = s_begin + num_kt, G = gridDim.x;
+      c_first = (int)(((s_begin + 1) * G + p.total - 1) / p.total) - 1;   // the last CTA whose range begins at or before the slab's first stage
+      const int c_last = (int)((s_end * G + p.total - 1) / p.total) - 1;  // ... at or before its last stage
+      nparts = c_last - c_first + 1;
+      // this CTA's slot: 0 if the slab is the first of its range, else 1
+      float* slot = p.slots + ((size_t)blockIdx.x * 2 + (slab == head_slab ? 0 : 1)) * (MP * ROWS);
+      for (int idx = tid; idx < MP * ROWS; idx += NCONS * 32) {
+        const int m = idx / ROWS, r = idx - m * ROWS;
+        float v = 0.f;
 #pragma unroll
-      for (int wv = 0; wv < NCONS; ++wv) v += red[((size_t)wv * MP + m) * RLD + r];
-      if (p.gated) {
-        float uval = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < NCONS; ++wv) uval += red[((size_t)wv * MP + m) * RLD + ROWS / 2 + r];
-        v = v / (1.f + __expf(-v)) * uval;
-      } else if (p.bias != nullptr) {
-        v += load_as_float(p.bias, p.bias_dtype, col);
+        for (int wv = 0; wv < NCONS; ++wv) v += red[((size_t)wv * MP + m) * RLD + r];
+        slot[idx] = v;
       }
-      if (p.out_dtype == ATOM_F32)
-        reinterpret_cast<float*>(p.out)[(int64_t)m * p.ldc + col] = v;
-      else
-        reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.ldc + col] = __float2bfloat16_rn(v);
+      __threadfence();
+      consumer_sync();
+      if (tid == 0) {
+        const int old = atomicAdd(p.counters + slab, 1);
+        is_last = old == nparts - 1;
+        if (is_last) p.counters[slab] = 0;
+      }
+      consumer_sync();
+      finish = is_last != 0;
+      if (finish) {
+        __threadfence();
+        for (int j = tid; j < nparts; j += NCONS * 32) {
+          const int c = c_first + j;
+          const bool head = (range_begin(p, c, num_kt) / num_kt) == slab;   // the slab is the first of c's range
+          part_slot[j] = c * 2 + (head ? 0 : 1);
+        }
+        consumer_sync();
+      }
+    }
+    if (finish) {
+      for (int idx = tid; idx < out_per_slab * p.M; idx += NCONS * 32) {
+        const int m = idx / out_per_slab, r = idx - m * out_per_slab;
+        const int col = n0 + r;
+        if (col >= p.N) continue;
+        float v = 0.f, uval = 0.f;
+        if (whole) {
+#pragma unroll
+          for (int wv = 0; wv < NCONS; ++wv) v += red[((size_t)wv * MP + m) * RLD + r];
+          if (p.gated) {
+#pragma unroll
+            for (int wv = 0; wv < NCONS; ++wv) uval += red[((size_t)wv * MP + m) * RLD + ROWS / 2 + r];
+          }
+        } else {
+          // four contributors' loads in flight at a time; added in the order of the ranges
+          for (int j0 = 0; j0 < nparts; j0 += 4) {
+            float t[4], tu[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              t[q] = tu[q] = 0.f;
+              if (j0 + q < nparts) {
+                const float* slot = p.slots + (size_t)part_slot[j0 + q] * (MP * ROWS);
+                t[q] = __ldcg(slot + m * ROWS + r);
+                if (p.gated) tu[q] = __ldcg(slot + m * ROWS + ROWS / 2 + r);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              v += t[q];
+              uval += tu[q];
+            }
+          }
+        }
+        if (p.gated) {
+          v = v / (1.f + __expf(-v)) * uval;
+        } else if (p.bias != nullptr) {
+          v += load_as_float(p.bias, p.bias_dtype, col);
+        }
+        if (p.out_dtype == ATOM_F32)
+          reinterpret_cast<float*>(p.out)[(int64_t)m * p.ldc + col] = v;
+        else
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.ldc + col] = __float2bfloat16_rn(v);
+      }
     }
     consumer_sync();   // the reduction buffer is free for the next slab
   }
@@ -273,7 +418,8 @@ struct Shape {
 };
 
 template <int MT, int RT>
-static int launch(const Params& p, const void* X, int64_t lda, const void* W, cudaStream_t stream) {
+static int launch(Params p, const void* X, int64_t lda, const void* W, void* scratch, int64_t scratch_bytes,
+                  cudaStream_t stream) {
   using S = Shape<MT, RT>;
   using C = Cfg<MT, RT, S::NS>;
   static_assert(C::SMEM <= 227 * 1024, "shared memory of a CTA");
@@ -290,15 +436,31 @@ static int launch(const Params& p, const void* X, int64_t lda, const void* W, cu
       !cached_map(&xmap, X, p.M, p.K, lda, C::MP, NCONS))
     return ATOM_ERR_LIB;
   const int out_per_slab = p.gated ? C::ROWS / 2 : C::ROWS;
-  const int num_slabs = (p.N + out_per_slab - 1) / out_per_slab;
-  const int grid = num_slabs < sm_count() ? num_slabs : sm_count();
-  atom::launch_pdl(kern, dim3(grid), dim3(NTHREADS), C::SMEM, stream, wmap, xmap, p, num_slabs);
+  const int num_kt = (p.K + BK - 1) / BK;
+  p.num_slabs = (p.N + out_per_slab - 1) / out_per_slab;
+  p.total = (long long)p.num_slabs * num_kt;
+  // Scratch: [grid][2] slots of MP x ROWS floats, then one counter per slab.
+  int grid = sm_count() < MAX_GRID ? sm_count() : MAX_GRID;
+  // (the counters lie behind the largest slot area any shape needs, so no shape's slots ever cover them)
+  const int64_t slot_bytes = (int64_t)MAX_GRID * 2 * 16 * 64 * (int64_t)sizeof(float);
+  const int64_t need = slot_bytes + (int64_t)p.num_slabs * (int64_t)sizeof(int);
+  p.whole_slabs = (scratch == nullptr || scratch_bytes < need || ((uintptr_t)scratch % 16) != 0) ? 1 : 0;
+  if (p.whole_slabs) {
+    if (grid > p.num_slabs) grid = p.num_slabs;
+    p.slots = nullptr;
+    p.counters = nullptr;
+  } else {
+    if ((long long)grid > p.total) grid = (int)p.total;
+    p.slots = reinterpret_cast<float*>(scratch);
+    p.counters = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(scratch) + slot_bytes);
+  }
+  atom::launch_pdl(kern, dim3(grid), dim3(NTHREADS), C::SMEM, stream, wmap, xmap, p);
   return check_launch();
 }
 
-// Estimated time (arbitrary unit) of streaming N rows in slabs of `rows` over G persistent
-// CTAs: whole rounds run at full bandwidth; a last partial round of r CTAs is limited by the
-// bytes those CTAs keep in flight (about 10 MB saturate the memory system).
+// Rows of W per slab.  With ranges cut anywhere the balance does not depend on it: the tallest
+// slab that leaves every CTA a few stages reads X least often (X travels once per slab and stage).
+// With whole slabs: the height whose slab count fills the CTAs' rounds best.
 static double slab_cost(int n_out, int out_per_slab, int rows, double in_flight_bytes, int G) {
   const int slabs = (n_out + out_per_slab - 1) / out_per_slab;
   const int full = slabs / G, rem = slabs % G;
@@ -315,27 +477,44 @@ static double slab_cost(int n_out, int out_per_slab, int rows, double in_flight_
 }
 
 template <int MT>
-static int launch_mt(const Params& p, const void* X, int64_t lda, const void* W, cudaStream_t stream) {
+static int launch_mt(const Params& p, const void* X, int64_t lda, const void* W, void* scratch, int64_t scratch_bytes,
+                     cudaStream_t stream) {
   const int G = sm_count();
-  double best = 1e300;
   int rt = 2;
-  const int n_out = p.N;
+  static const int forced = [] { const char* e = getenv("ATOM_GEMM_RT"); return e ? atoi(e) : 0; }();
+  // Ranges cut inside slabs pay where a CTA streams much (the settling of a shared slab costs a few
+  // microseconds of its consumers' time): measured better from about half a megabyte of W per CTA.
+  static const int mode = [] { const char* e = getenv("ATOM_GEMM_STREAMK"); return e ? atoi(e) : -1; }();
+  const double w_bytes_per_cta = 2.0 * (p.gated ? 2.0 : 1.0) * p.N * (double)p.K / G;
+  const bool cut = mode < 0 ? w_bytes_per_cta >= 512.0 * 1024 : mode != 0;
+  if (!cut) scratch = nullptr;
+  if (scratch != nullptr) {
+    // stages per CTA with slabs of 64 rows: at least 4, else lower slabs
+    const long long num_kt = (p.K + BK - 1) / BK;
+    rt = 4;
+    while (rt > (p.gated ? 2 : 1) && ((long long)((p.N + (p.gated ? rt * 8 : rt * 16) - 1) / (p.gated ? rt * 8 : rt * 16)) * num_kt) < 4LL * G)
+      rt = p.gated ? rt - 2 : rt - 1;
+  } else {
+    double best = 1e300;
+    const int n_out = p.N;
 #define ATOM_TRY(RT)                                                                              \
   {                                                                                               \
     const int rows = RT * 16, out = p.gated ? rows / 2 : rows;                                    \
     const double c = slab_cost(n_out, out, rows, (double)Shape<MT, RT>::W_IN_FLIGHT, G);          \
     if (c < best) { best = c; rt = RT; }                                                          \
   }
-  if (!p.gated) ATOM_TRY(1)
-  ATOM_TRY(2)
-  if (!p.gated) ATOM_TRY(3)
-  ATOM_TRY(4)
+    if (!p.gated) ATOM_TRY(1)
+    ATOM_TRY(2)
+    if (!p.gated) ATOM_TRY(3)
+    ATOM_TRY(4)
 #undef ATOM_TRY
+  }
+  if (forced >= 1 && forced <= 4 && !(p.gated && (forced & 1))) rt = forced;
   switch (rt) {
-    case 1: return launch<MT, 1>(p, X, lda, W, stream);
-    case 2: return launch<MT, 2>(p, X, lda, W, stream);
-    case 3: return launch<MT, 3>(p, X, lda, W, stream);
-    default: return launch<MT, 4>(p, X, lda, W, stream);
+    case 1: return launch<MT, 1>(p, X, lda, W, scratch, scratch_bytes, stream);
+    case 2: return launch<MT, 2>(p, X, lda, W, scratch, scratch_bytes, stream);
+    case 3: return launch<MT, 3>(p, X, lda, W, scratch, scratch_bytes, stream);
+    default: return launch<MT, 4>(p, X, lda, W, scratch, scratch_bytes, stream);
   }
 }
 
@@ -350,10 +529,17 @@ ATOM_EXPORT int atom_gemm_smallm_supports(int M, int N, int K, int64_t lda) {
 
 // C[M, N] = X[M, K] * W[N, K]^T (+ bias), or with gated != 0: W is [2N, K] = [gate ; up] and
 // C[M, N] = silu(X gate^T) * (X up^T).  X, W bf16; C bf16 or float32.  `error` is a device int
-// that is set to 2 if a wait inside the kernel ran out.
+// that is set to 2 if a wait inside the kernel ran out.  `scratch` (16-byte aligned, zero before
+// its first use and left zero where it matters; may be null): room for the partial sums of slabs
+// that several CTAs share, atom_gemm_smallm_scratch_bytes(N) bytes; one launch at a time may use it.
+ATOM_EXPORT int64_t atom_gemm_smallm_scratch_bytes(int N) {
+  using namespace atom::smallm;
+  return (int64_t)MAX_GRID * 2 * 16 * 64 * (int64_t)sizeof(float) + ((int64_t)(N + 7) / 8) * (int64_t)sizeof(int);
+}
+
 ATOM_EXPORT int atom_gemm_smallm(void* C, int c_dtype, int64_t ldc, const void* X, int64_t lda, const void* W,
                                  const void* bias, int bias_dtype, int M, int N, int K, int gated, int* error,
-                                 cudaStream_t stream) {
+                                 void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
   using namespace atom::smallm;
   if (M <= 0 || N <= 0) return ATOM_OK;
   if (!atom_gemm_smallm_supports(M, N, K, lda) || ldc < N || (gated && bias != nullptr) || error == nullptr ||
@@ -370,6 +556,11 @@ ATOM_EXPORT int atom_gemm_smallm(void* C, int c_dtype, int64_t ldc, const void* 
   p.K = K;
   p.gated = gated ? 1 : 0;
   p.error = error;
-  if (M <= 8) return launch_mt<1>(p, X, lda, W, stream);
-  return launch_mt<2>(p, X, lda, W, stream);
+  p.num_slabs = 0;
+  p.total = 0;
+  p.slots = nullptr;
+  p.counters = nullptr;
+  p.whole_slabs = 1;
+  if (M <= 8) return launch_mt<1>(p, X, lda, W, scratch, scratch_bytes, stream);
+  return launch_mt<2>(p, X, lda, W, scratch, scratch_bytes, stream);
 }

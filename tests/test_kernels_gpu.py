@@ -506,6 +506,33 @@ def test_gemm_smallm_rows_do_not_depend_on_the_batch(native):
     torch.testing.assert_close(outs[8], outs[16][:8], rtol=1e-5, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,N,K,gated", [(8, 4096, 12288, False), (3, 6144, 4096, False), (8, 2048, 1024, True),
+                                         (5, 48, 8192, False), (8, 1000, 320, False)])
+def test_gemm_smallm_shared_slabs_repeat_bit_equal(native, M, N, K, gated):
+    """CTAs' ranges of work are cut inside slabs of W rows; the partial sums of a shared slab are added
+    in the order of the ranges by whoever arrives last.  The result is the same bits every time, also
+    with other products in between (the arrival counters are left clean), and it is right."""
+    a = _rand((M, K), torch.bfloat16, 40)
+    w = _rand((2 * N if gated else N, K), torch.bfloat16, 41)
+    other_a, other_w = _rand((2, 704), torch.bfloat16, 42), _rand((333, 704), torch.bfloat16, 43)
+    other = torch.empty((2, 333), dtype=torch.float32, device=DEV)
+    outs = []
+    for i in range(6):
+        out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+        native.gemm_smallm(out, a, w, None, gated=gated)
+        native.gemm_smallm(other, other_a, other_w)
+        outs.append(out)
+    native.check_error_flags()
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    if gated:
+        g, u = a.float() @ w[:N].float().T, a.float() @ w[N:].float().T
+        want = torch.nn.functional.silu(g) * u
+    else:
+        want = a.float() @ w.float().T
+    torch.testing.assert_close(outs[0], want, rtol=2e-3, atol=2e-3 * math.sqrt(K / 96))
+    torch.testing.assert_close(other, other_a.float() @ other_w.float().T, rtol=2e-3, atol=5e-3)
+
+
 def test_gemm_smallm_refuses_other_sizes(native):
     assert not native.gemm_smallm_supports(17, 64, 64, 64)
     assert not native.gemm_smallm_supports(4, 64, 96, 96)      # K no multiple of 64
