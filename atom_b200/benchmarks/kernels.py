@@ -2,6 +2,7 @@
 
     python -m atom_b200.benchmarks.kernels gemm      [--rows 1,8] [--shape qkv|o|gate_up|down|lm_head]
     python -m atom_b200.benchmarks.kernels attention [--mode decode|prefill] [--batch 1,8,64] [--context 4096]
+    python -m atom_b200.benchmarks.kernels elementwise [--tokens 8,2048]
 
 Sizes default to Qwen3-8B's (hidden 4096, 32 heads, 8 kv heads, head size 128, feed-forward
 12288, vocabulary 151936).  Every timing replays a CUDA graph of several launches over
@@ -105,11 +106,44 @@ def bench_attention(args) -> None:
             print(f"prefill batch={B:3d} tokens={ctx} ({kind}): {t:8.1f} us  {fl / t / 1e6:7.1f} TFLOP/s", flush=True)
 
 
+def bench_elementwise(args) -> None:
+    """Residual add + RMSNorm, per-head norm + rotation + cache write, SiLU * mul: bytes moved / time."""
+    H, I, nh, nkv, hd, page = args.hidden, args.intermediate, args.heads, args.kv_heads, args.head_dim, args.page
+    bf = torch.bfloat16
+    for T in args.tokens:
+        copies = 4
+        P = -(-T // page)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        w, qw, kw = torch.ones(H, device=DEV, dtype=bf), torch.ones(hd, device=DEV, dtype=bf), torch.ones(hd, device=DEV, dtype=bf)
+        cos_sin = torch.randn(T + 1, hd, device=DEV)
+        pos = torch.arange(T, dtype=torch.int32, device=DEV)
+        sot = torch.zeros(T, dtype=torch.int32, device=DEV)
+        bt = torch.randperm(P, device=DEV).to(torch.int32).view(1, P).contiguous()
+        sets = []
+        for _ in range(copies):
+            sets.append(dict(res=torch.randn(T, H, device=DEV), delta=torch.randn(T, H, device=DEV).to(bf),
+                             out=torch.empty(T, H, device=DEV, dtype=bf),
+                             qkv=torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(bf),
+                             kp=torch.zeros(P, nkv, page, hd, device=DEV, dtype=bf),
+                             vp=torch.zeros(P, nkv, page, hd, device=DEV, dtype=bf),
+                             gu=torch.randn(T, 2 * I, device=DEV).to(bf), act=torch.empty(T, I, device=DEV, dtype=bf)))
+        t = _time_graph([(lambda d=d: native.add_rmsnorm(d["out"], d["res"], d["delta"], w, 1e-6)) for d in sets])
+        by = T * H * (2 + 4 + 4 + 2)
+        print(f"add_rmsnorm         tokens={T:5d}: {t:7.1f} us  {by / t / 1e3:6.0f} GB/s", flush=True)
+        t = _time_graph([(lambda d=d: native.qknorm_rope_kvwrite(d["qkv"], nh, nkv, hd, qw, kw, 1e-6, cos_sin, hd, pos, sot,
+                                                                 bt, page, d["kp"], d["vp"], status)) for d in sets])
+        by = T * hd * 2 * ((nh + 2 * nkv) + nh + 2 * nkv)
+        print(f"qknorm_rope_kvwrite tokens={T:5d}: {t:7.1f} us  {by / t / 1e3:6.0f} GB/s", flush=True)
+        t = _time_graph([(lambda d=d: native.silu_mul(d["act"], d["gu"])) for d in sets])
+        by = T * I * 2 * 3
+        print(f"silu_mul            tokens={T:5d}: {t:7.1f} us  {by / t / 1e3:6.0f} GB/s", flush=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
     ints = lambda s: [int(x) for x in s.split(",")]
-    for name in ("gemm", "attention"):
+    for name in ("gemm", "attention", "elementwise"):
         p = sub.add_parser(name)
         p.add_argument("--hidden", type=int, default=4096)
         p.add_argument("--heads", type=int, default=32)
@@ -120,6 +154,9 @@ def main(argv=None) -> int:
         if name == "gemm":
             p.add_argument("--rows", type=ints, default=[1, 8])
             p.add_argument("--shape", default=None)
+        elif name == "elementwise":
+            p.add_argument("--tokens", type=ints, default=[8, 2048])
+            p.add_argument("--page", type=int, default=16)
         else:
             p.add_argument("--mode", choices=["decode", "prefill"], default="decode")
             p.add_argument("--batch", type=ints, default=[1, 8, 64])
@@ -128,7 +165,7 @@ def main(argv=None) -> int:
             p.add_argument("--tc", type=int, default=1, help="0: keep long portions off the tcgen05 kernel")
     args = ap.parse_args(argv)
     native.lib()
-    (bench_gemm if args.what == "gemm" else bench_attention)(args)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.what](args)
     return 0
 
 

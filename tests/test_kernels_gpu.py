@@ -130,15 +130,18 @@ def _ref_qknorm_rope(qkv, nh, nkv, hd, qw, kw, eps, table, rd, positions):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,rd,page,use_norm", [(4, 2, 16, 16, 16, True), (5, 5, 48, 48, 8, True),
-                                                          (8, 1, 128, 64, 24, False), (6, 2, 80, 80, 16, True)])
-def test_qknorm_rope_kvwrite(native, dtype, nh, nkv, hd, rd, page, use_norm):
-    q_lens, starts = [3, 1, 19], [5, 40, 0]
+                                                          (8, 1, 128, 64, 24, False), (6, 2, 80, 80, 16, True),
+                                                          (32, 8, 128, 128, 16, True), (7, 7, 64, 64, 8, False),
+                                                          (6, 2, 256, 256, 16, True), (3, 1, 128, 0, 16, True)])
+@pytest.mark.parametrize("q_lens,starts", [([3, 1, 19], [5, 40, 0]), ([90, 1, 70], [3, 127, 0])])
+def test_qknorm_rope_kvwrite(native, dtype, nh, nkv, hd, rd, page, use_norm, q_lens, starts):
     S, T = len(q_lens), sum(q_lens)
     max_pos, eps, theta = 128, 1e-5, 10000.0
     table = _rope_table(max_pos, rd, theta)
     pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, q_lens)]).to(torch.int32).to(DEV)
     sot = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEV)
-    n_pages, P = 40, 8
+    P = -(-max_pos // page)
+    n_pages = S * P + 4
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(12))[: S * P].view(S, P)
     bt = perm.to(torch.int32).to(DEV)
     qkv = _rand((T, (nh + 2 * nkv) * hd), dtype, 13)
