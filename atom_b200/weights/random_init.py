@@ -67,3 +67,34 @@ def random_weights_on_device(model: Model, seed: int, compute: torch.dtype, devi
                 t[r0:r1].copy_(_draw((r1 - r0,) + tuple(ps.shape[1:]), ps.init, gen, device))
             out[f"{path}.{name}"] = t
     return out
+
+
+def main(argv=None) -> int:
+    """``python -m atom_b200.weights --config DIR_OR_JSON --seed N --out DIR``: a model
+    folder with the architecture and sizes of the given config.json and seeded random weights."""
+    import argparse
+    import shutil
+    import tempfile
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--config", required=True, help="a config.json, or a folder that holds one")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="storage type of the tensors")
+    args = ap.parse_args(argv)
+    from ..config.model_config import load_model_config
+
+    src = args.config
+    if os.path.isfile(src):        # load_model_config reads <folder>/config.json
+        tmp = tempfile.mkdtemp()
+        try:
+            shutil.copy(src, os.path.join(tmp, "config.json"))
+            config = load_model_config(tmp)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+    else:
+        config = load_model_config(src)
+    write_random_model(args.out, config, args.seed, torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
+    print(f"wrote {args.out}: {config.architecture}, seed {args.seed}")
+    return 0
+
