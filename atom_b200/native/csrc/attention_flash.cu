@@ -553,6 +553,12 @@ __global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
 // page instead and masked like any key outside the causal range (the cache holds finite numbers
 // everywhere, so 0 * V is 0).
 //
+// Launched with programmatic stream serialization, the kernel asks for the pages that hold only
+// earlier steps' keys before it waits for the kernel in front of it.  That is right when that
+// kernel writes, of the cache, only this step's new keys and values and itself waited for its
+// predecessors before it released this one: the rotation / cache-write kernel, which always
+// comes directly before attention.
+//
 // A warp's tile: S^T[KTW keys, 8 NQ rows] = K Q^T (A = K from ldmatrix, B = Q^T held in
 // registers; two accumulators over the head size to shorten the dependent chain), softmax down
 // the key axis (a thread holds keys g, g + 8 of each 16 for columns 2 t4, 2 t4 + 1; the maximum
@@ -753,7 +759,7 @@ __device__ __forceinline__ void warp_tile_t(AccT<NQ>& acc, const uint32_t (*qf)[
 template <int NQ, int KTW>
 __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, unsigned char* ring, uint64_t* full,
                                                 const CUtensorMap* kmap, const CUtensorMap* vmap, int* aborted,
-                                                const __nv_bfloat16* sQ, int tile_begin, int tile_end,
+                                                __nv_bfloat16* sQ, int tile_begin, int tile_end,
                                                 int key_end, int split, unsigned char* smem_raw) {
   constexpr int TMA_STAGE_BYTES = tma_stage_bytes(KTW);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -787,17 +793,35 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
     if (issuer) atom::tma::load_chunks(ring + st * TMA_STAGE_BYTES + my_dst, my_map, row, 0, &full[st]);
   };
 
-  // The warp's first RING tiles.
+  // The warp's first RING tiles.  Those that hold only keys from before this step are asked for at
+  // once: the kernel before this one (which may still be running) writes the step's new keys and
+  // nothing else of the cache, and the step's arrays were filled before it began.  The others, and Q,
+  // follow once that kernel has completed.
   int row_next;
   {
     int rows[RING + 1];
 #pragma unroll
     for (int i = 0; i <= RING; ++i) rows[i] = box_row(tile_begin + warp + 4 * i);
+    bool early[RING];
+#pragma unroll
+    for (int i = 0; i < RING; ++i) {
+      const int t = tile_begin + warp + 4 * i;
+      early[i] = t < tile_end && (t + 1) * KTW <= w.q_start;
+      if (early[i]) issue(i, rows[i]);
+    }
+    atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+    atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
 #pragma unroll
     for (int i = 0; i < RING; ++i)
-      if (tile_begin + warp + 4 * i < tile_end) issue(i, rows[i]);
+      if (!early[i] && tile_begin + warp + 4 * i < tile_end) issue(i, rows[i]);
     row_next = rows[RING];
   }
+  if (tile_begin < tile_end) {
+    load_q_tile<16>(p, w, sQ);
+    cp_async_commit();
+    cp_async_wait<0>();
+  }
+  __syncthreads();
 
   int pos[NQ][2];
 #pragma unroll
@@ -890,8 +914,8 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
     atom::tma::prefetch_map(&vmap);
   }
   __syncthreads();
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+  // (no wait for the kernel before this one yet: see decode_tma_body.  The arrays read here were
+  // filled before that kernel began, since it waited for its own predecessors before it let this one start.)
 
   Work w;
   w.seq = blockIdx.x;
@@ -917,12 +941,6 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
   const int tile_begin = big_begin * (BN / KTW);
   const int tile_end = min(big_end * (BN / KTW), (key_end + KTW - 1) / KTW);
 
-  if (tile_begin < tile_end) {
-    load_q_tile<16>(p, w, sQ);
-    cp_async_commit();
-    cp_async_wait<0>();
-  }
-  __syncthreads();
   const int warp = threadIdx.x >> 5;
   unsigned char* ring = rings + warp * RING * TMA_STAGE_BYTES;
   if (w.rows_total <= 8)
