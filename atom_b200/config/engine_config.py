@@ -25,6 +25,7 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     load_dummy: Optional[str] = None      # "random": seeded random weights instead of the file
     seed: int = 0
+    torch_profiler_dir: Optional[str] = None   # where start_profile / stop_profile write their traces
 
     def __post_init__(self) -> None:
         aliases = {"bf16": "bfloat16", "fp32": "float32"}

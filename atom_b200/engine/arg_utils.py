@@ -2,7 +2,8 @@
 has them (atom/model_engine/arg_utils.py:90-542): --model :93, --enforce-eager :145,
 --kv_cache_dtype :163, --block-size :180, --max-model-len :183, --cudagraph-capture-sizes :189,
 --load_dummy :209, --max-num-batched-tokens :331, --long-prefill-token-threshold :337,
---enable_chunked_prefill :373, --max-num-seqs :380, --gpu-memory-utilization :386.
+--enable_chunked_prefill :373, --max-num-seqs :380, --gpu-memory-utilization :386,
+--torch-profiler-dir :233.
 Added: --dtype, --seed, --num-kvcache-blocks.  Options for several GPUs, servers,
 quantization and speculative decoding are not taken."""
 from __future__ import annotations
@@ -30,6 +31,7 @@ class EngineArgs:
     gpu_memory_utilization: float = 0.9
     num_kvcache_blocks: int = -1
     seed: int = 0
+    torch_profiler_dir: Optional[str] = None
 
     @staticmethod
     def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
@@ -58,6 +60,8 @@ class EngineArgs:
         parser.add_argument("--num-kvcache-blocks", type=int, default=-1,
                             help="Pages of the KV cache (-1: size from free memory).")
         parser.add_argument("--seed", type=int, default=0, help="Seed of random weights and of sampling.")
+        parser.add_argument("--torch-profiler-dir", type=str, default=None,
+                            help="Directory to save torch profiler traces")
         return parser
 
     @classmethod
@@ -75,7 +79,7 @@ class EngineArgs:
             long_prefill_token_threshold=self.long_prefill_token_threshold,
             enable_chunked_prefill=self.enable_chunked_prefill, max_num_seqs=self.max_num_seqs,
             gpu_memory_utilization=self.gpu_memory_utilization, num_kvcache_blocks=self.num_kvcache_blocks,
-            seed=self.seed,
+            seed=self.seed, torch_profiler_dir=self.torch_profiler_dir,
         )
 
     def create_engine(self):

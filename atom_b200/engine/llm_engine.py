@@ -74,6 +74,41 @@ class LLMEngine:
         self.num_overlapped = 0
         self._pin_ring = None
         self._pin_next = 0
+        self._profiler = None
+
+    # ------------------------------------------------------------------ profiling
+
+    def start_profile(self) -> None:
+        """Starts a torch profiler (host and device activity) if ``torch_profiler_dir`` is set; the
+        trace is written by ``stop_profile``.  (The reference's start_profile / stop_profile,
+        atom/model_engine/llm_engine.py:286-295, model_runner.py:1025-1130.)"""
+        if self.config.torch_profiler_dir is None or self._profiler is not None:
+            return
+        from torch.profiler import ProfilerActivity, profile
+
+        os.makedirs(self.config.torch_profiler_dir, exist_ok=True)
+        self._profiler = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA])
+        self._profiler.__enter__()
+
+    def stop_profile(self) -> Optional[str]:
+        """Stops the profiler and writes ``<model name>_ts_<time>.pt.trace.json.gz``; returns its path."""
+        if self._profiler is None:
+            return None
+        import gzip
+        import shutil
+
+        prof, self._profiler = self._profiler, None
+        torch.cuda.synchronize(self.runner.device)
+        prof.__exit__(None, None, None)
+        name = os.path.basename(self.config.model.rstrip("/")) or "trace"
+        name = "".join(c if c.isalnum() or c in "_-." else "_" for c in name)
+        stamp = time.strftime("%Y%m%d_%H%M%S") + f"_{int(time.time() % 1 * 1000):03d}"
+        path = os.path.join(self.config.torch_profiler_dir, f"{name}_ts_{stamp}.pt.trace.json")
+        prof.export_chrome_trace(path)
+        with open(path, "rb") as src, gzip.open(path + ".gz", "wb") as dst:
+            shutil.copyfileobj(src, dst)
+        os.remove(path)
+        return path + ".gz"
 
     # ------------------------------------------------------------------ requests
 

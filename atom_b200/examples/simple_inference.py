@@ -41,7 +41,11 @@ def main(argv=None) -> int:
             prompts = [[1 % V, 2 % V, 3 % V], [(7 * i + 5) % V for i in range(19)]]
     sp = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, top_k=args.top_k,
                         top_p=args.top_p, ignore_eos=args.ignore_eos)
+    llm.start_profile()          # does nothing without --torch-profiler-dir
     outputs = llm.generate(prompts, sp)
+    trace = llm.stop_profile()
+    if trace:
+        print(f"profiler trace: {trace}")
     for prompt, out in zip(prompts, outputs):
         print("\n")
         print(f"Prompt: {prompt!r}")

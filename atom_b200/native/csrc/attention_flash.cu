@@ -956,15 +956,15 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
 // first take one split each to find the common maximum and the weights, then one output
 // element each (all loads of a pass are independent).  At most 64 splits.
 __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_of_token, int T) {
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T * p.nh) return;
   const int t = warp / p.nh;
-  const int s = seq_of_token[t];
+  const int s = seq_of_token[t];   // (the step's arrays are older than the kernel in front of this one)
   if (s < 0) return;  // a padding row of a fixed-size batch
   const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
   if (rows > 16) return;
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;
   const float* po = p.part_o + (int64_t)warp * p.num_splits * HD;
   const int k0 = lane, k1 = lane + 32;

@@ -70,11 +70,34 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
                                             const __nv_bfloat16* __restrict__ delta,
                                             const void* __restrict__ w, int w_dtype, float eps,
                                             const int* __restrict__ rows, int H) {
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
+  // The norm weights do not depend on the kernel in front of this one: they are on their way before the wait.
+  float wv[NV][8];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 8;
+    if (i < H) {
+      if (w_dtype == ATOM_F32) {
+        const float4 a = *reinterpret_cast<const float4*>((const float*)w + i);
+        const float4 b = *reinterpret_cast<const float4*>((const float*)w + i + 4);
+        wv[k][0] = a.x; wv[k][1] = a.y; wv[k][2] = a.z; wv[k][3] = a.w;
+        wv[k][4] = b.x; wv[k][5] = b.y; wv[k][6] = b.z; wv[k][7] = b.w;
+      } else {
+        const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          wv[k][2 * e] = f.x;
+          wv[k][2 * e + 1] = f.y;
+        }
+      }
+    }
+  }
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   float* res = residual + src * H;
   const __nv_bfloat16* d = delta ? delta + src * H : nullptr;
   float v[NV][8];
@@ -112,26 +135,11 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
   for (int k = 0; k < NV; ++k) {
     const int i = (threadIdx.x + k * blockDim.x) * 8;
     if (i < H) {
-      float wv[8];
-      if (w_dtype == ATOM_F32) {
-        const float4 a = *reinterpret_cast<const float4*>((const float*)w + i);
-        const float4 b = *reinterpret_cast<const float4*>((const float*)w + i + 4);
-        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-      } else {
-        const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + i);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h[e]);
-          wv[2 * e] = f.x;
-          wv[2 * e + 1] = f.y;
-        }
-      }
       uint4 q;
       __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        h[e] = __floats2bfloat162_rn(v[k][2 * e] * rstd * wv[2 * e], v[k][2 * e + 1] * rstd * wv[2 * e + 1]);
+        h[e] = __floats2bfloat162_rn(v[k][2 * e] * rstd * wv[k][2 * e], v[k][2 * e + 1] * rstd * wv[k][2 * e + 1]);
       *reinterpret_cast<uint4*>(o + i) = q;
     }
   }

@@ -105,8 +105,8 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
     int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
     int64_t num_pages, int* __restrict__ status) {
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+  // Where the token lies, its angles and the weights are read before the wait for the kernel in
+  // front of this one (which writes qkv only): they were there before that kernel began.
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int t = blockIdx.x;
@@ -162,6 +162,15 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     }
   };
   bool have_q = false, have_k = false;
+  if (head0 < nh) {
+    load_weights(q_w);
+    have_q = true;
+  } else if (head0 < nh + nkv) {
+    load_weights(k_w);
+    have_k = true;
+  }
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int stride = gridDim.y * warps;
   for (int head = head0; head < head_end; head += stride) {
     const bool is_q = head < nh;
@@ -235,8 +244,7 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
     int max_pages, int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
     int64_t num_pages, int* __restrict__ status) {
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+  // (what does not depend on the kernel in front of this one is read before the wait for it)
   constexpr int HD = 16 * LPH, HPW = 32 / LPH;   // heads a warp takes at a time
   const int lane = threadIdx.x & 31, sub = lane / LPH, l = lane % LPH;
   const int warps = blockDim.x >> 5;
@@ -275,6 +283,8 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
     wk[j] = k_w ? load_as_float(k_w, w_dtype, 8 * l + j) : 1.f;
     wk[8 + j] = k_w ? load_as_float(k_w, w_dtype, HD / 2 + 8 * l + j) : 1.f;
   }
+  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
+  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int stride = gridDim.y * warps * HPW;
   // every lane of a warp runs the same number of rounds (the shuffles below need all lanes)
   const int warp_head0 = (blockIdx.y * warps + (threadIdx.x >> 5)) * HPW;
