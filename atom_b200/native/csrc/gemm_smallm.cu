@@ -9,11 +9,14 @@
 // engine's rate is counted in operations as much as in bytes.
 // Four consumer warps take one box each and feed mma.sync.m16n8k16 with W rows as the 16-row
 // operand and the tokens as the 8-column operand, so padding the few tokens to 8 wastes
-// tensor flops, not bytes.  At the end of a slab the four warps' partial sums are added in
-// shared memory in a fixed order (the result does not depend on timing) and written as bf16
-// or 32-bit, with an optional bias, or, in gated mode, as silu(gate) * up for
+// tensor flops, not bytes.  At the end of a slab the four warps put their partial sums into
+// one of two buffers in shared memory and go on with the next slab at once; a sixth warp adds
+// them in a fixed order (the result does not depend on timing) and writes them as bf16 or
+// 32-bit, with an optional bias, or, in gated mode, as silu(gate) * up for
 // W = [gate rows ; up rows]: the feed-forward's activation never travels through memory.
-// Meanwhile the producer is already streaming the next slab.
+// The consumers never stand still for an epilogue, so stages are released and loads are asked
+// for without a pause: one SM's stream from HBM runs at no more than ~22 bytes a clock, about
+// its share of the memory bandwidth, and every pause of it is lost for good.
 //
 // Work is the sequence of all (slab, 256-k stage) pairs, slab-major, cut into one contiguous
 // range per CTA of equal length (+-1 stage), so every CTA streams the same number of bytes
@@ -37,7 +40,7 @@ namespace smallm {
 using namespace atom::tma;
 
 constexpr int NCONS = 4;                 // consumer warps, one 64-element box of a stage each
-constexpr int NTHREADS = (NCONS + 1) * 32;
+constexpr int NTHREADS = (NCONS + 2) * 32;   // + the producer warp and the epilogue warp
 constexpr int BK = NCONS * BOX_COLS;     // k elements per stage
 constexpr int MAX_GRID = 256;            // most CTAs of a launch whose ranges may share slabs
 
@@ -138,11 +141,20 @@ struct Cfg {
   static constexpr int STAGE = NCONS * (W_BOX + X_BOX);
   static constexpr size_t RING = (size_t)NS * STAGE;
   static constexpr int RLD = ROWS + 1;   // padded stride of the reduction buffer [warp][token][row]
-  static constexpr size_t RED = sizeof(float) * (size_t)NCONS * MP * RLD;
-  static constexpr size_t SMEM = 1024 + RING + ((RED + 15) / 16) * 16 + 2 * NS * sizeof(uint64_t) + 16;
+  static constexpr size_t RED1 = ((sizeof(float) * (size_t)NCONS * MP * RLD + 15) / 16) * 16;   // one buffer
+  static constexpr size_t RED = 2 * RED1;
+  static constexpr size_t SMEM = 1024 + RING + RED + (2 * NS + 4) * sizeof(uint64_t) + 16;
 };
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(NCONS * 32) : "memory"); }
+// The next piece of a CTA's walk that lies in one slab: stages [kt_first, kt_last) of `slab`.
+__device__ __forceinline__ void next_segment(Walk& w, int& slab, int& kt_first, int& kt_last) {
+  slab = w.slab;
+  kt_first = kt_last = w.kt;
+  while (w.valid() && w.slab == slab && w.kt == kt_last) {
+    ++kt_last;
+    w.advance();
+  }
+}
 
 template <int MT, int RT, int NS>
 __global__ void __launch_bounds__(NTHREADS)
@@ -154,9 +166,11 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   extern __shared__ unsigned char smem_raw[];
   // boxes of the 128-byte swizzle start on 1024-byte boundaries
   unsigned char* ring = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-  float* red = reinterpret_cast<float*>(ring + C::RING);   // [NCONS][MP][RLD]
-  uint64_t* full = reinterpret_cast<uint64_t*>(ring + C::RING + ((C::RED + 15) / 16) * 16);
+  float* red = reinterpret_cast<float*>(ring + C::RING);   // two buffers [NCONS][MP][RLD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + C::RING + C::RED);
   uint64_t* empty = full + NS;
+  uint64_t* red_full = empty + NS;     // [2] the consumers have put a segment's sums into the buffer
+  uint64_t* red_empty = red_full + 2;  // [2] the epilogue warp has taken them out
   __shared__ int aborted;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -165,6 +179,10 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     for (int s = 0; s < NS; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], NCONS);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&red_full[b], NCONS);
+      mbar_init(&red_empty[b], 1);
     }
     mbar_fence_init();
   }
@@ -226,19 +244,142 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     return;
   }
 
-  // ------------------------------------------------------------------ consumers
-  // (their first full barrier completes only after the producer's wait, so the outputs below
-  // are written after the kernels before this one have completed)
-  const int mat = lane >> 3, r8 = lane & 7;
-  const int tid = threadIdx.x;   // 0 .. NCONS * 32 - 1
-  __shared__ int is_last;
-  __shared__ int part_slot[MAX_GRID];   // for the contributors of a shared slab: index of the slot each wrote
   const int head_slab = (int)(g_begin / num_kt);
+  auto write_out = [&](int m, int col, float v, float uval) {
+    if (p.gated) {
+      v = v / (1.f + __expf(-v)) * uval;
+    } else if (p.bias != nullptr) {
+      v += load_as_float(p.bias, p.bias_dtype, col);
+    }
+    if (p.out_dtype == ATOM_F32)
+      reinterpret_cast<float*>(p.out)[(int64_t)m * p.ldc + col] = v;
+    else
+      reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.ldc + col] = __float2bfloat16_rn(v);
+  };
+  // Outputs first, first + stride, ... of a slab that this CTA holds whole: the four warps' sums, added in order.
+  auto write_whole = [&](const float* rb, int n0, int first, int stride) {
+    const int n_out = out_per_slab * p.M;
+    for (int idx = first; idx < n_out; idx += stride) {
+      const int m = idx / out_per_slab, r = idx - m * out_per_slab;
+      if (n0 + r >= p.N) continue;
+      float v = 0.f, uval = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < NCONS; ++wv) v += rb[((size_t)wv * MP + m) * RLD + r];
+      if (p.gated) {
+#pragma unroll
+        for (int wv = 0; wv < NCONS; ++wv) uval += rb[((size_t)wv * MP + m) * RLD + ROWS / 2 + r];
+      }
+      write_out(m, n0 + r, v, uval);
+    }
+  };
+  if (warp == NCONS + 1) {
+    // ---------------------------------------------------------------- epilogue warp
+    __shared__ int part_slot[MAX_GRID];   // for the contributors of a shared slab: index of the slot each wrote
+    Walk walk(g_begin, g_end, num_kt);
+    for (int seg = 0; walk.valid(); ++seg) {
+      int slab, kt_first, kt_last;
+      next_segment(walk, slab, kt_first, kt_last);
+      const int n0 = slab * out_per_slab;
+      const int b = seg & 1;
+      const float* rb = red + (size_t)b * (C::RED1 / sizeof(float));
+      mbar_wait(&red_full[b], (seg >> 1) & 1, &aborted, p.error);
+
+      // Does this range hold the whole slab?  If not: which CTAs share it, and which of them is this one.
+      const bool whole = kt_first == 0 && kt_last == num_kt;
+      int c_first = blockIdx.x, nparts = 1;
+      bool finish = true;
+      if (!whole) {
+        const long long s_begin = (long long)slab * num_kt, s_end = s_begin + num_kt, G = gridDim.x;
+        c_first = (int)(((s_begin + 1) * G + p.total - 1) / p.total) - 1;   // the last CTA whose range begins at or before the slab's first stage
+        const int c_last = (int)((s_end * G + p.total - 1) / p.total) - 1;  // ... at or before its last stage
+        nparts = c_last - c_first + 1;
+        // this CTA's slot: 0 if the slab is the first of its range, else 1
+        float* slot = p.slots + ((size_t)blockIdx.x * 2 + (slab == head_slab ? 0 : 1)) * (MP * ROWS);
+        for (int idx = lane; idx < MP * ROWS; idx += 32) {
+          const int m = idx / ROWS, r = idx - m * ROWS;
+          float v = 0.f;
+#pragma unroll
+          for (int wv = 0; wv < NCONS; ++wv) v += rb[((size_t)wv * MP + m) * RLD + r];
+          slot[idx] = v;
+        }
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          const int old = atomicAdd(p.counters + slab, 1);
+          last = old == nparts - 1;
+          if (last) p.counters[slab] = 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        finish = last != 0;
+        if (finish) {
+          __threadfence();
+          for (int j = lane; j < nparts; j += 32) {
+            const int c = c_first + j;
+            const bool head = (range_begin(p, c, num_kt) / num_kt) == slab;   // the slab is the first of c's range
+            part_slot[j] = c * 2 + (head ? 0 : 1);
+          }
+          __syncwarp();
+        }
+      }
+      if (finish) {
+        const int n_out = out_per_slab * p.M;
+        if (whole) {
+          // the last segment of the walk has nothing after it to hide behind: the consumer warps share its outputs
+          const bool shared = !walk.valid();
+          write_whole(rb, n0, shared ? NCONS * 32 + lane : lane, shared ? (NCONS + 1) * 32 : 32);
+        } else {
+          // The contributors' sums come from L2: eight outputs of a lane at a time, all their loads in
+          // flight together, added in the order of the ranges.
+          constexpr int E = 8;
+          for (int base = 0; base < n_out; base += 32 * E) {
+            float v[E], uval[E];
+            int off[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              const int idx = base + e * 32 + lane;
+              const int m = idx / out_per_slab, r = idx - m * out_per_slab;
+              off[e] = (idx < n_out && n0 + r < p.N) ? m * ROWS + r : -1;
+              v[e] = uval[e] = 0.f;
+            }
+            for (int j = 0; j < nparts; ++j) {
+              const float* slot = p.slots + (size_t)part_slot[j] * (MP * ROWS);
+              float t[E], tu[E];
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                t[e] = off[e] >= 0 ? __ldcg(slot + off[e]) : 0.f;
+                tu[e] = (off[e] >= 0 && p.gated) ? __ldcg(slot + off[e] + ROWS / 2) : 0.f;
+              }
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                v[e] += t[e];
+                uval[e] += tu[e];
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              if (off[e] < 0) continue;
+              const int idx = base + e * 32 + lane;
+              const int m = idx / out_per_slab, r = idx - m * out_per_slab;
+              write_out(m, n0 + r, v[e], uval[e]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_empty[b]);   // the buffer may take the segment after the next
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  // (their first full barrier completes only after the producer's wait, so everything that is
+  // written to global memory, by the epilogue warp, comes after the kernels before this one)
+  const int mat = lane >> 3, r8 = lane & 7;
   int s = 0, u = 0;   // stage s of the ring, in its u-th use
   Walk walk(g_begin, g_end, num_kt);
-  while (walk.valid()) {
-    const int slab = walk.slab, kt_first = walk.kt;
-    const int n0 = slab * out_per_slab;
+  for (int seg = 0; walk.valid(); ++seg) {
+    const int kt_first = walk.kt, slab = walk.slab;
     float acc[RT][MT][4];
 #pragma unroll
     for (int i = 0; i < RT; ++i)
@@ -294,104 +435,30 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         ++u;
       }
     }
-    // The four warps' partial sums go to shared memory; they are added in a fixed order below.
+    // The warp's partial sums go to the segment's buffer as soon as the epilogue warp has emptied it.
     {
+      const int b = seg & 1;
+      float* rb = red + (size_t)b * (C::RED1 / sizeof(float));
+      mbar_wait(&red_empty[b], ((seg >> 1) & 1) ^ 1, &aborted, p.error);
       const int g4 = lane >> 2, t4 = lane & 3;
 #pragma unroll
       for (int i = 0; i < RT; ++i)
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          float* base = red + ((size_t)warp * MP + j * 8 + 2 * t4) * RLD + i * 16 + g4;
+          float* base = rb + ((size_t)warp * MP + j * 8 + 2 * t4) * RLD + i * 16 + g4;
           base[0] = acc[i][j][0];
           base[RLD] = acc[i][j][1];
           base[8] = acc[i][j][2];
           base[RLD + 8] = acc[i][j][3];
         }
-    }
-    consumer_sync();
-
-    // Does this range hold the whole slab?  If not: which CTAs share it, and which of them is this one.
-    const bool whole = kt_first == 0 && kt_last == num_kt;
-    int c_first = blockIdx.x, nparts = 1;
-    bool finish = true;
-    if (!whole) {
-      const long long s_begin = (long long)slab * num_kt, s_end = s_begin + num_kt, G = gridDim.x;
-      c_first = (int)(((s_begin + 1) * G + p.total - 1) / p.total) - 1;   // the last CTA whose range begins at or before the slab's first stage
-      const int c_last = (int)((s_end * G + p.total - 1) / p.total) - 1;  // ... at or before its last stage
-      nparts = c_last - c_first + 1;
-      // this CTA's slot: 0 if the slab is the first of its range, else 1
-      float* slot = p.slots + ((size_t)blockIdx.x * 2 + (slab == head_slab ? 0 : 1)) * (MP * ROWS);
-      for (int idx = tid; idx < MP * ROWS; idx += NCONS * 32) {
-        const int m = idx / ROWS, r = idx - m * ROWS;
-        float v = 0.f;
-#pragma unroll
-        for (int wv = 0; wv < NCONS; ++wv) v += red[((size_t)wv * MP + m) * RLD + r];
-        slot[idx] = v;
-      }
-      __threadfence();
-      consumer_sync();
-      if (tid == 0) {
-        const int old = atomicAdd(p.counters + slab, 1);
-        is_last = old == nparts - 1;
-        if (is_last) p.counters[slab] = 0;
-      }
-      consumer_sync();
-      finish = is_last != 0;
-      if (finish) {
-        __threadfence();
-        for (int j = tid; j < nparts; j += NCONS * 32) {
-          const int c = c_first + j;
-          const bool head = (range_begin(p, c, num_kt) / num_kt) == slab;   // the slab is the first of c's range
-          part_slot[j] = c * 2 + (head ? 0 : 1);
-        }
-        consumer_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_full[b]);
+      if (!walk.valid() && kt_first == 0 && kt_last == num_kt) {
+        // the walk's last segment, a whole slab: every warp writes a share of its outputs
+        mbar_wait(&red_full[b], (seg >> 1) & 1, &aborted, p.error);
+        write_whole(rb, slab * out_per_slab, warp * 32 + lane, (NCONS + 1) * 32);
       }
     }
-    if (finish) {
-      for (int idx = tid; idx < out_per_slab * p.M; idx += NCONS * 32) {
-        const int m = idx / out_per_slab, r = idx - m * out_per_slab;
-        const int col = n0 + r;
-        if (col >= p.N) continue;
-        float v = 0.f, uval = 0.f;
-        if (whole) {
-#pragma unroll
-          for (int wv = 0; wv < NCONS; ++wv) v += red[((size_t)wv * MP + m) * RLD + r];
-          if (p.gated) {
-#pragma unroll
-            for (int wv = 0; wv < NCONS; ++wv) uval += red[((size_t)wv * MP + m) * RLD + ROWS / 2 + r];
-          }
-        } else {
-          // four contributors' loads in flight at a time; added in the order of the ranges
-          for (int j0 = 0; j0 < nparts; j0 += 4) {
-            float t[4], tu[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              t[q] = tu[q] = 0.f;
-              if (j0 + q < nparts) {
-                const float* slot = p.slots + (size_t)part_slot[j0 + q] * (MP * ROWS);
-                t[q] = __ldcg(slot + m * ROWS + r);
-                if (p.gated) tu[q] = __ldcg(slot + m * ROWS + ROWS / 2 + r);
-              }
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              v += t[q];
-              uval += tu[q];
-            }
-          }
-        }
-        if (p.gated) {
-          v = v / (1.f + __expf(-v)) * uval;
-        } else if (p.bias != nullptr) {
-          v += load_as_float(p.bias, p.bias_dtype, col);
-        }
-        if (p.out_dtype == ATOM_F32)
-          reinterpret_cast<float*>(p.out)[(int64_t)m * p.ldc + col] = v;
-        else
-          reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)m * p.ldc + col] = __float2bfloat16_rn(v);
-      }
-    }
-    consumer_sync();   // the reduction buffer is free for the next slab
   }
 }
 
@@ -410,7 +477,7 @@ static int sm_count() {
 template <int MT, int RT>
 struct Shape {
   static constexpr size_t STAGE = (size_t)NCONS * (RT * 16 + MT * 8) * 128;
-  static constexpr size_t RED = sizeof(float) * (size_t)NCONS * MT * 8 * (RT * 16 + 1) + 16;
+  static constexpr size_t RED = 2 * (sizeof(float) * (size_t)NCONS * MT * 8 * (RT * 16 + 1) + 16);   // two buffers
   static constexpr int FIT = (int)((220 * 1024 - RED - 1024 - 256) / STAGE);
   static constexpr int NS = FIT > 8 ? 8 : FIT;
   static_assert(NS >= 2, "at least two stages");

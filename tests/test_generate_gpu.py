@@ -199,3 +199,19 @@ def test_overlapped_decode_steps_give_the_same_tokens(model_dirs, dtype):
     eng.overlap_steps = False
     again = eng.generate(prompts, sps)
     assert [o["token_ids"] for o in again] == [o["token_ids"] for o in outs]
+
+
+def test_profiler_hook_writes_a_trace(model_dirs, tmp_path):
+    """start_profile / stop_profile (the reference's names) write a chrome trace with the engine's kernels."""
+    import gzip
+    import json
+    eng = _engine(model_dirs["A"], "bfloat16", pages=32, page=8, torch_profiler_dir=str(tmp_path / "prof"))
+    eng.start_profile()
+    from atom_b200 import SamplingParams
+    eng.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    path = eng.stop_profile()
+    assert path and path.endswith(".pt.trace.json.gz")
+    with gzip.open(path) as f:
+        names = [e["name"] for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+    assert any("rmsnorm" in n for n in names) and any("embedding" in n for n in names)
+    assert eng.stop_profile() is None            # nothing running any more
