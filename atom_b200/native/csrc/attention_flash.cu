@@ -303,8 +303,8 @@ constexpr size_t prefill_smem_bytes() {
 }
 
 __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sKV = sQ + BM * LDS;
@@ -444,8 +444,8 @@ constexpr size_t decode_smem_bytes() {
 }
 
 __global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sKV = sQ + 16 * LDS;
@@ -554,10 +554,8 @@ __global__ void __launch_bounds__(NT, 2) flash_decode_kernel(const Params p) {
 // everywhere, so 0 * V is 0).
 //
 // Launched with programmatic stream serialization, the kernel asks for the pages that hold only
-// earlier steps' keys before it waits for the kernel in front of it.  That is right when that
-// kernel writes, of the cache, only this step's new keys and values and itself waited for its
-// predecessors before it released this one: the rotation / cache-write kernel, which always
-// comes directly before attention.
+// earlier steps' keys before it waits for the kernels in front of it: within a step the cache
+// receives only that step's new keys and values.
 //
 // A warp's tile: S^T[KTW keys, 8 NQ rows] = K Q^T (A = K from ldmatrix, B = Q^T held in
 // registers; two accumulators over the head size to shorten the dependent chain), softmax down
@@ -809,8 +807,7 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
       early[i] = t < tile_end && (t + 1) * KTW <= w.q_start;
       if (early[i]) issue(i, rows[i]);
     }
-    atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-    atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+    atom::pdl_wait();      // inputs written by the kernels before this one are visible from here on
 #pragma unroll
     for (int i = 0; i < RING; ++i)
       if (!early[i] && tile_begin + warp + 4 * i < tile_end) issue(i, rows[i]);
@@ -914,8 +911,8 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
     atom::tma::prefetch_map(&vmap);
   }
   __syncthreads();
-  // (no wait for the kernel before this one yet: see decode_tma_body.  The arrays read here were
-  // filled before that kernel began, since it waited for its own predecessors before it let this one start.)
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
+  // (no wait for the kernels before this one yet: see decode_tma_body.  No kernel of the step writes the arrays read here.)
 
   Work w;
   w.seq = blockIdx.x;
@@ -924,7 +921,10 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
   w.q_begin = p.cu_q[w.seq];
   const int q_len = p.cu_q[w.seq + 1] - w.q_begin;
   w.rows_total = q_len * p.group;
-  if (w.rows_total <= 0 || w.rows_total > 16) return;
+  if (w.rows_total <= 0 || w.rows_total > 16) {
+    atom::pdl_wait();   // a grid is complete only after what came before it
+    return;
+  }
   w.ctx = p.ctx_len[w.seq];
   w.q_start = w.ctx - q_len;
   w.row0 = 0;
@@ -956,15 +956,15 @@ __global__ void __launch_bounds__(NT, decode_tma_ctas(KTW)) flash_decode_tma_ker
 // first take one split each to find the common maximum and the weights, then one output
 // element each (all loads of a pass are independent).  At most 64 splits.
 __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_of_token, int T) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= T * p.nh) return;
-  const int t = warp / p.nh;
-  const int s = seq_of_token[t];   // (the step's arrays are older than the kernel in front of this one)
-  if (s < 0) return;  // a padding row of a fixed-size batch
-  const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
-  if (rows > 16) return;
-  atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
+  int s = -1, rows = 0;
+  if (warp < T * p.nh) {
+    s = seq_of_token[warp / p.nh];   // (no kernel of the step writes the step's arrays)
+    if (s >= 0) rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
+  }
+  atom::pdl_wait();      // inputs written by the kernels before this one are visible from here on
+  if (s < 0 || rows > 16) return;   // beyond the batch, a padding row of a fixed-size batch, or not a short request
   const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;
   const float* po = p.part_o + (int64_t)warp * p.num_splits * HD;
   const int k0 = lane, k1 = lane + 32;

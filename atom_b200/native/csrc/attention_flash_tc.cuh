@@ -167,8 +167,8 @@ __global__ void __launch_bounds__(Roles<TMA>::NTHREADS, 1)
 flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Maps maps) {
   static_assert(HD == 128, "the tcgen05 attention kernel is written for head size 128");
   constexpr int LOADERS = Roles<TMA>::LOADERS, MMA_WARP = Roles<TMA>::MMA_WARP;
-  atom::pdl_wait();
   atom::pdl_trigger();
+  atom::pdl_wait();
   extern __shared__ unsigned char smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   Bars* bars = reinterpret_cast<Bars*>(smem_raw + (sbase - smem_u32(smem_raw)) + SMEM_DATA);

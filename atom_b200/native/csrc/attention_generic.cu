@@ -21,8 +21,8 @@ paged_attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int
                                const int* __restrict__ positions,
                                const int* __restrict__ seq_of_token, int nh, int nkv, int hd,
                                float scale, int window) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int64_t* row_off = (int64_t*)smem_raw;           // [kAttnChunk] element offset of a key's row
   float* prob = (float*)(row_off + kAttnChunk);    // [kAttnChunk]

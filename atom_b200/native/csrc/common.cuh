@@ -76,13 +76,19 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 // ------------------------------------------------------------------ programmatic dependent launch
-// Every kernel of the library starts with pdl_wait(): it returns when the kernels before it
-// in the stream have completed and their writes are visible.  Launched with launch_pdl, a
-// kernel may be scheduled while the one before it is still draining (after all of that
-// kernel's CTAs have passed pdl_trigger() or exited), so launch latency, the prologue, and,
-// where a kernel has inputs that no earlier kernel writes (weights), their first loads
-// overlap the predecessor's tail.  Nothing that depends on an earlier kernel may be read, and
-// nothing written, before pdl_wait().  Set ATOM_PDL=0 in the environment for plain launches.
+// Launched with launch_pdl, a kernel may be scheduled as soon as every CTA of the kernel before
+// it has passed pdl_trigger() (or exited), that is, while that kernel, and the ones before it,
+// still run.  pdl_wait() returns when the kernel before it has completed and its writes are
+// visible.  The rules that make a chain of such kernels right:
+//   * pdl_trigger() stands at the top of every kernel, so launch latency and prologues overlap
+//     whatever is still running;
+//   * before pdl_wait() a kernel reads only what no kernel of the same step writes: weights,
+//     tables, the step's index arrays (filled by copies before the step's first kernel), cache
+//     pages of earlier steps' tokens; it writes nothing to global memory;
+//   * every path through a kernel passes pdl_wait() before it ends (in at least one thread of
+//     every CTA that could otherwise be the last to finish: simplest, before every early
+//     return), so that a completed grid means that everything before it has completed too.
+// Set ATOM_PDL=0 in the environment for plain launches.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 

@@ -7,8 +7,8 @@ namespace atom {
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int H, int V) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int t = blockIdx.x;
   int id = ids[t];
   // Ids are validated on the host; the clamp only keeps a bad id from reading outside the table.

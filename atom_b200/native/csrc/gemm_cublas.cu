@@ -21,8 +21,8 @@ static cublasHandle_t handle_for_current_device() {
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ C, const void* __restrict__ bias, int bias_dtype,
                                 int64_t n, int N) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     C[i] = from_float<T>(to_float(C[i]) + load_as_float(bias, bias_dtype, i % N));

@@ -11,8 +11,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W,
                 const float* __restrict__ bias, int M, int N, int K, int64_t lda, int64_t ldc) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each

@@ -13,8 +13,8 @@ template <typename TA>
 __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ residual,
                                    const TA* __restrict__ delta, const void* __restrict__ w,
                                    int w_dtype, float eps, const int* __restrict__ rows, int H) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
@@ -45,8 +45,8 @@ __global__ void add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ res
 template <typename TA>
 __global__ void rmsnorm_kernel(TA* __restrict__ out, const TA* __restrict__ x,
                                const void* __restrict__ w, int w_dtype, float eps, int H) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float scratch[32];
   const TA* xi = x + (int64_t)blockIdx.x * H;
   TA* o = out + (int64_t)blockIdx.x * H;
@@ -70,6 +70,7 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
                                             const __nv_bfloat16* __restrict__ delta,
                                             const void* __restrict__ w, int w_dtype, float eps,
                                             const int* __restrict__ rows, int H) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int64_t src = rows ? rows[r] : r;
@@ -97,7 +98,6 @@ __global__ void add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, flo
     }
   }
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   float* res = residual + src * H;
   const __nv_bfloat16* d = delta ? delta + src * H : nullptr;
   float v[NV][8];

@@ -21,8 +21,8 @@ __global__ void qknorm_rope_kvwrite_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
     int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int64_t num_pages,
     int* __restrict__ status) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
@@ -105,8 +105,9 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
     int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
     int64_t num_pages, int* __restrict__ status) {
-  // Where the token lies, its angles and the weights are read before the wait for the kernel in
-  // front of this one (which writes qkv only): they were there before that kernel began.
+  // Where the token lies, its angles and the weights are read before the wait for the kernels in
+  // front of this one: no kernel of the step writes them.
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int t = blockIdx.x;
@@ -114,9 +115,15 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
   const bool write_cache = k_pages != nullptr;
   const int head_end = write_cache ? n_heads_total : nh;
   const int head0 = blockIdx.y * warps + (threadIdx.x >> 5);
-  if (head0 >= head_end) return;
+  if (head0 >= head_end) {
+    atom::pdl_wait();
+    return;
+  }
   const int seq = seq_of_token[t];
-  if (seq < 0) return;  // a padding row of a fixed-size batch
+  if (seq < 0) {  // a padding row of a fixed-size batch
+    atom::pdl_wait();
+    return;
+  }
   const int pos = positions[t];
 
   // where this token's keys and values go
@@ -125,7 +132,10 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     const int page = block_table[(int64_t)seq * max_pages + pos / page_size];
     if (page < 0 || page >= num_pages) {
       if (lane == 0 && head0 == 0) atomicExch(status, 1);
-      if (head0 >= nh) return;          // q heads of the token are still rotated
+      if (head0 >= nh) {                // q heads of the token are still rotated
+        atom::pdl_wait();
+        return;
+      }
     } else {
       kv_row = (int64_t)page * nkv * page_size + (pos % page_size);
     }
@@ -170,7 +180,6 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
     have_k = true;
   }
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int stride = gridDim.y * warps;
   for (int head = head0; head < head_end; head += stride) {
     const bool is_q = head < nh;
@@ -244,7 +253,8 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
     int max_pages, int page_size, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
     int64_t num_pages, int* __restrict__ status) {
-  // (what does not depend on the kernel in front of this one is read before the wait for it)
+  // (what no kernel of the step writes is read before the wait for the kernels in front of this one)
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   constexpr int HD = 16 * LPH, HPW = 32 / LPH;   // heads a warp takes at a time
   const int lane = threadIdx.x & 31, sub = lane / LPH, l = lane % LPH;
   const int warps = blockDim.x >> 5;
@@ -253,7 +263,10 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
   const bool write_cache = k_pages != nullptr;
   const int head_end = write_cache ? n_heads_total : nh;
   const int seq = seq_of_token[t];
-  if (seq < 0) return;  // a padding row of a fixed-size batch
+  if (seq < 0) {  // a padding row of a fixed-size batch
+    atom::pdl_wait();
+    return;
+  }
   const int pos = positions[t];
   int64_t kv_row = -1;   // row of the page matrices [pages * nkv * page][hd] for kv head 0
   if (write_cache) {
@@ -284,7 +297,6 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
     wk[8 + j] = k_w ? load_as_float(k_w, w_dtype, HD / 2 + 8 * l + j) : 1.f;
   }
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   const int stride = gridDim.y * warps * HPW;
   // every lane of a warp runs the same number of rounds (the shuffles below need all lanes)
   const int warp_head0 = (blockIdx.y * warps + (threadIdx.x >> 5)) * HPW;

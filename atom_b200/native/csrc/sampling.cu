@@ -61,8 +61,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits,
               const float* __restrict__ temperature, const uint32_t* __restrict__ seeds,
               const uint32_t* __restrict__ indices, const int* __restrict__ top_k,
               const float* __restrict__ top_p, float* __restrict__ probs, int V) {
+  atom::pdl_trigger();   // the next kernel may be scheduled at once: before its own wait it reads nothing a kernel of this step writes
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
-  atom::pdl_trigger();   // the next kernel may be scheduled (it waits in the same way)
   __shared__ float fscratch[32];
   __shared__ Best bscratch[32];
   const int r = blockIdx.x;
