@@ -1006,6 +1006,7 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
 
 #if ATOM_HD == 128
 #include "attention_flash_tc.cuh"
+#include "attention_flash_tc2.cuh"
 #endif
 
 namespace atom {
@@ -1144,7 +1145,19 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
         return ATOM_ERR_LAUNCH;
       tc_attr = true;
     }
-    if (use_tma)
+    static const bool two_tiles = [] { const char* e = getenv("ATOM_TC2"); return !(e != nullptr && e[0] == '0'); }();
+    if (use_tma && two_tiles) {
+      static bool tc2_attr = false;
+      if (!tc2_attr) {
+        if (cudaFuncSetAttribute(tc2::flash_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)tc2::smem_bytes2()) != cudaSuccess)
+          return ATOM_ERR_LAUNCH;
+        tc2_attr = true;
+      }
+      // (long_tiles counts 128-row tiles: an upper bound of the 256-row tiles; the CTAs beyond them leave at once)
+      atom::launch_pdl(tc2::flash_prefill_tc2_kernel, dim3(long_tiles, nkv), dim3(tc2::NTHREADS2), tc2::smem_bytes2(),
+                       stream, p, long_rows, maps);
+    } else if (use_tma)
       atom::launch_pdl(tc::flash_prefill_tc_kernel<true>, dim3(long_tiles, nkv), dim3(tc::Roles<true>::NTHREADS),
                        tc::smem_bytes(), stream, p, long_rows, maps);
     else

@@ -73,6 +73,14 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0)
       : "memory");
 }
+// The same with A taken from tensor memory: lane = row, 16 bf16 of a row in 8 consecutive 32-bit columns.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0)
+      : "memory");
+}
 // The mbarrier gets one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
@@ -392,10 +400,14 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
         const uint32_t pa = sbase + SMEM_P, va = sbase + SMEM_V + st * 2 * BLOCK;
 #pragma unroll
         for (int ks = 0; ks < TN / 16; ++ks) {
-          // P: K-major along the keys; V: MN-major, 16 keys are 2048 bytes further, the second
-          // 64 of the head size one block further.
-          umma(tmem + O_COL, smem_desc(pa + (ks >> 2) * BLOCK + (ks & 3) * 32, 16, 1024),
-               smem_desc(va + ks * 2048, BLOCK, 1024), idesc_o, (j > 0 || ks > 0));
+          // P: K-major along the keys (TMA variant: bf16 pairs in tensor memory, in the first 64 columns of the
+          // tile's S buffer); V: MN-major, 16 keys are 2048 bytes further, the second 64 of the head size one block further.
+          if constexpr (TMA)
+            umma_ts(tmem + O_COL, tmem + ((j & 1) ? S_COL1 : S_COL0) + ks * 8, smem_desc(va + ks * 2048, BLOCK, 1024),
+                    idesc_o, (j > 0 || ks > 0));
+          else
+            umma(tmem + O_COL, smem_desc(pa + (ks >> 2) * BLOCK + (ks & 3) * 32, 16, 1024),
+                 smem_desc(va + ks * 2048, BLOCK, 1024), idesc_o, (j > 0 || ks > 0));
         }
         umma_commit(&bars->v_empty[st]);
         umma_commit(&bars->o_full);
@@ -471,19 +483,18 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
         }
       }
       m = mx;
+      // P as bf16 pairs into the first 64 columns of this tile's S buffer (the row was read whole above)
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        uint32_t pk[4];
+      for (int q = 0; q < 2; ++q) {
+        float pk[32];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(s[8 * k + 2 * e], s[8 * k + 2 * e + 1]);
-          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        for (int e = 0; e < 32; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[q * 64 + 2 * e], s[q * 64 + 2 * e + 1]);
+          pk[e] = __uint_as_float(*reinterpret_cast<uint32_t*>(&h));
         }
-        const uint32_t a = sw_addr(sbase + SMEM_P, r, k);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(a), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
-                     "r"(pk[3])
-                     : "memory");
+        tmem_st32(scol + q * 32, pk);
       }
+      tmem_wait_st();
      } else {
       // Two passes over the row in tensor memory, 32 columns at a time (few live registers, the
       // next chunk's load in flight while this one is worked on): first the maximum, then P.

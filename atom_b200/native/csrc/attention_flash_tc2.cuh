@@ -1,0 +1,364 @@
+// Paged causal attention for long portions on tcgen05, two query tiles per CTA: head size 128,
+// bf16, pages of a power of two of 8 to 128 tokens, a group size that divides 128 (the sizes
+// whose pages and packed query rows come as TMA boxes).  Included by attention_flash.cu after
+// attention_flash_tc.cuh, whose primitives it uses.
+//
+// One CTA takes 256 packed query rows (row = token * G + head in group) of one (request, kv
+// head) as two tiles A and B of 128 rows, and walks over the request's keys in tiles of 128:
+//     S_X = Q_X K^T     tcgen05.mma, operands from shared memory, S_X (128 x 128, 32-bit) in
+//                       tensor memory, one buffer per query tile
+//     P_X = softmax     one warpgroup per query tile, one row per thread, 32 columns at a time
+//                       in two passes (maximum, then exponentials); P_X goes back into the
+//                       first 64 columns of S_X as bf16 pairs
+//     O_X += P_X V      tcgen05.mma with A from tensor memory, V as it lies in the pages
+// The single MMA-issuing thread alternates between the tiles, S_A(0) S_B(0) | PV_A(0) S_A(1)
+// | PV_B(0) S_B(1) | PV_A(1) ..., so while one warpgroup computes exponentials the tensor
+// cores work for the other tile, and every K and V tile that comes into shared memory is used
+// for twice the rows.  Tensor memory: S_A, S_B, O_A, O_B = 512 columns.  Shared memory: Q 64 KB,
+// two stages of K and of V, 32 KB each.
+// Warps 0-3 softmax and epilogue of tile A, 4-7 of tile B (warp w owns TMEM lanes
+// 32 (w mod 4) ...), warp 8 issues the TMA boxes, warp 9 allocates tensor memory and issues
+// every MMA from one thread.  All waits are bounded; tensor memory is freed on every path.
+#pragma once
+#include "attention_flash_tc.cuh"
+
+namespace atom {
+namespace flash {
+namespace tc2 {
+
+using namespace atom::flash::tc;
+
+constexpr int ROWS2 = 2 * TM;                 // packed query rows per CTA
+constexpr int NTHREADS2 = 256 + 64;           // two softmax warpgroups, the loader warp, the MMA warp
+constexpr int LOAD_WARP = 8, MMA_WARP2 = 9;
+constexpr int KV_STAGES = 2;
+constexpr uint32_t SA_COL = 0, SB_COL = 128, OA_COL = 256, OB_COL = 384;
+// shared memory: Q_A, Q_B (2 blocks each), K stages (2 blocks each), V stages (2 blocks each)
+constexpr int S2_Q = 0, S2_K = 4 * BLOCK, S2_V = S2_K + KV_STAGES * 2 * BLOCK, S2_DATA = S2_V + KV_STAGES * 2 * BLOCK;
+constexpr size_t smem_bytes2() { return 1024 + S2_DATA + 256; }
+
+struct Bars2 {
+  uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_full[2], o_full[2];   // [0] tile A, [1] tile B
+  uint32_t tmem_base;
+  int aborted;
+};
+
+__global__ void __launch_bounds__(NTHREADS2, 1)
+flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ Maps maps) {
+  static_assert(HD == 128, "the tcgen05 attention kernel is written for head size 128");
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  Bars2* bars = reinterpret_cast<Bars2*>(smem_raw + (sbase - smem_u32(smem_raw)) + S2_DATA);
+
+  // Which (request, 256-row tile) is this CTA?  Requests with fewer than min_rows packed rows
+  // belong to the other kernels.  Within a request the last (longest) tiles come first.  The
+  // grid is sized for 128-row tiles, an upper bound: CTAs beyond the last tile leave at once.
+  Work w;
+  {
+    int tile = blockIdx.x, s = 0, nt = 0;
+    for (; s < p.num_seqs; ++s) {
+      const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
+      nt = rows >= min_rows ? (rows + ROWS2 - 1) / ROWS2 : 0;
+      if (tile < nt) break;
+      tile -= nt;
+    }
+    if (s == p.num_seqs) return;
+    w.seq = s;
+    w.kvh = blockIdx.y;
+    w.q_begin = p.cu_q[s];
+    const int q_len = p.cu_q[s + 1] - w.q_begin;
+    w.ctx = p.ctx_len[s];
+    w.q_start = w.ctx - q_len;
+    w.rows_total = q_len * p.group;
+    w.row0 = (nt - 1 - tile) * ROWS2;
+    w.bt = p.block_table + (int64_t)s * p.max_pages;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // key tiles of each query tile (0: the tile has no row)
+  int n_of[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int first = w.row0 + x * TM;
+    if (first >= w.rows_total) {
+      n_of[x] = 0;
+    } else {
+      const int last = min(first + TM, w.rows_total) - 1;
+      n_of[x] = (w.q_start + last / p.group + 1 + TN - 1) / TN;
+    }
+  }
+  const int n_tiles = max(n_of[0], n_of[1]);     // (tile B sees at least the keys tile A sees)
+  const int key_end = w.q_start + (min(w.row0 + ROWS2, w.rows_total) - 1) / p.group + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&bars->s_full[x], 1);
+      mbar_init(&bars->p_full[x], 128);
+      mbar_init(&bars->o_full[x], 1);
+    }
+    bars->aborted = 0;
+    mbar_fence_init();
+  }
+  if (warp == MMA_WARP2) tmem_alloc(&bars->tmem_base, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* aborted = &bars->aborted;
+
+  if (warp == LOAD_WARP) {
+    // ------------------------------------------------------------------ loader: TMA boxes
+    // A tile of 128 keys is 128 / page_size pages (or part of one page when pages are larger);
+    // every page gives two boxes, one per 64-element half of the head.  Lane l issues box l.
+    const int ps = p.page_size;
+    const int box_rows = ps < TN ? ps : TN;
+    const int ppt = TN / box_rows;                   // pages (boxes per half) of a tile
+    const int n_ops = 2 * ppt;
+    const int my_pg = lane >> 1, my_half = lane & 1;
+    const bool active = lane < n_ops;
+    // Row of the page matrix where this lane's box of tile j starts.  Pages beyond the last key
+    // are replaced by the request's first page: finite values that the causal mask removes.
+    auto box_row = [&](int j) -> int {
+      const int key = j * TN + my_pg * box_rows;
+      int lp = p.page_shift >= 0 ? (key >> p.page_shift) : (key / ps);
+      int in_page = key - lp * ps;
+      if (key >= key_end) { lp = 0; in_page = 0; }
+      const int page = active ? __ldg(w.bt + lp) : 0;
+      return (page * p.nkv + w.kvh) * ps + in_page;
+    };
+    if (lane < 4) {   // Q: each 128-row tile is 128 / group tokens of the group's heads, two 64-column boxes
+      if (lane == 0) atom::tma::mbar_expect_tx(&bars->q_full, 4 * BLOCK);
+      __syncwarp(0xfu);
+      const int x = lane >> 1, half = lane & 1;
+      // a tile without rows still gets a box (of rows that exist or of the fill value): the byte count stays fixed
+      const int tok0 = w.q_begin + min(w.row0 + x * TM, max(w.rows_total - 1, 0)) / p.group;
+      asm volatile(
+          "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::
+              "r"(sbase + S2_Q + (x * 2 + half) * BLOCK),
+          "l"(&maps.q), "r"(half * 64), "r"(w.kvh * p.group), "r"(tok0), "r"(smem_u32(&bars->q_full))
+          : "memory");
+    }
+    int row_k = box_row(0), row_v = row_k;
+    const int n_groups = 2 * n_tiles;     // K0, V0, K1, V1, ...
+#pragma unroll 1
+    for (int g = 0; g < n_groups; ++g) {
+      const bool is_k = (g & 1) == 0;
+      const int j = g >> 1, st = j % KV_STAGES;
+      uint64_t* full = is_k ? &bars->k_full[st] : &bars->v_full[st];
+      if (j >= KV_STAGES)
+        mbar_wait(is_k ? &bars->k_empty[st] : &bars->v_empty[st], ((j / KV_STAGES) & 1) ^ 1, aborted, p.error);
+      if (lane == 0) atom::tma::mbar_expect_tx(full, 2 * BLOCK);
+      __syncwarp();
+      if (active) {
+        const uint32_t dst = sbase + (is_k ? S2_K : S2_V) + st * 2 * BLOCK + my_half * BLOCK + my_pg * box_rows * 128;
+        atom::tma::load_box(reinterpret_cast<void*>(0), is_k ? &maps.k : &maps.v, my_half * 64, is_k ? row_k : row_v, full, dst);
+      }
+      if (is_k) row_k = box_row(j + 1); else row_v = box_row(j + 1);   // looked up a tile ahead
+    }
+  } else if (warp == MMA_WARP2) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t idesc_s = instr_desc(TM, TN, false), idesc_o = instr_desc(TM, HD, true);
+      const uint32_t s_col[2] = {SA_COL, SB_COL}, o_col[2] = {OA_COL, OB_COL};
+      int k_ready = -1;     // the last K tile whose arrival has been waited for
+      auto issue_s = [&](int x, int j) {
+        const int st = j % KV_STAGES;
+        if (k_ready < j) {
+          mbar_wait(&bars->k_full[st], (j / KV_STAGES) & 1, aborted, p.error);
+          tc_fence_after();
+          k_ready = j;
+        }
+        const uint32_t qa = sbase + S2_Q + x * 2 * BLOCK, ka = sbase + S2_K + st * 2 * BLOCK;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t o = (ks >> 2) * BLOCK + (ks & 3) * 32;
+          umma(tmem + s_col[x], smem_desc(qa + o, 16, 1024), smem_desc(ka + o, 16, 1024), idesc_s, ks > 0);
+        }
+        umma_commit(&bars->s_full[x]);
+      };
+      // K(j) is free when the last S of tile j has been issued and completed: tile B's if it has that tile,
+      // else tile A's.
+      auto last_user = [&](int j) { return j < n_of[1] ? 1 : 0; };
+      auto issue_pv = [&](int x, int j) {
+        const int st = j % KV_STAGES;
+        mbar_wait(&bars->p_full[x], j & 1, aborted, p.error);
+        tc_fence_after();
+        const uint32_t va = sbase + S2_V + st * 2 * BLOCK;
+#pragma unroll
+        for (int ks = 0; ks < TN / 16; ++ks)
+          umma_ts(tmem + o_col[x], tmem + s_col[x] + ks * 8, smem_desc(va + ks * 2048, BLOCK, 1024), idesc_o,
+                  (j > 0 || ks > 0));
+        umma_commit(&bars->o_full[x]);
+      };
+      mbar_wait(&bars->q_full, 0, aborted, p.error);
+      for (int x = 0; x < 2; ++x)
+        if (n_of[x] > 0) {
+          issue_s(x, 0);
+          if (last_user(0) == x) umma_commit(&bars->k_empty[0]);
+        }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j % KV_STAGES;
+        bool v_waited = false;
+        for (int x = 0; x < 2; ++x) {
+          if (j >= n_of[x]) continue;
+          if (!v_waited) {
+            mbar_wait(&bars->v_full[st], (j / KV_STAGES) & 1, aborted, p.error);
+            v_waited = true;
+          }
+          issue_pv(x, j);
+          if (last_user(j) == x) umma_commit(&bars->v_empty[st]);
+          if (j + 1 < n_of[x]) {
+            issue_s(x, j + 1);
+            if (last_user(j + 1) == x) umma_commit(&bars->k_empty[(j + 1) % KV_STAGES]);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax and epilogue of tile x
+    const int x = warp >> 2;
+    const int r = threadIdx.x & 127;                 // row of the tile = TMEM lane
+    const int R = w.row0 + x * TM + r;
+    const int pos = R < w.rows_total ? w.q_start + R / p.group : -1;
+    const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+    const uint32_t scol = tmem + lane_base + (x ? SB_COL : SA_COL);
+    const uint32_t ocol = tmem + lane_base + (x ? OB_COL : OA_COL);
+    const float c = p.scale_log2;
+    const int n_mine = n_of[x];
+    float m = -INFINITY, l = 0.f;
+    for (int j = 0; j < n_mine; ++j) {
+      mbar_wait(&bars->s_full[x], j & 1, aborted, p.error);
+      tc_fence_after();
+      const int key0 = j * TN;
+      const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
+      // first pass: the row's maximum, 32 columns at a time, the next chunk's load in flight
+      float buf[2][32];
+      float mx4[4] = {m, -INFINITY, -INFINITY, -INFINITY};
+      tmem_ld32(scol, buf[0]);
+#pragma unroll
+      for (int q = 0; q < TN / 32; ++q) {
+        float* cur = buf[q & 1];
+        tmem_wait_ld();
+        if (q + 1 < TN / 32) tmem_ld32(scol + (q + 1) * 32, buf[(q + 1) & 1]);
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + q * 32 + i > pos) cur[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          mx4[0] = fmaxf(mx4[0], cur[i]);
+          mx4[1] = fmaxf(mx4[1], cur[i + 1]);
+          mx4[2] = fmaxf(mx4[2], cur[i + 2]);
+          mx4[3] = fmaxf(mx4[3], cur[i + 3]);
+        }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float alpha = ex2((m - m_use) * c);
+      const float mc = m_use * c;
+      tmem_ld32(scol, buf[0]);                 // first chunk of the second pass
+      // O of the tile before: its MMA was issued before this tile's S, so it is complete by now; the
+      // wait only makes that visible to this thread.
+      if (j > 0) {
+        mbar_wait(&bars->o_full[x], (j - 1) & 1, aborted, p.error);
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, mx > m)) {      // some row of this warp has a new maximum: rescale O
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < HD / 32; ++q) {
+            float* o = buf[1];
+            tmem_ld32(ocol + q * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(ocol + q * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      m = mx;
+      // second pass: exponentials, their sum, and P as bf16 pairs into columns 16 q .. 16 q + 15 of the
+      // same buffer (behind the columns that have been read)
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < TN / 32; ++q) {
+        float* cur = buf[q & 1];
+        tmem_wait_ld();
+        if (q + 1 < TN / 32) tmem_ld32(scol + (q + 1) * 32, buf[(q + 1) & 1]);
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (key0 + q * 32 + i > pos) cur[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            cur[i + e] = ex2(fmaf(cur[i + e], c, -mc));
+            sum4[e] += cur[i + e];
+          }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(cur[2 * e], cur[2 * e + 1]);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::
+                "r"(scol + q * 16),
+            "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]), "r"(pk[8]),
+            "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]), "r"(pk[15])
+            : "memory");
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[x]);
+    }
+    // epilogue: O / l -> bf16 -> global
+    if (n_mine > 0) {
+      mbar_wait(&bars->o_full[x], (n_mine - 1) & 1, aborted, p.error);
+      tc_fence_after();
+      const float inv = 1.f / l;
+      __nv_bfloat16* orow = nullptr;
+      if (R < w.rows_total) {
+        const int tok = R / p.group, hig = R - tok * p.group;
+        orow = p.out + ((int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig)) * HD;
+      }
+#pragma unroll
+      for (int q = 0; q < HD / 32; ++q) {
+        float o[32];
+        tmem_ld32(ocol + q * 32, o);
+        tmem_wait_ld();
+        if (orow != nullptr && !*aborted) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 v;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(o[8 * k + 2 * e] * inv, o[8 * k + 2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(orow + q * 32 + k * 8) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP2) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace tc2
+}  // namespace flash
+}  // namespace atom
