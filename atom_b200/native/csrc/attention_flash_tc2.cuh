@@ -7,9 +7,9 @@
 // head) as two tiles A and B of 128 rows, and walks over the request's keys in tiles of 128:
 //     S_X = Q_X K^T     tcgen05.mma, operands from shared memory, S_X (128 x 128, 32-bit) in
 //                       tensor memory, one buffer per query tile
-//     P_X = softmax     one warpgroup per query tile, one row per thread, 32 columns at a time
-//                       in two passes (maximum, then exponentials); P_X goes back into the
-//                       first 64 columns of S_X as bf16 pairs
+//     P_X = softmax     one warpgroup per query tile, one row per thread (tcgen05.ld of the
+//                       row, running maximum and sum in 32-bit); P_X goes back into the first
+//                       64 columns of S_X as bf16 pairs
 //     O_X += P_X V      tcgen05.mma with A from tensor memory, V as it lies in the pages
 // The single MMA-issuing thread alternates between the tiles, S_A(0) S_B(0) | PV_A(0) S_A(1)
 // | PV_B(0) S_B(1) | PV_A(1) ..., so while one warpgroup computes exponentials the tensor
@@ -17,8 +17,10 @@
 // for twice the rows.  Tensor memory: S_A, S_B, O_A, O_B = 512 columns.  Shared memory: Q 64 KB,
 // two stages of K and of V, 32 KB each.
 // Warps 0-3 softmax and epilogue of tile A, 4-7 of tile B (warp w owns TMEM lanes
-// 32 (w mod 4) ...), warp 8 issues the TMA boxes, warp 9 allocates tensor memory and issues
-// every MMA from one thread.  All waits are bounded; tensor memory is freed on every path.
+// 32 (w mod 4) ...; a thread holds its whole row of S in registers, which the third warpgroup
+// cedes to these two with setmaxnreg), warp 8 issues the TMA boxes, warp 9 allocates tensor
+// memory and issues every MMA from one thread, warps 10 and 11 only fill the third warpgroup.
+// All waits are bounded; tensor memory is freed on every path.
 #pragma once
 #include "attention_flash_tc.cuh"
 
@@ -29,7 +31,8 @@ namespace tc2 {
 using namespace atom::flash::tc;
 
 constexpr int ROWS2 = 2 * TM;                 // packed query rows per CTA
-constexpr int NTHREADS2 = 256 + 64;           // two softmax warpgroups, the loader warp, the MMA warp
+constexpr int NTHREADS2 = 384;                // two softmax warpgroups and a third with the loader warp and the MMA warp
+constexpr int SOFTMAX_REGS = 224, OTHER_REGS = 56;   // registers per thread after the warpgroups have traded them
 constexpr int LOAD_WARP = 8, MMA_WARP2 = 9;
 constexpr int KV_STAGES = 2;
 constexpr uint32_t SA_COL = 0, SB_COL = 128, OA_COL = 256, OB_COL = 384;
@@ -114,8 +117,11 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* aborted = &bars->aborted;
-
-  if (warp == LOAD_WARP) {
+  // The softmax threads hold a whole row of S (128 values) in registers: the third warpgroup gives
+  // up registers it does not need and the softmax warpgroups take them.
+  if (warp >= 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(OTHER_REGS));
+   if (warp == LOAD_WARP) {
     // ------------------------------------------------------------------ loader: TMA boxes
     // A tile of 128 keys is 128 / page_size pages (or part of one page when pages are larger);
     // every page gives two boxes, one per 64-element half of the head.  Lane l issues box l.
@@ -223,8 +229,10 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
         }
       }
     }
+   }
   } else {
     // ------------------------------------------------------------------ softmax and epilogue of tile x
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(SOFTMAX_REGS));
     const int x = warp >> 2;
     const int r = threadIdx.x & 127;                 // row of the tile = TMEM lane
     const int R = w.row0 + x * TM + r;
@@ -240,43 +248,45 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
       tc_fence_after();
       const int key0 = j * TN;
       const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
-      // first pass: the row's maximum, 32 columns at a time, the next chunk's load in flight
-      float buf[2][32];
-      float mx4[4] = {m, -INFINITY, -INFINITY, -INFINITY};
-      tmem_ld32(scol, buf[0]);
+      // the whole row in registers: one round trip to tensor memory per tile
+      float s[TN];
 #pragma unroll
-      for (int q = 0; q < TN / 32; ++q) {
-        float* cur = buf[q & 1];
-        tmem_wait_ld();
-        if (q + 1 < TN / 32) tmem_ld32(scol + (q + 1) * 32, buf[(q + 1) & 1]);
-        if (diag) {
+      for (int q = 0; q < TN / 32; ++q) tmem_ld32(scol + q * 32, s + q * 32);
+      tmem_wait_ld();
+      if (diag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (key0 + q * 32 + i > pos) cur[i] = -INFINITY;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          mx4[0] = fmaxf(mx4[0], cur[i]);
-          mx4[1] = fmaxf(mx4[1], cur[i + 1]);
-          mx4[2] = fmaxf(mx4[2], cur[i + 2]);
-          mx4[3] = fmaxf(mx4[3], cur[i + 3]);
-        }
+        for (int i = 0; i < TN; ++i)
+          if (key0 + i > pos) s[i] = -INFINITY;
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx8[8] = {m, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < TN; i += 8) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = ex2((m - m_use) * c);
       const float mc = m_use * c;
-      tmem_ld32(scol, buf[0]);                 // first chunk of the second pass
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < TN; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[i + e] = ex2(fmaf(s[i + e], c, -mc));
+          sum4[e] += s[i + e];
+        }
+      }
       // O of the tile before: its MMA was issued before this tile's S, so it is complete by now; the
       // wait only makes that visible to this thread.
       if (j > 0) {
         mbar_wait(&bars->o_full[x], (j - 1) & 1, aborted, p.error);
         tc_fence_after();
         if (__any_sync(0xffffffffu, mx > m)) {      // some row of this warp has a new maximum: rescale O
-          tmem_wait_ld();
 #pragma unroll
           for (int q = 0; q < HD / 32; ++q) {
-            float* o = buf[1];
+            float o[32];
             tmem_ld32(ocol + q * 32, o);
             tmem_wait_ld();
 #pragma unroll
@@ -287,39 +297,16 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
         }
       }
       m = mx;
-      // second pass: exponentials, their sum, and P as bf16 pairs into columns 16 q .. 16 q + 15 of the
-      // same buffer (behind the columns that have been read)
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // P as bf16 pairs into the first 64 columns of the same buffer (the row has been read whole)
 #pragma unroll
-      for (int q = 0; q < TN / 32; ++q) {
-        float* cur = buf[q & 1];
-        tmem_wait_ld();
-        if (q + 1 < TN / 32) tmem_ld32(scol + (q + 1) * 32, buf[(q + 1) & 1]);
-        if (diag) {
+      for (int q = 0; q < 2; ++q) {
+        float pk[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (key0 + q * 32 + i > pos) cur[i] = -INFINITY;
+        for (int e = 0; e < 32; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[q * 64 + 2 * e], s[q * 64 + 2 * e + 1]);
+          pk[e] = __uint_as_float(*reinterpret_cast<uint32_t*>(&h));
         }
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            cur[i + e] = ex2(fmaf(cur[i + e], c, -mc));
-            sum4[e] += cur[i + e];
-          }
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(cur[2 * e], cur[2 * e + 1]);
-          pk[e] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::
-                "r"(scol + q * 16),
-            "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]), "r"(pk[8]),
-            "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]), "r"(pk[15])
-            : "memory");
+        tmem_st32(scol + q * 32, pk);
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       tmem_wait_st();
