@@ -244,8 +244,10 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
     const int n_mine = n_of[x];
     float m = -INFINITY, l = 0.f;
     for (int j = 0; j < n_mine; ++j) {
+      if (r == 0) TC_TRACE(x * 4 + 0, j);
       mbar_wait(&bars->s_full[x], j & 1, aborted, p.error);
       tc_fence_after();
+      if (r == 0) TC_TRACE(x * 4 + 1, j);
       const int key0 = j * TN;
       const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
       // the whole row in registers: one round trip to tensor memory per tile
@@ -258,16 +260,24 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
         for (int i = 0; i < TN; ++i)
           if (key0 + i > pos) s[i] = -INFINITY;
       }
-      float mx8[8] = {m, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float mx8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx8[e] = -INFINITY;
 #pragma unroll
       for (int i = 0; i < TN; i += 8) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
       }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+      const float mt = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                              fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      // The exponent's offset m follows the row maximum lazily: it moves (and O and l are rescaled)
+      // only when the maximum has outgrown it by more than 2^8, so P stays below 256 and most tiles
+      // need no pass over O.  The quotient O / l does not depend on the offset.
+      const bool grow = (mt - m) * c > 8.f || (m == -INFINITY && mt != -INFINITY);
+      const bool rescale = __any_sync(0xffffffffu, grow);
+      const float mx = rescale ? fmaxf(m, mt) : m;
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = ex2((m - m_use) * c);
+      const float alpha = ex2((m - m_use) * c);     // 1 where the offset stays (2^-inf = 0 where it was -inf: O and l are 0 there)
       const float mc = m_use * c;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -278,12 +288,13 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
           sum4[e] += s[i + e];
         }
       }
+      if (r == 0) TC_TRACE(x * 4 + 2, j);
       // O of the tile before: its MMA was issued before this tile's S, so it is complete by now; the
       // wait only makes that visible to this thread.
       if (j > 0) {
         mbar_wait(&bars->o_full[x], (j - 1) & 1, aborted, p.error);
         tc_fence_after();
-        if (__any_sync(0xffffffffu, mx > m)) {      // some row of this warp has a new maximum: rescale O
+        if (rescale) {      // some row of this warp moves its offset: rescale O
 #pragma unroll
           for (int q = 0; q < HD / 32; ++q) {
             float o[32];
@@ -312,6 +323,7 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&bars->p_full[x]);
+      if (r == 0) TC_TRACE(x * 4 + 3, j);
     }
     // epilogue: O / l -> bf16 -> global
     if (n_mine > 0) {

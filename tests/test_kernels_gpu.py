@@ -279,6 +279,11 @@ TC_CASES = [
     (8, 1, 24, [33, 64], [33, 200]),          # group 8, pages of 24 tokens
     (6, 2, 16, [129, 1, 43, 2048 // 16], [129, 1000, 300, 128]),
     (16, 4, 8, [520], [520]),                 # several key tiles, rows not a multiple of 128
+    # two query tiles per CTA (pages of 8, 16, ... tokens, a group size that divides 128):
+    (8, 1, 32, [16, 33, 64], [16, 400, 64]),  # group 8: 128, 264 and 512 packed rows; the second tile empty, 8 rows, full
+    (4, 4, 128, [129, 257], [129, 900]),      # group 1: the second tile sees one key tile more than the first; pages of 128
+    (8, 2, 16, [32, 1, 64, 96], [32, 77, 1000, 96]),   # several requests, exactly 128 / 256 / 384 rows, a long prefix
+    (2, 1, 64, [700], [1500]),                # group 2, 1400 rows, prefix of 800 keys
 ]
 
 
