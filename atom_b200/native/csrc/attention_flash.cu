@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
   // the other kernel.  Within a request the last (longest) tiles come first.
   Work w;
   {
-    int tile = blockIdx.x, s = 0, nt = 0;
+    int tile = blockIdx.y, s = 0, nt = 0;   // (blocks are handed out with x fastest: all kv heads of the longest tile first)
     for (; s < p.num_seqs; ++s) {
       const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
       nt = (rows > 16 && rows < p.long_rows) ? (rows + BM - 1) / BM : 0;
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(NT) flash_prefill_kernel(const Params p) {
     }
     if (s == p.num_seqs) return;
     w.seq = s;
-    w.kvh = blockIdx.y;
+    w.kvh = blockIdx.x;
     w.q_begin = p.cu_q[s];
     const int q_len = p.cu_q[s + 1] - w.q_begin;
     w.ctx = p.ctx_len[s];
@@ -1074,7 +1074,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   using namespace atom::flash;
   if (T <= 0 || num_seqs <= 0) return ATOM_OK;
   if (hd != HD || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || num_splits < 1 ||
-      nkv > 65535 || num_splits > 65535 || (q_stride % 8) != 0 || (num_splits > 1 && scratch == nullptr) ||
+      nkv > 65535 || num_splits > 65535 || long_tiles > 65535 || prefill_tiles > 65535 || (q_stride % 8) != 0 || (num_splits > 1 && scratch == nullptr) ||
       !(scale > 0.f))
     return ATOM_ERR_ARG;
   Params p;
@@ -1155,18 +1155,18 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
         tc2_attr = true;
       }
       // (long_tiles counts 128-row tiles: an upper bound of the 256-row tiles; the CTAs beyond them leave at once)
-      atom::launch_pdl(tc2::flash_prefill_tc2_kernel, dim3(long_tiles, nkv), dim3(tc2::NTHREADS2), tc2::smem_bytes2(),
+      atom::launch_pdl(tc2::flash_prefill_tc2_kernel, dim3(nkv, long_tiles), dim3(tc2::NTHREADS2), tc2::smem_bytes2(),
                        stream, p, long_rows, maps);
     } else if (use_tma)
-      atom::launch_pdl(tc::flash_prefill_tc_kernel<true>, dim3(long_tiles, nkv), dim3(tc::Roles<true>::NTHREADS),
+      atom::launch_pdl(tc::flash_prefill_tc_kernel<true>, dim3(nkv, long_tiles), dim3(tc::Roles<true>::NTHREADS),
                        tc::smem_bytes(), stream, p, long_rows, maps);
     else
-      atom::launch_pdl(tc::flash_prefill_tc_kernel<false>, dim3(long_tiles, nkv), dim3(tc::Roles<false>::NTHREADS),
+      atom::launch_pdl(tc::flash_prefill_tc_kernel<false>, dim3(nkv, long_tiles), dim3(tc::Roles<false>::NTHREADS),
                        tc::smem_bytes(), stream, p, long_rows, maps);
   }
 #endif
   if (prefill_tiles > 0) {
-    dim3 grid(prefill_tiles, nkv);
+    dim3 grid(nkv, prefill_tiles);
     atom::launch_pdl(flash_prefill_kernel, dim3(grid), dim3(NT), prefill_smem_bytes(), stream, p);
   }
   if (has_short) {

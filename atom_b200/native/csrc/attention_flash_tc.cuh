@@ -185,7 +185,7 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
   // belong to the other kernels.  Within a request the last (longest) tiles come first.
   Work w;
   {
-    int tile = blockIdx.x, s = 0, nt = 0;
+    int tile = blockIdx.y, s = 0, nt = 0;   // (blocks are handed out with x fastest: all kv heads of the longest tile first)
     for (; s < p.num_seqs; ++s) {
       const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
       nt = rows >= min_rows ? (rows + TM - 1) / TM : 0;
@@ -194,7 +194,7 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
     }
     if (s == p.num_seqs) return;
     w.seq = s;
-    w.kvh = blockIdx.y;
+    w.kvh = blockIdx.x;
     w.q_begin = p.cu_q[s];
     const int q_len = p.cu_q[s + 1] - w.q_begin;
     w.ctx = p.ctx_len[s];

@@ -61,7 +61,7 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
   // grid is sized for 128-row tiles, an upper bound: CTAs beyond the last tile leave at once.
   Work w;
   {
-    int tile = blockIdx.x, s = 0, nt = 0;
+    int tile = blockIdx.y, s = 0, nt = 0;   // (blocks are handed out with x fastest: all kv heads of the longest tile first)
     for (; s < p.num_seqs; ++s) {
       const int rows = (p.cu_q[s + 1] - p.cu_q[s]) * p.group;
       nt = rows >= min_rows ? (rows + ROWS2 - 1) / ROWS2 : 0;
@@ -70,7 +70,7 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
     }
     if (s == p.num_seqs) return;
     w.seq = s;
-    w.kvh = blockIdx.y;
+    w.kvh = blockIdx.x;
     w.q_begin = p.cu_q[s];
     const int q_len = p.cu_q[s + 1] - w.q_begin;
     w.ctx = p.ctx_len[s];
