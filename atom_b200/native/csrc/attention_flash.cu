@@ -1136,17 +1136,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
                 atom::tma::make_map_raw(&maps.v, v_pages, 2, d2, s2, b2) &&
                 atom::tma::make_map_raw(&maps.q, q, 3, d3, s3, b3);
     }
-    static bool tc_attr = false;
-    if (!tc_attr) {
-      if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)tc::smem_bytes()) != cudaSuccess ||
-          cudaFuncSetAttribute(tc::flash_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)tc::smem_bytes()) != cudaSuccess)
-        return ATOM_ERR_LAUNCH;
-      tc_attr = true;
-    }
-    static const bool two_tiles = [] { const char* e = getenv("ATOM_TC2"); return !(e != nullptr && e[0] == '0'); }();
-    if (use_tma && two_tiles) {
+    if (use_tma) {
       static bool tc2_attr = false;
       if (!tc2_attr) {
         if (cudaFuncSetAttribute(tc2::flash_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1157,12 +1147,17 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
       // (long_tiles counts 128-row tiles: an upper bound of the 256-row tiles; the CTAs beyond them leave at once)
       atom::launch_pdl(tc2::flash_prefill_tc2_kernel, dim3(nkv, long_tiles), dim3(tc2::NTHREADS2), tc2::smem_bytes2(),
                        stream, p, long_rows, maps);
-    } else if (use_tma)
-      atom::launch_pdl(tc::flash_prefill_tc_kernel<true>, dim3(nkv, long_tiles), dim3(tc::Roles<true>::NTHREADS),
-                       tc::smem_bytes(), stream, p, long_rows, maps);
-    else
-      atom::launch_pdl(tc::flash_prefill_tc_kernel<false>, dim3(nkv, long_tiles), dim3(tc::Roles<false>::NTHREADS),
-                       tc::smem_bytes(), stream, p, long_rows, maps);
+    } else {
+      static bool tc_attr = false;
+      if (!tc_attr) {
+        if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)tc::smem_bytes()) != cudaSuccess)
+          return ATOM_ERR_LAUNCH;
+        tc_attr = true;
+      }
+      atom::launch_pdl(tc::flash_prefill_tc_kernel, dim3(nkv, long_tiles), dim3(tc::NTHREADS), tc::smem_bytes(), stream, p,
+                       long_rows);
+    }
   }
 #endif
   if (prefill_tiles > 0) {

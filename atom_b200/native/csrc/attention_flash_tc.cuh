@@ -1,5 +1,7 @@
 // Paged causal attention for long portions on the 5th-generation tensor cores (tcgen05), head
-// size 128, bf16.  Included by attention_flash.cu (namespace atom::flash, its Params / Work).
+// size 128, bf16, for any page size and group size (where pages and query rows come as TMA boxes
+// the kernel of attention_flash_tc2.cuh runs instead; it uses the primitives defined here).
+// Included by attention_flash.cu (namespace atom::flash, its Params / Work).
 //
 // One CTA takes 128 packed query rows (row = token * G + head in group) of one (request, kv
 // head) and walks over that request's keys in tiles of 128:
@@ -30,17 +32,9 @@ using atom::tma::smem_u32;
 
 constexpr int TM = 128;          // packed query rows per CTA
 constexpr int TN = 128;          // keys per tile
-// Two ways to bring K and V (and Q) into shared memory:
-//   TMA   one warp issues tensor-map boxes, one per page and 64-element half of the head (pages of a
-//         power of two of 8 to 128 tokens, a group size that divides 128).  Measured: ~88 cycles per
-//         2 KB box with 16 issuing lanes, 23 B/clk/SM, far above what cp.async can carry.
-//   else  eight warps copy with cp.async (any page size, any group size): ~2.5 B/clk per warp.
-template <bool TMA> struct Roles {
-  static constexpr int LOADERS = TMA ? 32 : 256;            // loader threads
-  static constexpr int NTHREADS = 128 + LOADERS + 32;       // 4 softmax warps, the loaders, 1 MMA warp
-  static constexpr int MMA_WARP = (128 + LOADERS) / 32;
-  static constexpr int FULL_ARRIVALS = TMA ? 1 : LOADERS;   // arrivals that complete a K or V stage
-};
+constexpr int LOADERS = 256;                  // loader threads: eight warps copy with cp.async (~2.5 B/clk per warp)
+constexpr int NTHREADS = 128 + LOADERS + 32;  // 4 softmax warps, the loaders, 1 MMA warp
+constexpr int MMA_WARP = (128 + LOADERS) / 32;
 constexpr int BLOCK = 128 * 128; // bytes of one [128 rows][64 elements] swizzled block
 constexpr int K_STAGES = 3, V_STAGES = 2;   // K is wanted one tile ahead of V and is free again sooner
 constexpr uint32_t TMEM_COLS = 512;
@@ -158,7 +152,7 @@ __device__ __forceinline__ uint32_t sw_addr(uint32_t base, int row, int ch) {
 #endif
 
 struct Bars {
-  uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES], s_full[2], p_full, o_full, q_full;
+  uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES], s_full[2], p_full, o_full;
   uint32_t tmem_base;
   int aborted;
 };
@@ -170,11 +164,9 @@ struct Maps {
   CUtensorMap k, v, q;
 };
 
-template <bool TMA>
-__global__ void __launch_bounds__(Roles<TMA>::NTHREADS, 1)
-flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Maps maps) {
+__global__ void __launch_bounds__(NTHREADS, 1)
+flash_prefill_tc_kernel(const Params p, int min_rows) {
   static_assert(HD == 128, "the tcgen05 attention kernel is written for head size 128");
-  constexpr int LOADERS = Roles<TMA>::LOADERS, MMA_WARP = Roles<TMA>::MMA_WARP;
   atom::pdl_trigger();
   atom::pdl_wait();
   extern __shared__ unsigned char smem_raw[];
@@ -210,18 +202,17 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < K_STAGES; ++i) {
-      mbar_init(&bars->k_full[i], Roles<TMA>::FULL_ARRIVALS);
+      mbar_init(&bars->k_full[i], LOADERS);
       mbar_init(&bars->k_empty[i], 1);
     }
     for (int i = 0; i < V_STAGES; ++i) {
-      mbar_init(&bars->v_full[i], Roles<TMA>::FULL_ARRIVALS);
+      mbar_init(&bars->v_full[i], LOADERS);
       mbar_init(&bars->v_empty[i], 1);
     }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_full, 128);
     mbar_init(&bars->o_full, 1);
-    mbar_init(&bars->q_full, 1);
     bars->aborted = 0;
     mbar_fence_init();
   }
@@ -233,57 +224,7 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
   volatile int* aborted = &bars->aborted;
 
   if (warp >= 4 && warp < MMA_WARP) {
-   if constexpr (TMA) {
-    // ------------------------------------------------------------------ loader, TMA: one warp
-    // A tile of 128 keys is 128 / page_size pages (or part of one page when pages are larger);
-    // every page gives two boxes, one per 64-element half of the head.  Lane l issues box l.
-    const int ps = p.page_size;
-    const int box_rows = ps < TN ? ps : TN;
-    const int ppt = TN / box_rows;                   // pages (boxes per half) of a tile
-    const int n_ops = 2 * ppt;
-    const int my_pg = lane >> 1, my_half = lane & 1;
-    const bool active = lane < n_ops;
-    // Row of the page matrix where this lane's box of tile j starts.  Pages beyond the last key
-    // are replaced by the request's first page: finite values that the causal mask removes.
-    auto box_row = [&](int j) -> int {
-      const int key = j * TN + my_pg * box_rows;
-      int lp = p.page_shift >= 0 ? (key >> p.page_shift) : (key / ps);
-      int in_page = key - lp * ps;
-      if (key >= key_end) { lp = 0; in_page = 0; }
-      const int page = active ? __ldg(w.bt + lp) : 0;
-      return (page * p.nkv + w.kvh) * ps + in_page;
-    };
-    if (lane < 2) {   // Q: the CTA's 128 packed rows are 128 / group tokens of the group's heads
-      if (lane == 0) atom::tma::mbar_expect_tx(&bars->q_full, 2 * BLOCK);
-      __syncwarp(0x3u);
-      asm volatile(
-          "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::
-              "r"(sbase + SMEM_Q + lane * BLOCK),
-          "l"(&maps.q), "r"(lane * 64), "r"(w.kvh * p.group), "r"(w.q_begin + w.row0 / p.group), "r"(smem_u32(&bars->q_full))
-          : "memory");
-    }
-    int row_k = box_row(0), row_v = row_k;
-    const int n_groups = 2 * n_tiles;     // K0, V0, K1, V1, ...
-#pragma unroll 1
-    for (int g = 0; g < n_groups; ++g) {
-      const bool is_k = (g & 1) == 0;
-      const int j = g >> 1;
-      uint64_t* full = is_k ? &bars->k_full[j % K_STAGES] : &bars->v_full[j % V_STAGES];
-      if (is_k) {
-        if (j >= K_STAGES) mbar_wait(&bars->k_empty[j % K_STAGES], ((j / K_STAGES) & 1) ^ 1, aborted, p.error);
-      } else {
-        if (j >= V_STAGES) mbar_wait(&bars->v_empty[j % V_STAGES], ((j / V_STAGES) & 1) ^ 1, aborted, p.error);
-      }
-      if (lane == 0) atom::tma::mbar_expect_tx(full, 2 * BLOCK);
-      __syncwarp();
-      if (active) {
-        const uint32_t dst = (is_k ? sbase + SMEM_K + (j % K_STAGES) * 2 * BLOCK : sbase + SMEM_V + (j % V_STAGES) * 2 * BLOCK) +
-                             my_half * BLOCK + my_pg * box_rows * 128;
-        atom::tma::load_box(reinterpret_cast<void*>(0), is_k ? &maps.k : &maps.v, my_half * 64, is_k ? row_k : row_v, full, dst);
-      }
-      if (is_k) row_k = box_row(j + 1); else row_v = box_row(j + 1);   // looked up a tile ahead
-    }
-   } else {
+   {
     // ------------------------------------------------------------------ loaders
     constexpr int RSTEP = LOADERS / 16, RPT = 128 / RSTEP;   // a thread's rows are r0, r0 + RSTEP, ...: RPT of them
     const int t = threadIdx.x - 128;               // 0 .. LOADERS - 1
@@ -386,9 +327,6 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
         umma_commit(&bars->s_full[j & 1]);
         umma_commit(&bars->k_empty[st]);
       };
-      if constexpr (TMA) {
-        mbar_wait(&bars->q_full, 0, aborted, p.error);
-      }
       if (n_tiles > 0) issue_s(0);
       for (int j = 0; j < n_tiles; ++j) {
         if (j + 1 < n_tiles) issue_s(j + 1);
@@ -400,14 +338,10 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
         const uint32_t pa = sbase + SMEM_P, va = sbase + SMEM_V + st * 2 * BLOCK;
 #pragma unroll
         for (int ks = 0; ks < TN / 16; ++ks) {
-          // P: K-major along the keys (TMA variant: bf16 pairs in tensor memory, in the first 64 columns of the
-          // tile's S buffer); V: MN-major, 16 keys are 2048 bytes further, the second 64 of the head size one block further.
-          if constexpr (TMA)
-            umma_ts(tmem + O_COL, tmem + ((j & 1) ? S_COL1 : S_COL0) + ks * 8, smem_desc(va + ks * 2048, BLOCK, 1024),
-                    idesc_o, (j > 0 || ks > 0));
-          else
-            umma(tmem + O_COL, smem_desc(pa + (ks >> 2) * BLOCK + (ks & 3) * 32, 16, 1024),
-                 smem_desc(va + ks * 2048, BLOCK, 1024), idesc_o, (j > 0 || ks > 0));
+          // P: K-major along the keys; V: MN-major, 16 keys are 2048 bytes further, the second
+          // 64 of the head size one block further.
+          umma(tmem + O_COL, smem_desc(pa + (ks >> 2) * BLOCK + (ks & 3) * 32, 16, 1024),
+               smem_desc(va + ks * 2048, BLOCK, 1024), idesc_o, (j > 0 || ks > 0));
         }
         umma_commit(&bars->v_empty[st]);
         umma_commit(&bars->o_full);
@@ -426,76 +360,7 @@ flash_prefill_tc_kernel(const Params p, int min_rows, const __grid_constant__ Ma
       mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, aborted, p.error);
       tc_fence_after();
       if (threadIdx.x == 0) TC_TRACE(1, j);
-     if constexpr (TMA) {
-      const uint32_t scol = tmem + lane_base + ((j & 1) ? S_COL1 : S_COL0);
-      const int key0 = j * TN;
-      const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
-      // The whole row in registers (the TMA variant has few threads, so many registers each): one
-      // round trip to tensor memory per tile.
-      float s[TN];
-#pragma unroll
-      for (int q = 0; q < TN / 32; ++q) tmem_ld32(scol + q * 32, s + q * 32);
-      tmem_wait_ld();
-      if (diag) {
-#pragma unroll
-        for (int i = 0; i < TN; ++i)
-          if (key0 + i > pos) s[i] = -INFINITY;
-      }
-      float mx8[8] = {m, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int i = 0; i < TN; i += 8) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
-      }
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = ex2((m - m_use) * c);
-      const float mc = m_use * c;
-      if (threadIdx.x == 0) TC_TRACE(2, j);
-      // the exponentials do not depend on the tile before; only O and the P buffer do
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int i = 0; i < TN; i += 4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          s[i + e] = ex2(fmaf(s[i + e], c, -mc));
-          sum4[e] += s[i + e];
-        }
-      }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      if (threadIdx.x == 0) TC_TRACE(3, j);
-      if (j > 0) {
-        mbar_wait(&bars->o_full, (j - 1) & 1, aborted, p.error);
-        tc_fence_after();
-        if (threadIdx.x == 0) TC_TRACE(4, j);
-        if (__any_sync(0xffffffffu, mx > m)) {      // some row of this warp has a new maximum: rescale O
-#pragma unroll
-          for (int q = 0; q < HD / 32; ++q) {
-            float o[32];
-            tmem_ld32(tmem + lane_base + O_COL + q * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32(tmem + lane_base + O_COL + q * 32, o);
-          }
-          tmem_wait_st();
-        }
-      }
-      m = mx;
-      // P as bf16 pairs into the first 64 columns of this tile's S buffer (the row was read whole above)
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        float pk[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(s[q * 64 + 2 * e], s[q * 64 + 2 * e + 1]);
-          pk[e] = __uint_as_float(*reinterpret_cast<uint32_t*>(&h));
-        }
-        tmem_st32(scol + q * 32, pk);
-      }
-      tmem_wait_st();
-     } else {
+     {
       // Two passes over the row in tensor memory, 32 columns at a time (few live registers, the
       // next chunk's load in flight while this one is worked on): first the maximum, then P.
       const uint32_t scol = tmem + lane_base + ((j & 1) ? S_COL1 : S_COL0);
