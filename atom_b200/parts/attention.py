@@ -35,6 +35,7 @@ class PagedAttention(Mixer):
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.position = registry.build("position", position)
         self._table = None
+        self._long_rows = None    # packed rows from which a request runs on the tcgen05 kernel (0: never)
 
     def params(self) -> Dict[str, ParamSpec]:
         q, kv = self.nh * self.hd, self.nkv * self.hd
@@ -85,12 +86,16 @@ class PagedAttention(Mixer):
         bfloat16 and head sizes in steps of 16, else the 32-bit kernel that takes any size."""
         if native.flash_supports(self.hd, qkv.dtype):
             T = o.shape[0]
-            plan = step.plans.get(("flash", self.nh, self.nkv))
+            # the plan depends on the step's shape and on these sizes: layers that share them share it
+            if self._long_rows is None:
+                self._long_rows = native.LONG_ROWS if (not self.window and native.flash_has_tc(self.hd)) else 0
+            long_rows = self._long_rows
+            key = ("flash", self.nh, self.nkv, long_rows)
+            plan = step.plans.get(key)
             if plan is None:
-                long_rows = native.LONG_ROWS if (not self.window and native.flash_has_tc(self.hd)) else 0
                 plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
                                          long_rows=long_rows)
-                step.plans[("flash", self.nh, self.nkv)] = plan
+                step.plans[key] = plan
             scratch = None
             if plan[2] > 1:
                 n = native.flash_scratch_elems(T, self.nh, self.hd, plan[2])

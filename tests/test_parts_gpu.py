@@ -423,3 +423,109 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         err = np.abs(np.concatenate(got[r]) - ref[r]).max()
         assert err < 2e-4, f"{r}: max abs error {err:.2e}"
     assert runner.cache.state_slots.num_free == 4
+
+
+# ----------------------------------------------------------------------------- layers with different mixers
+
+
+def _register_hybrid():
+    from dataclasses import dataclass
+    from typing import Any, Dict
+
+    from atom_b200.config.model_config import ModelConfig
+    from atom_b200.models.registry import register_architecture, registered_architectures
+    from atom_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    if "ToyHybridLM" in registered_architectures():
+        return
+
+    @dataclass(frozen=True)
+    class HybridConfig(ModelConfig):
+        hidden_size: int = 0
+        vocab_size: int = 0
+        window: int = 0
+
+        def to_dict(self) -> Dict[str, Any]:
+            return {"architectures": [self.architecture], "hidden_size": self.hidden_size,
+                    "vocab_size": self.vocab_size, "window": self.window}
+
+    def from_dict(d):
+        return HybridConfig("ToyHybridLM", d["hidden_size"], d["vocab_size"], d["window"])
+
+    def build_spec(cfg):
+        H = cfg.hidden_size
+        pos = PartSpec("rope_neox", {"rotary_dim": 128, "theta": 10000.0, "max_position": 1024})
+        layers = []
+        for i, window in enumerate((None, cfg.window, None)):   # all keys, a window, all keys: same head counts
+            p = f"l{i}"
+            mixer = PartSpec("paged_attention",
+                             dict(hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=128, position=pos, qk_norm=False,
+                                  window=window),
+                             {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",)})
+            norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": (f"{p}.{n}",)})
+            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"),
+                                    PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 2 * H},
+                                             {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})))
+        return ModelSpec(
+            architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, max_position=1024,
+            embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": H}, {"weight": ("emb",)}),
+            layers=tuple(layers), run_order=tuple(RunEntry(i, i) for i in range(3)),
+            final_norm=PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": ("norm",)}),
+            lm_head=PartSpec("lm_head", {"vocab_size": cfg.vocab_size, "hidden_size": H, "tied": True}, {}))
+
+    register_architecture("ToyHybridLM", from_dict, build_spec)
+
+
+def _hybrid_plain(model_dir, tokens, window):
+    w = plain.read_tensors(model_dir)
+    T = len(tokens)
+    r = w["emb"][torch.as_tensor(tokens)]
+    cos, sin = plain.rope_cos_sin(torch.arange(T), 128, 10000.0)
+    for i, win in enumerate((None, window, None)):
+        p = f"l{i}"
+        a = plain.rms_norm(r, w[f"{p}.n1"], 1e-5)
+        q = (a @ w[f"{p}.q"].T).view(T, 2, 128)
+        k = (a @ w[f"{p}.k"].T).view(T, 1, 128)
+        v = (a @ w[f"{p}.v"].T).view(T, 1, 128)
+        o = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v, 128 ** -0.5, win)
+        r = r + o.reshape(T, 256) @ w[f"{p}.o"].T
+        b = plain.rms_norm(r, w[f"{p}.n2"], 1e-5)
+        r = r + plain.silu_and_mul(torch.cat((b @ w[f"{p}.gate"].T, b @ w[f"{p}.up"].T), dim=-1)) @ w[f"{p}.down"].T
+    return (plain.rms_norm(r, w["norm"], 1e-5) @ w["emb"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_beside_layers_without(tmp_path, dtype):
+    """Layers of one model choose their mixers' options one by one: all keys in layers 0 and 2, a window in
+    layer 1, with the same head counts.  The long portion runs on the tcgen05 kernel in layers 0 and 2 only
+    (a launch plan made for them must not be handed to layer 1); the windowed layer's pages are given back
+    as the window passes them (two page groups)."""
+    from atom_b200.config import EngineConfig, config_from_dict
+    from atom_b200.engine.batch import StepEntry
+    from atom_b200.engine.runner import ModelRunner
+    from atom_b200.weights import write_random_model
+
+    _register_hybrid()
+    window = 48
+    cfg = config_from_dict({"architectures": ["ToyHybridLM"], "hidden_size": 96, "vocab_size": 211, "window": window})
+    d = str(tmp_path / "hybrid")
+    write_random_model(d, cfg, seed=5)
+    runner = ModelRunner(EngineConfig(model=d, dtype=dtype, kv_cache_block_size=16, num_kvcache_blocks=40,
+                                      max_num_seqs=4, enforce_eager=True))
+    assert len(runner.cache.groups) == 2
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, 211, 230).tolist()
+    ref = _hybrid_plain(d, toks, window)
+    got, done = [], 0
+    for n in (150, 1, 70, 2, 7):            # 300 packed rows at once, then single tokens and portions
+        got.append(runner.step([StepEntry("a", toks[done:done + n], list(range(n)))]).cpu().numpy())
+        done += n
+    runner.check_status()
+    got = np.concatenate(got)
+    err = np.abs(got - ref).max()
+    scale = np.abs(ref).max()
+    assert err < (2e-4 if dtype == "float32" else 0.08 * scale), f"max abs error {err:.2e} (scale {scale:.2f})"
+    used = [g.pool.num_used for g in runner.cache.groups]
+    assert min(used) < max(used)            # the windowed group holds fewer pages than the full one
+    runner.finish("a")
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
