@@ -204,7 +204,7 @@ def main() -> int:
     t_setup = time.time()
     eng = LLMEngine("", model_config=mcfg, dtype="bfloat16", load_dummy="random", seed=WEIGHT_SEED,
                     kv_cache_block_size=PAGE, num_kvcache_blocks=pages, max_num_seqs=max(64, max_b),
-                    max_num_batched_tokens=8192, max_model_len=ctx_end + 8)
+                    max_num_batched_tokens=8192, max_model_len=max(ctx_end, PREFILL_TOKENS) + 8)
     runner = eng.runner
     rng = np.random.default_rng(8)
     sp_greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
