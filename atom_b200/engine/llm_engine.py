@@ -37,8 +37,9 @@ class _Pending:
     """A launched step: its schedule, the sampled ids on the device, their pinned host copy
     (in flight) and the event that marks the copy's end."""
 
-    def __init__(self, sched, ids, host, event):
+    def __init__(self, sched, ids, host, event, lp_host=None):
         self.sched, self.ids, self.host, self.event = sched, ids, host, event
+        self.lp_host = lp_host      # pinned copy of the tokens' log-probabilities, if some request wants them
 
 
 class LLMEngine:
@@ -113,6 +114,16 @@ class LLMEngine:
     # ------------------------------------------------------------------ requests
 
     def add_request(self, prompt: Union[str, Seq[int]], sampling_params: Optional[SamplingParams] = None) -> int:
+        """One request; returns its id.  For ``n > 1`` use ``add_request_fanout``."""
+        params = sampling_params or SamplingParams()
+        if params.n != 1:
+            raise ValueError("add_request makes one request; for SamplingParams.n > 1 call add_request_fanout")
+        return self.add_request_fanout(prompt, params)[0]
+
+    def add_request_fanout(self, prompt: Union[str, Seq[int]],
+                           sampling_params: Optional[SamplingParams] = None) -> List[int]:
+        """Tokenizes once and makes ``sampling_params.n`` sibling requests with the same prompt and
+        random streams of their own (atom/model_engine/llm_engine.py:618-720); returns their ids."""
         params = sampling_params or SamplingParams()
         if isinstance(prompt, str):
             if self.tokenizer is None:
@@ -125,17 +136,28 @@ class LLMEngine:
         V = self.runner.spec.vocab_size
         if min(ids) < 0 or max(ids) >= V:
             raise ValueError(f"prompt has a token id outside [0, {V})")
-        seq = Sequence(ids, params)
-        self._seqs[seq.seq_id] = seq
-        self.scheduler.add(seq)
-        return seq.seq_id
+        stops: List[List[int]] = []
+        if params.stop_strings:
+            if self.tokenizer is None:
+                raise ValueError("stop_strings need a tokenizer in the model folder; use stop_token_ids")
+            for text in params.stop_strings:
+                toks = self.tokenizer.encode(text, add_special_tokens=False)
+                if toks:
+                    stops.append([int(t) for t in toks])
+        out = []
+        for i in range(params.n):
+            seq = Sequence(ids, params, stop_token_sequences=stops, sibling_index=i)
+            self._seqs[seq.seq_id] = seq
+            self.scheduler.add(seq)
+            out.append(seq.seq_id)
+        return out
 
     def abort(self, seq_id: int) -> None:
         self.scheduler.abort(seq_id)
 
     def _seed_of(self, seq: Sequence) -> int:
         if seq.params.seed is not None:
-            return seq.params.seed
+            return (seq.params.seed + seq.sibling_index) & 0xFFFFFFFF
         return (self.config.seed * 0x9E3779B1 + seq.seq_id * 0x85EBCA6B + 1) & 0xFFFFFFFF
 
     # ------------------------------------------------------------------ one step
@@ -148,24 +170,36 @@ class LLMEngine:
             logits, [s.params for s in sampling], [self._seed_of(s) for s in sampling],
             [s.num_output_tokens + ahead for s in sampling])
 
-    def _read_later(self, sched: ScheduledStep, ids: torch.Tensor) -> "_Pending":
+    def _logprobs(self, logits, ids, sampling: List[Sequence]) -> Optional[torch.Tensor]:
+        """Log-probabilities of the sampled tokens (device, float32) if a request of the batch wants them."""
+        if not any(s.return_logprobs for s in sampling):
+            return None
+        return self.sampler.logprobs(logits, ids)
+
+    def _read_later(self, sched: ScheduledStep, ids: torch.Tensor, lps: Optional[torch.Tensor] = None) -> "_Pending":
         """Starts the copy of the sampled ids to pinned host memory; the host waits for it later."""
-        if self._pin_ring is None or self._pin_ring[0].numel() < ids.numel():
-            self._pin_ring = [torch.empty(max(ids.numel(), 64), dtype=torch.int32).pin_memory() for _ in range(4)]
+        if self._pin_ring is None or self._pin_ring[0].numel() < 2 * ids.numel():
+            self._pin_ring = [torch.empty(max(2 * ids.numel(), 128), dtype=torch.int32).pin_memory() for _ in range(4)]
         self._pin_next = (self._pin_next + 1) % 4      # a buffer is read two calls later at most
-        host = self._pin_ring[self._pin_next][: ids.numel()]
+        n = ids.numel()
+        host = self._pin_ring[self._pin_next][:n]
         host.copy_(ids, non_blocking=True)
+        lp_host = None
+        if lps is not None:
+            lp_host = self._pin_ring[self._pin_next][n:2 * n].view(torch.float32)
+            lp_host.copy_(lps, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        return _Pending(sched, ids, host, ev)
+        return _Pending(sched, ids, host, ev, lp_host)
 
     def _resolve(self, pending: "_Pending") -> List[Sequence]:
         """Waits for a launched step's tokens and does its bookkeeping."""
         pending.event.synchronize()
         tokens = pending.host.tolist()
-        self.d2h_bytes += 4 * len(tokens)
+        lps = pending.lp_host.tolist() if pending.lp_host is not None else None
+        self.d2h_bytes += 4 * len(tokens) * (2 if lps is not None else 1)
         self.num_generated_tokens += len(tokens)
-        return self.scheduler.postprocess(pending.sched, tokens)
+        return self.scheduler.postprocess(pending.sched, tokens, lps)
 
     def _look_ahead(self, pending: "_Pending") -> Optional["_Pending"]:
         """Launches the decode step after ``pending`` without knowing its tokens, if nothing but
@@ -196,7 +230,7 @@ class LLMEngine:
         ids = self._sample(logits, seqs, ahead=1)
         self.num_steps += 1
         self.num_overlapped += 1
-        return self._read_later(sched, ids)
+        return self._read_later(sched, ids, self._logprobs(logits, ids, seqs))
 
     def step(self) -> List[Sequence]:
         """schedule -> run the batch -> sample -> bookkeeping; returns what finished.
@@ -231,14 +265,16 @@ class LLMEngine:
         if not sampling:
             return finished + self.scheduler.postprocess(sched, [])
         ids = self._sample(logits, sampling)
+        lps = self._logprobs(logits, ids, sampling)
         pure_decode = all(e.samples and e.num_tokens == 1 for e in sched.entries)
         if self.overlap_steps and pure_decode and self.runner._graph_size(entries):
-            self._pending = self._read_later(sched, ids)
+            self._pending = self._read_later(sched, ids, lps)
             return finished
         tokens = ids.tolist()
-        self.d2h_bytes += 4 * len(tokens)
+        lp_list = lps.tolist() if lps is not None else None
+        self.d2h_bytes += 4 * len(tokens) * (2 if lps is not None else 1)
         self.num_generated_tokens += len(tokens)
-        return finished + self.scheduler.postprocess(sched, tokens)
+        return finished + self.scheduler.postprocess(sched, tokens, lp_list)
 
     # ------------------------------------------------------------------ whole requests
 
@@ -248,11 +284,11 @@ class LLMEngine:
             sampling_params = [sampling_params or SamplingParams()] * len(prompts)
         if len(sampling_params) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
-        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        ids = [i for p, sp in zip(prompts, sampling_params) for i in self.add_request_fanout(p, sp)]
         while not self.is_finished():
             self.step()
         self.runner.check_status()
-        return [self._output(self._seqs.pop(i)) for i in ids]
+        return [self._output(self._seqs.pop(i)) for i in ids]     # n outputs per prompt, in the prompts' order
 
     def _output(self, seq: Sequence) -> dict:
         out = seq.output_token_ids
@@ -262,7 +298,7 @@ class LLMEngine:
         return {
             "text": self.tokenizer.decode(out) if self.tokenizer is not None else None,
             "token_ids": out,
-            "logprobs": None,
+            "logprobs": list(seq.logprobs) if seq.return_logprobs else None,
             "latency": end - seq.arrive_time,
             "finish_reason": seq.finish_reason,
             "num_tokens_input": seq.num_prompt_tokens,

@@ -183,24 +183,36 @@ class Scheduler:
         if release and seq.seq_id in self.cache.requests:
             self.cache.release(seq.seq_id)
 
-    def postprocess(self, step: ScheduledStep, sampled: Seq[int]) -> List[Sequence]:
-        """``sampled``: one token for every entry with ``samples`` set, in order.  Advances the
-        requests, appends tokens, applies the stop rules in the reference's order: EOS unless
-        ignore_eos, stop_token_ids, max_tokens (atom/model_engine/scheduler.py:2316-2329)."""
+    def postprocess(self, step: ScheduledStep, sampled: Seq[int],
+                    logprobs: Optional[Seq[float]] = None) -> List[Sequence]:
+        """``sampled``: one token for every entry with ``samples`` set, in order (``logprobs``: their
+        log-probabilities, if some request asked for them).  Advances the requests, appends tokens,
+        applies the stop rules in the reference's order: stop sequences, EOS unless ignore_eos,
+        stop_token_ids, max_tokens (atom/model_engine/scheduler.py:2298-2329)."""
         finished = []
         it = iter(sampled)
+        lp = iter(logprobs) if logprobs is not None else None
         for e in step.entries:
             seq = e.seq
             if seq.is_finished:      # ended while this (look-ahead) step was in flight: its token is dropped
-                next(it, None) if e.samples else None
+                if e.samples:
+                    next(it, None)
+                    if lp is not None:
+                        next(lp, None)
                 continue
             seq.num_computed = e.start + e.num_tokens
             if not e.samples:
                 continue
             tok = int(next(it))
             seq.append_token(tok)
+            if lp is not None:
+                v = float(next(lp))
+                if seq.return_logprobs:
+                    seq.logprobs.append(v)
             reason = None
-            if not seq.params.ignore_eos and tok in self.eos_token_ids:
+            if any(len(st) <= seq.num_tokens and seq.token_ids[-len(st):] == st for st in seq.stop_token_sequences):
+                reason = "stop_sequence"
+            elif not seq.params.ignore_eos and tok in self.eos_token_ids:
                 reason = "eos"
             elif tok in seq.params.stop_token_ids:
                 reason = f"stop_{tok}"

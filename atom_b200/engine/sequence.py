@@ -18,7 +18,8 @@ class SequenceStatus(enum.Enum):
 class Sequence:
     _next_id = 0
 
-    def __init__(self, prompt_token_ids: List[int], params: SamplingParams, seq_id: Optional[int] = None):
+    def __init__(self, prompt_token_ids: List[int], params: SamplingParams, seq_id: Optional[int] = None,
+                 stop_token_sequences: Optional[List[List[int]]] = None, sibling_index: int = 0):
         if seq_id is None:
             seq_id = Sequence._next_id
             Sequence._next_id += 1
@@ -33,6 +34,10 @@ class Sequence:
         self.arrive_time = time.perf_counter()
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
+        self.stop_token_sequences: List[List[int]] = [list(x) for x in (stop_token_sequences or []) if x]
+        self.sibling_index = sibling_index        # which of the n completions of one prompt this is
+        self.return_logprobs = bool(params.logprobs)
+        self.logprobs: List[float] = []           # of every generated token, if asked for
 
     @property
     def num_tokens(self) -> int:

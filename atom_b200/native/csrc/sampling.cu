@@ -229,3 +229,35 @@ ATOM_EXPORT int atom_sample(int* out, const float* logits, const float* temperat
                                                  top_p, probs, V);
   return atom::check_launch();
 }
+
+
+// ------------------------------------------------------------------ log-probability of chosen tokens
+namespace atom {
+// out[r] = logits[r, ids[r]] - log sum_v exp(logits[r, v]), in 32-bit: the log-probability of
+// the sampled token under the model's distribution (as torch.log_softmax(...).gather(...) in
+// atom/model_engine/model_runner.py:3233-3240).  One block per row.
+__global__ void __launch_bounds__(512)
+token_logprob_kernel(float* __restrict__ out, const float* __restrict__ logits, const int* __restrict__ ids, int V) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  __shared__ float scratch[32];
+  const float* row = logits + (int64_t)blockIdx.x * V;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+  mx = block_max(mx, scratch);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) sum += __expf(row[i] - mx);
+  sum = block_sum(sum, scratch);
+  if (threadIdx.x == 0) {
+    const int id = ids[blockIdx.x];
+    out[blockIdx.x] = (id >= 0 && id < V) ? row[id] - mx - __logf(sum) : -INFINITY;
+  }
+}
+}  // namespace atom
+
+ATOM_EXPORT int atom_token_logprob(float* out, const float* logits, const int* ids, int R, int V, cudaStream_t stream) {
+  if (R <= 0) return ATOM_OK;
+  if (V <= 0) return ATOM_ERR_ARG;
+  atom::launch_pdl(atom::token_logprob_kernel, dim3(R), dim3(512), 0, stream, out, logits, ids, V);
+  return atom::check_launch();
+}

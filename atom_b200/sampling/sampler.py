@@ -14,6 +14,7 @@ from .params import SamplingParams
 _vp, _i = ctypes.c_void_p, ctypes.c_int
 native.declare("atom_sample", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp])
 native.declare("atom_sample_simple", [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp])
+native.declare("atom_token_logprob", [_vp, _vp, _vp, _i, _i, _vp])
 
 
 class Sampler:
@@ -83,4 +84,14 @@ class Sampler:
             probs.data_ptr() if probs is not None else None, R, V,
             torch.cuda.current_stream().cuda_stream)
         native._check(code, "sample")
+        return out
+
+    def logprobs(self, logits: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """float32 [R]: log-probability of ids[r] under softmax(logits[r]) (the raw distribution, before
+        temperature and filters: what the reference reports, atom/model_engine/model_runner.py:3233-3240)."""
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and ids.numel() == R
+        out = torch.empty(R, dtype=torch.float32, device=self.device)
+        native._check(native.lib().atom_token_logprob(out.data_ptr(), logits.data_ptr(), ids.data_ptr(), R, V,
+                                                      native._stream()), "token_logprob")
         return out

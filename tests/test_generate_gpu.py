@@ -215,3 +215,40 @@ def test_profiler_hook_writes_a_trace(model_dirs, tmp_path):
         names = [e["name"] for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
     assert any("rmsnorm" in n for n in names) and any("embedding" in n for n in names)
     assert eng.stop_profile() is None            # nothing running any more
+
+
+def test_n_completions_logprobs_and_stop_sequences(model_dirs):
+    """n sibling requests of one prompt sample from random streams of their own (seed + i); the
+    log-probability reported for a token is log softmax of the plain implementation's logits at
+    its place; a stop sequence of token ids ends a request with reason stop_sequence."""
+    from atom_b200 import SamplingParams
+    name = "A"
+    cfg, w = _plain(model_dirs[name])
+    prompt = tiny.prompts(name, [11], seed=5)[0]
+    eng = _engine(model_dirs[name], "float32", pages=64, page=8)
+    sp = SamplingParams(temperature=0.9, max_tokens=12, ignore_eos=True, seed=21, n=3, logprobs=True)
+    outs = eng.generate([prompt], sp)
+    assert len(outs) == 3 and len({tuple(o["token_ids"]) for o in outs}) > 1
+    for i, o in enumerate(outs):
+        ids = list(prompt)
+        assert len(o["logprobs"]) == len(o["token_ids"]) == 12
+        for j, tok in enumerate(o["token_ids"]):
+            row = plain.forward(cfg, w, ids)[-1]
+            assert tok == plain.sample_temperature(row, 0.9, 21 + i, j)
+            want = float(torch.log_softmax(row.double(), -1)[tok])
+            assert abs(o["logprobs"][j] - want) < 2e-4
+            ids.append(tok)
+    # greedy with a stop sequence taken from the greedy continuation itself
+    ref = plain.generate_greedy(cfg, w, prompt, 10)
+    sid = eng.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    eng._seqs[sid].stop_token_sequences = [ref[3:5]]
+    while not eng.is_finished():
+        eng.step()
+    seq = eng._seqs.pop(sid)
+    full = list(prompt) + ref       # (the sequence may also end at the prompt's last token and the first new one)
+    cut = next(k for k in range(1, 11) if full[len(prompt) + k - 2:len(prompt) + k] == ref[3:5])
+    assert seq.finish_reason == "stop_sequence" and seq.output_token_ids == ref[:cut]
+    with pytest.raises(ValueError):
+        eng.add_request(prompt, SamplingParams(stop_strings=["x"]))      # no tokenizer in this model folder
+    with pytest.raises(ValueError):
+        eng.add_request(prompt, SamplingParams(n=2))

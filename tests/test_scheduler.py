@@ -176,6 +176,39 @@ def test_stop_rules():
     assert s.is_finished() and cache.num_free_pages(0) == 64
 
 
+def test_stop_sequences_and_logprobs():
+    """A request ends when its tokens end with one of its stop sequences (checked before EOS, as in
+    atom/model_engine/scheduler.py:2298-2316); log-probabilities are kept for the requests that ask."""
+    s, cache = make(num_pages=64, budget=64, max_len=40, eos=(2,), max_seqs=8)
+    a = Sequence([3, 4, 5], SamplingParams(max_tokens=20, logprobs=True), seq_id=1, stop_token_sequences=[[7, 8, 9], [6]])
+    b = Sequence([3, 4, 8], SamplingParams(max_tokens=20), seq_id=2, stop_token_sequences=[[8, 9]])   # may span prompt and output
+    c = Sequence([3, 4, 5], SamplingParams(max_tokens=20), seq_id=3, stop_token_sequences=[[9, 2]])
+    for q in (a, b, c):
+        s.add(q)
+    fin = s.postprocess(_commit(cache, s.schedule()), [7, 9, 9], [-0.5, -1.0, -2.0])
+    assert [q.seq_id for q in fin] == [2] and b.finish_reason == "stop_sequence" and b.logprobs == []
+    fin = s.postprocess(_commit(cache, s.schedule()), [8, 2], [-0.25, -3.0])
+    assert [q.seq_id for q in fin] == [3] and c.finish_reason == "stop_sequence"      # not "eos": sequences come first
+    fin = s.postprocess(_commit(cache, s.schedule()), [9], [-0.125])
+    assert [q.seq_id for q in fin] == [1] and a.finish_reason == "stop_sequence"
+    assert a.output_token_ids == [7, 8, 9] and a.logprobs == [-0.5, -0.25, -0.125]
+    assert s.is_finished() and cache.num_free_pages(0) == 64
+
+
+def _commit(cache, step):
+    for e in step.entries:
+        cache.commit(e.seq.seq_id, e.start + e.num_tokens)
+    return step
+
+
+def test_sampling_params_checks():
+    with pytest.raises(ValueError):
+        SamplingParams(n=0)
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    assert SamplingParams(stop_strings="x").stop_strings == ["x"]
+
+
 def test_abort_frees_pages():
     s, cache = make()
     a = seq(9, sid=1)
