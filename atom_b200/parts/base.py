@@ -27,11 +27,16 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple, torch.Tensor] = {}    # (tag, dtype, shape) -> the view handed out last time
         self.frozen = False  # set while a CUDA graph holds pointers into the buffers
 
     def get(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A view of the buffer ``tag``.  zero: the buffer is zero when it is first made (or
         made larger); its users keep it so."""
+        vkey = (tag, dtype, shape)
+        v = self._views.get(vkey)
+        if v is not None:
+            return v
         n = 1
         for s in shape:
             n *= s
@@ -43,7 +48,14 @@ class Workspace:
             make = torch.zeros if zero else torch.empty
             buf = make(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:n].view(shape)
+            # views of the old buffer are stale
+            for k in [k for k in self._views if k[0] == tag and k[1] == dtype]:
+                del self._views[k]
+        v = buf[:n].view(shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = v
+        return v
 
 
 @dataclass
