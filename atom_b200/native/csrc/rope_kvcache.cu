@@ -289,75 +289,99 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
   }
   // norm weights of this lane's elements, packed as they are used: (first half, second half) per kind
   float wq[16], wk[16];
+  // (eight consecutive weights are one or two 16-byte loads; the vectors are 16-byte aligned: checked by the launcher)
+  auto load8 = [&](const void* w, int first, float* out) {
+    if (w == nullptr) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    wq[j] = q_w ? load_as_float(q_w, w_dtype, 8 * l + j) : 1.f;
-    wq[8 + j] = q_w ? load_as_float(q_w, w_dtype, HD / 2 + 8 * l + j) : 1.f;
-    wk[j] = k_w ? load_as_float(k_w, w_dtype, 8 * l + j) : 1.f;
-    wk[8 + j] = k_w ? load_as_float(k_w, w_dtype, HD / 2 + 8 * l + j) : 1.f;
-  }
+      for (int j = 0; j < 8; ++j) out[j] = 1.f;
+    } else if (w_dtype == ATOM_F32) {
+      const float4 u = *reinterpret_cast<const float4*>((const float*)w + first);
+      const float4 v = *reinterpret_cast<const float4*>((const float*)w + first + 4);
+      out[0] = u.x, out[1] = u.y, out[2] = u.z, out[3] = u.w, out[4] = v.x, out[5] = v.y, out[6] = v.z, out[7] = v.w;
+    } else {
+      const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + first);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        out[2 * j] = f.x, out[2 * j + 1] = f.y;
+      }
+    }
+  };
+  load8(q_w, 8 * l, wq);
+  load8(q_w, HD / 2 + 8 * l, wq + 8);
+  load8(k_w, 8 * l, wk);
+  load8(k_w, HD / 2 + 8 * l, wk + 8);
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
   const int stride = gridDim.y * warps * HPW;
   // every lane of a warp runs the same number of rounds (the shuffles below need all lanes)
   const int warp_head0 = (blockIdx.y * warps + (threadIdx.x >> 5)) * HPW;
-  for (int hbase = warp_head0; hbase < head_end; hbase += stride) {
-    const int head = hbase + sub;
-    const bool live = head < head_end;
-    const bool is_q = head < nh;
-    const bool is_k = !is_q && head < nh + nkv;
-    const bool act = live && (is_q || kv_row >= 0);
-    __nv_bfloat16* x = qkv + ((int64_t)t * n_heads_total + (live ? head : 0)) * HD;
-    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-    if (act) {
-      lo = *reinterpret_cast<const uint4*>(x + 8 * l);
-      hi = *reinterpret_cast<const uint4*>(x + HD / 2 + 8 * l);
-    }
-    __nv_bfloat16* dst = x;
-    if (act && !is_q) {
-      const int kvh = is_k ? head - nh : head - nh - nkv;
-      dst = (is_k ? k_pages : v_pages) + (kv_row + (int64_t)kvh * page_size) * HD;
-    }
-    float a[8], b[8];
-    {
-      const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+  // Three rounds at a time: their loads are all asked for before the first is used, so that enough
+  // bytes are in flight per SM.
+  constexpr int UNROLL = 3;
+  for (int hbase = warp_head0; hbase < head_end; hbase += UNROLL * stride) {
+    uint4 lo[UNROLL], hi[UNROLL];
+    __nv_bfloat16* dst[UNROLL];
+    int kind[UNROLL];   // 0 q, 1 k, 2 v, -1 nothing to do
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = __bfloat1622float2(l2[j]), fb = __bfloat1622float2(h2[j]);
-        a[2 * j] = fa.x, a[2 * j + 1] = fa.y, b[2 * j] = fb.x, b[2 * j + 1] = fb.y;
+    for (int u = 0; u < UNROLL; ++u) {
+      const int head = hbase + u * stride + sub;
+      kind[u] = head >= head_end ? -1 : (head < nh ? 0 : (head < nh + nkv ? 1 : 2));
+      if (kind[u] > 0 && kv_row < 0) kind[u] = -1;        // no page for this token (reported above)
+      lo[u] = hi[u] = make_uint4(0, 0, 0, 0);
+      dst[u] = nullptr;
+      if (kind[u] < 0) continue;
+      __nv_bfloat16* x = qkv + ((int64_t)t * n_heads_total + head) * HD;
+      lo[u] = *reinterpret_cast<const uint4*>(x + 8 * l);
+      hi[u] = *reinterpret_cast<const uint4*>(x + HD / 2 + 8 * l);
+      dst[u] = x;
+      if (kind[u] > 0) {
+        const int kvh = kind[u] == 1 ? head - nh : head - nh - nkv;
+        dst[u] = (kind[u] == 1 ? k_pages : v_pages) + (kv_row + (int64_t)kvh * page_size) * HD;
       }
     }
-    float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+    for (int u = 0; u < UNROLL; ++u) {
+      float a[8], b[8];
+      {
+        const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo[u]);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi[u]);
 #pragma unroll
-    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (!act) continue;
-    if (is_q || is_k) {
-      const void* w = is_q ? q_w : k_w;
-      const float rstd = w != nullptr ? rsqrtf(ss / (float)HD + eps) : 1.f;
-      uint4 olo, ohi;
-      __nv_bfloat162* ol2 = reinterpret_cast<__nv_bfloat162*>(&olo);
-      __nv_bfloat162* oh2 = reinterpret_cast<__nv_bfloat162*>(&ohi);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float y1[2], y2[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int i = 2 * j + e;
-          const float x1 = a[i] * rstd * (is_q ? wq[i] : wk[i]);
-          const float x2 = b[i] * rstd * (is_q ? wq[8 + i] : wk[8 + i]);
-          y1[e] = x1 * cs[i] - x2 * sn[i];
-          y2[e] = x2 * cs[i] + x1 * sn[i];
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = __bfloat1622float2(l2[j]), fb = __bfloat1622float2(h2[j]);
+          a[2 * j] = fa.x, a[2 * j + 1] = fa.y, b[2 * j] = fb.x, b[2 * j + 1] = fb.y;
         }
-        ol2[j] = __floats2bfloat162_rn(y1[0], y1[1]);
-        oh2[j] = __floats2bfloat162_rn(y2[0], y2[1]);
       }
-      lo = olo;
-      hi = ohi;
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // (every lane, whatever its head)
+      if (kind[u] < 0) continue;
+      if (kind[u] < 2) {
+        const bool is_q = kind[u] == 0;
+        const void* w = is_q ? q_w : k_w;
+        const float rstd = w != nullptr ? rsqrtf(ss / (float)HD + eps) : 1.f;
+        __nv_bfloat162* ol2 = reinterpret_cast<__nv_bfloat162*>(&lo[u]);
+        __nv_bfloat162* oh2 = reinterpret_cast<__nv_bfloat162*>(&hi[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float y1[2], y2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = 2 * j + e;
+            const float x1 = a[i] * rstd * (is_q ? wq[i] : wk[i]);
+            const float x2 = b[i] * rstd * (is_q ? wq[8 + i] : wk[8 + i]);
+            y1[e] = x1 * cs[i] - x2 * sn[i];
+            y2[e] = x2 * cs[i] + x1 * sn[i];
+          }
+          ol2[j] = __floats2bfloat162_rn(y1[0], y1[1]);
+          oh2[j] = __floats2bfloat162_rn(y2[0], y2[1]);
+        }
+      }
+      *reinterpret_cast<uint4*>(dst[u] + 8 * l) = lo[u];
+      *reinterpret_cast<uint4*>(dst[u] + HD / 2 + 8 * l) = hi[u];
     }
-    *reinterpret_cast<uint4*>(dst + 8 * l) = lo;
-    *reinterpret_cast<uint4*>(dst + HD / 2 + 8 * l) = hi;
   }
 }
 
@@ -390,7 +414,8 @@ ATOM_EXPORT int atom_qknorm_rope_kvwrite(void* qkv, int dtype, int T, int nh, in
              (uintptr_t)cos_sin % 8 == 0) {
     // (with few tokens the kernel below, a warp per head, is done sooner: measured 2.8 against 3.8 us at 8 tokens)
     const bool vec_ok = T >= 128 && rotary_dim == hd && (hd == 64 || hd == 128 || hd == 256) && (uintptr_t)qkv % 16 == 0 &&
-                        (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 && (uintptr_t)cos_sin % 16 == 0;
+                        (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 && (uintptr_t)cos_sin % 16 == 0 &&
+                        (uintptr_t)q_w % 16 == 0 && (uintptr_t)k_w % 16 == 0;
     if (vec_ok) {
       // a warp takes 32 / (hd / 16) heads at a time; few tokens: one round per warp; many: about 2048 blocks
       const int hpw = 32 / (hd / 16);
