@@ -1,0 +1,27 @@
+"""The host side of the attention kernels' launch plan (no GPU): which requests go to which
+kernel, and how many splits the short ones get."""
+from atom_b200 import native
+
+SMS = 148
+
+
+def test_requests_are_sorted_to_their_kernels():
+    # group 4: 1 token = 4 packed rows (short), 5 tokens = 20 rows (mid: one 64-row tile), 200 tokens = 800 rows
+    tiles, short, splits = native.flash_plan([1, 5, 200, 4, 0], 4, 8, 4096, sms=SMS)
+    assert short and tiles == 1 + 13                       # 20 rows -> 1 tile, 800 rows -> 13 tiles; 16 rows are short
+    tiles, short, splits, long_tiles = native.flash_plan([1, 5, 200, 4, 0], 4, 8, 4096, sms=SMS, long_rows=128)
+    assert short and tiles == 1 and long_tiles == 7        # 800 rows -> 7 tiles of 128 on the tcgen05 kernel
+    assert native.flash_plan([40, 40], 4, 8, 64, sms=SMS)[1] is False
+
+
+def test_splits_fill_one_wave_but_stay_long_enough():
+    # batch 8, 8 kv heads: 64 (request, kv head) pairs; two CTAs an SM -> 296 slots -> 4 splits
+    assert native.flash_plan([1] * 8, 4, 8, 4096, sms=SMS)[2] == 4
+    # batch 1: 8 pairs -> up to 37 splits, but no split shorter than 256 keys
+    assert native.flash_plan([1], 4, 8, 4096, sms=SMS)[2] == 16
+    assert native.flash_plan([1], 4, 8, 300, sms=SMS)[2] == 2
+    assert native.flash_plan([1], 4, 8, 100, sms=SMS)[2] == 1
+    # batch 64: more pairs than slots: more splits only where they fill whole waves much better
+    assert native.flash_plan([1] * 64, 4, 8, 4096, sms=SMS)[2] == 1
+    assert 1 <= native.flash_plan([1] * 40, 4, 8, 4096, sms=SMS)[2] <= 8
+    assert native.flash_plan([1] * 8, 4, 8, 1 << 20, sms=SMS)[2] <= 64
