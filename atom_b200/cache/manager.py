@@ -14,6 +14,14 @@ Accounting per request, in tokens:
 After the reference's BlockManager (atom/model_engine/block_manager.py: can_allocate :371,
 allocate :447, can_append :1109, may_append :1117, deallocate :1083), reshaped so that a
 step may hold prompt portions and decoded tokens together.
+
+Prefix caching (optional; the reference's chained block hashes, block_manager.py:181-187,
+371-445, 558-666): a full page is published, once the step that filled it has run, under a
+key that stands for all tokens from the request's first up to the page's last.  A new request
+whose tokens begin the same way takes such pages as one more holder instead of computing
+them (claim_prefix), all but its last token at most, so that there is always something to
+compute.  Pages that nobody holds keep their content until the pool needs them (page_pool).
+Only for models with one group of pages that keeps all keys and no per-request state.
 """
 from __future__ import annotations
 
@@ -44,14 +52,23 @@ class RequestCache:
     committed: int = 0               # tokens whose keys/values are in the cache
     reserved: int = 0                # positions [0, reserved) have pages (where still needed)
     tables: Dict[int, List[int]] = field(default_factory=dict)   # group -> page id per logical page
+    published: int = 0               # leading pages that answer to a prefix key (claimed or published by this request)
+    chain: Optional[int] = None      # key of the last of them
 
 
 class CacheManager:
-    def __init__(self, needs: Dict[int, CacheNeed], page_size: int, num_pages, max_requests: int):
+    def __init__(self, needs: Dict[int, CacheNeed], page_size: int, num_pages, max_requests: int,
+                 prefix_caching: bool = False):
         """needs: cache slot -> CacheNeed.  num_pages: int (every group) or {group key: int}."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
+        self.prefix_caching = prefix_caching
+        self._chains: Dict[Tuple, int] = {}      # (key of the pages before, the page's tokens) -> key
+        self._chain_of: Dict[int, Tuple] = {}    # key -> that pair, to forget it when its page is given up
+        self._next_key = 0
+        self.prefix_hit_tokens = 0               # tokens that requests did not have to compute
+        self.prefix_query_tokens = 0             # tokens of the requests that were looked up
         self.groups: List[CacheGroup] = []
         self.slot_group: Dict[int, int] = {}
         self.state_needs: Dict[int, CacheNeed] = {}
@@ -77,6 +94,9 @@ class CacheManager:
             self.slot_group[slot] = g.index
         self.state_slots = StateSlots(max_requests)
         self.requests: Dict[Hashable, RequestCache] = {}
+        if prefix_caching and (len(self.groups) != 1 or self.groups[0].window is not None or self.state_needs):
+            raise ValueError("prefix caching needs a model whose layers all keep all keys in pages of one kind "
+                             "and no per-request state")
 
     # ------------------------------------------------------------------ queries
 
@@ -191,6 +211,67 @@ class CacheManager:
             g.pool.free(reversed(held), (rid, g.index))
         self.state_slots.free(rc.state_slot)
 
+    # ------------------------------------------------------------------ prefix caching
+
+    def _key(self, parent: Optional[int], tokens: Tuple[int, ...], make: bool) -> Optional[int]:
+        pair = (parent, tokens)
+        k = self._chains.get(pair)
+        if k is None and make:
+            k = self._next_key
+            self._next_key += 1
+            self._chains[pair] = k
+            self._chain_of[k] = pair
+        return k
+
+    def claim_prefix(self, rid: Hashable, tokens) -> int:
+        """For a request that has just been admitted: takes the published pages that hold the
+        beginning of ``tokens`` (all but the last token at most) and returns how many tokens they
+        cover; the request continues behind them."""
+        if not self.prefix_caching:
+            return 0
+        rc = self.requests[rid]
+        if rc.committed or rc.tables[0]:
+            raise RuntimeError(f"request {rid!r} already holds pages")
+        pool, ps = self.groups[0].pool, self.page_size
+        self.prefix_query_tokens += len(tokens)
+        parent, n = None, 0
+        while (n + 1) * ps <= len(tokens) - 1:
+            key = self._key(parent, tuple(tokens[n * ps:(n + 1) * ps]), make=False)
+            page = pool.lookup(key) if key is not None else None
+            if page is None:
+                break
+            pool.share(page, (rid, 0))
+            rc.tables[0].append(page)
+            parent = key
+            n += 1
+        rc.published, rc.chain = n, parent
+        rc.committed = rc.reserved = n * ps
+        self.prefix_hit_tokens += n * ps
+        return n * ps
+
+    def publish(self, rid: Hashable, tokens) -> None:
+        """After a step: the request's pages that are full of committed tokens become findable.
+        ``tokens``: the request's tokens from its first one (at least the committed ones)."""
+        if not self.prefix_caching or rid not in self.requests:
+            return
+        rc = self.requests[rid]
+        pool, ps = self.groups[0].pool, self.page_size
+        while (rc.published + 1) * ps <= rc.committed:
+            i = rc.published
+            key = self._key(rc.chain, tuple(tokens[i * ps:(i + 1) * ps]), make=True)
+            pool.publish(rc.tables[0][i], key)     # (no effect if another page already answers to the key)
+            rc.chain = key
+            rc.published += 1
+        self._forget_dead_keys()
+
+    def _forget_dead_keys(self) -> None:
+        """Keys whose page was given up are of no use; dropped in bulk now and then."""
+        pool = self.groups[0].pool
+        if len(self._chain_of) <= 2 * pool.num_pages + 1024:
+            return
+        for k in [k for k in self._chain_of if pool.lookup(k) is None]:
+            del self._chains[self._chain_of.pop(k)]
+
     # ------------------------------------------------------------------ views
 
     def table(self, rid: Hashable, group: int) -> List[int]:
@@ -212,10 +293,17 @@ class CacheManager:
                 for p in rc.tables[g.index]:
                     if p == NO_PAGE:
                         continue
-                    if p in seen:
+                    if p in seen and not self.prefix_caching:
                         raise AssertionError(f"page {p} of group {g.index} is in two tables")
                     seen.add(p)
-                    if g.pool.owner_of(p) != (rid, g.index):
+                    if (rid, g.index) not in g.pool.holders_of(p):
                         raise AssertionError(f"page {p} of group {g.index}: owner mismatch")
+                if len(set(q for q in rc.tables[g.index] if q != NO_PAGE)) != sum(q != NO_PAGE for q in rc.tables[g.index]):
+                    raise AssertionError(f"request {rid!r} holds a page of group {g.index} twice")
+            if self.prefix_caching:
+                held = sum(len(g.pool.holders_of(p)) for p in seen)
+                in_tables = sum(sum(q != NO_PAGE for q in rc.tables[g.index]) for rc in self.requests.values())
+                if held != in_tables:
+                    raise AssertionError(f"group {g.index}: {held} holdings, {in_tables} table entries")
             if len(seen) != g.pool.num_used:
                 raise AssertionError(f"group {g.index}: {g.pool.num_used} pages held, {len(seen)} in tables")

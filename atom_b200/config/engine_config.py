@@ -23,6 +23,7 @@ class EngineConfig:
     cudagraph_capture_sizes: List[int] = field(default_factory=lambda: [1, 2, 4, 8, 16, 32, 48, 64])
     long_prefill_token_threshold: int = 0  # cap on one request's portion per step (0: none)
     enable_chunked_prefill: bool = True
+    enable_prefix_caching: bool = False   # requests that begin like earlier ones take their pages (the reference's default is on)
     load_dummy: Optional[str] = None      # "random": seeded random weights instead of the file
     seed: int = 0
     torch_profiler_dir: Optional[str] = None   # where start_profile / stop_profile write their traces

@@ -3,7 +3,7 @@ has them (atom/model_engine/arg_utils.py:90-542): --model :93, --enforce-eager :
 --kv_cache_dtype :163, --block-size :180, --max-model-len :183, --cudagraph-capture-sizes :189,
 --load_dummy :209, --max-num-batched-tokens :331, --long-prefill-token-threshold :337,
 --enable_chunked_prefill :373, --max-num-seqs :380, --gpu-memory-utilization :386,
---torch-profiler-dir :233.
+--torch-profiler-dir :233, --enable_prefix_caching :150 (off by default here).
 Added: --dtype, --seed, --num-kvcache-blocks.  Options for several GPUs, servers,
 quantization and speculative decoding are not taken."""
 from __future__ import annotations
@@ -27,6 +27,7 @@ class EngineArgs:
     max_num_batched_tokens: int = 16384
     long_prefill_token_threshold: int = 0
     enable_chunked_prefill: bool = True
+    enable_prefix_caching: bool = False
     max_num_seqs: int = 512
     gpu_memory_utilization: float = 0.9
     num_kvcache_blocks: int = -1
@@ -54,6 +55,8 @@ class EngineArgs:
                             help="Cap on the tokens of one prompt scheduled in one step (0: none).")
         parser.add_argument("--enable_chunked_prefill", action=argparse.BooleanOptionalAction, default=True,
                             help="Cut prompts into portions under the token budget.")
+        parser.add_argument("--enable_prefix_caching", action=argparse.BooleanOptionalAction, default=False,
+                            help="Requests that begin like earlier ones reuse their cache pages.")
         parser.add_argument("--max-num-seqs", type=int, default=512, help="Maximum number of running requests.")
         parser.add_argument("--gpu-memory-utilization", type=float, default=0.9,
                             help="Share of device memory the engine may use.")
@@ -77,7 +80,8 @@ class EngineArgs:
             max_model_len=self.max_model_len, cudagraph_capture_sizes=sizes, load_dummy=self.load_dummy,
             max_num_batched_tokens=self.max_num_batched_tokens,
             long_prefill_token_threshold=self.long_prefill_token_threshold,
-            enable_chunked_prefill=self.enable_chunked_prefill, max_num_seqs=self.max_num_seqs,
+            enable_chunked_prefill=self.enable_chunked_prefill, enable_prefix_caching=self.enable_prefix_caching,
+            max_num_seqs=self.max_num_seqs,
             gpu_memory_utilization=self.gpu_memory_utilization, num_kvcache_blocks=self.num_kvcache_blocks,
             seed=self.seed, torch_profiler_dir=self.torch_profiler_dir,
         )

@@ -320,4 +320,6 @@ class LLMEngine:
             "generation_tokens": self.num_generated_tokens,
             "kv_pages_total": [g.pool.num_pages for g in c.groups],
             "kv_pages_free": [g.pool.num_free for g in c.groups],
+            "prefix_cache_hit_tokens": c.prefix_hit_tokens,
+            "prefix_cache_query_tokens": c.prefix_query_tokens,
         }

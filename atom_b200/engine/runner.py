@@ -63,7 +63,8 @@ class ModelRunner:
         num_pages = engine_config.num_kvcache_blocks
         if num_pages <= 0:
             num_pages = self._pages_from_free_memory(probe)
-        self.cache = CacheManager(needs, self.page_size, num_pages, engine_config.max_num_seqs)
+        self.cache = CacheManager(needs, self.page_size, num_pages, engine_config.max_num_seqs,
+                                  prefix_caching=engine_config.enable_prefix_caching)
         self.storage = CacheStorage(self.cache, self.dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()

@@ -160,16 +160,18 @@ class Scheduler:
                 break  # preempted in this very step: it comes back in a later one
             if not self.cache.can_admit(seq.num_tokens + 1, self.portion_cap):
                 break
-            n = min(seq.num_tokens, self.portion_cap, budget)
-            if not self.enable_chunked_prefill and n < seq.num_tokens:
+            self.cache.admit(seq.seq_id)
+            hit = self.cache.claim_prefix(seq.seq_id, seq.token_ids)   # tokens whose pages an earlier request left
+            n = min(seq.num_tokens - hit, self.portion_cap, budget)
+            if not self.enable_chunked_prefill and hit + n < seq.num_tokens:
+                self.cache.release(seq.seq_id)
                 break
             self.waiting.popleft()
-            self.cache.admit(seq.seq_id)
-            self.cache.extend(seq.seq_id, n)
+            self.cache.extend(seq.seq_id, hit + n)
             seq.status = SequenceStatus.RUNNING
-            seq.num_computed = 0
+            seq.num_computed = hit
             self.running.append(seq)
-            step.entries.append(ScheduledEntry(seq, 0, n, n == seq.num_tokens))
+            step.entries.append(ScheduledEntry(seq, hit, n, hit + n == seq.num_tokens))
             budget -= n
         return step
 
@@ -202,9 +204,11 @@ class Scheduler:
                 continue
             seq.num_computed = e.start + e.num_tokens
             if not e.samples:
+                self.cache.publish(seq.seq_id, seq.token_ids)
                 continue
             tok = int(next(it))
             seq.append_token(tok)
+            self.cache.publish(seq.seq_id, seq.token_ids)     # (before a finished request's pages are let go)
             if lp is not None:
                 v = float(next(lp))
                 if seq.return_logprobs:

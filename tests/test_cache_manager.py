@@ -149,3 +149,111 @@ def test_random_orders_keep_the_books(seed):
     m.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.groups)
     assert m.state_slots.num_free == 6
+
+
+# ----------------------------------------------------------------------------- prefix caching
+
+
+def _run(c, rid, tokens, upto):
+    """Stands in for steps that compute the request's tokens up to ``upto``."""
+    c.extend(rid, upto)
+    c.commit(rid, upto)
+    c.publish(rid, tokens)
+
+
+def test_prefix_pages_are_published_claimed_shared_and_evicted_last_released_last():
+    c = CacheManager({0: FULL}, page_size=4, num_pages=6, max_requests=4, prefix_caching=True)
+    pool = c.groups[0].pool
+    a = list(range(100, 110))                       # 10 tokens: two full pages and a half
+    c.admit("a")
+    assert c.claim_prefix("a", a) == 0
+    _run(c, "a", a, 10)
+    pa = c.table("a", 0)
+    assert [pool.key_of(p) is not None for p in pa] == [True, True, False]
+    c.release("a")
+    assert pool.num_free == 6 and pool.num_cached == 2 and pool.num_used == 0
+    c.check()
+    # b begins like a (9 tokens), c like both; a request of exactly 8 tokens may take one page only
+    b = a[:9] + [7, 8, 9]
+    c.admit("b")
+    assert c.claim_prefix("b", b) == 8 and c.table("b", 0) == pa[:2] and c.committed("b") == 8
+    c.admit("c")
+    assert c.claim_prefix("c", a[:8]) == 4 and c.table("c", 0) == pa[:1]
+    assert sorted(pool.holders_of(pa[0])) == [("b", 0), ("c", 0)]
+    c.check()
+    _run(c, "b", b, 12)                             # its third page is published under another key than a's would be
+    _run(c, "c", a[:8], 8)                          # c computes the page b already holds: not published twice
+    assert pool.key_of(c.table("c", 0)[1]) is None
+    c.release("c")
+    c.release("b")
+    c.check()
+    assert pool.num_cached == 3 and pool.num_free == 6
+    # the pool gives vacant pages first, then the cached ones, least recently released first
+    c.admit("d")
+    c.extend("d", 12)                               # 3 vacant pages
+    assert pool.num_cached == 3 and pool.num_evictions == 0
+    c.extend("d", 16)                               # the 4th evicts b's last page (released first, in reverse order)
+    assert pool.num_evictions == 1 and pool.num_cached == 2
+    c.admit("e")
+    assert c.claim_prefix("e", b) == 8              # the first two pages are still there, the third is gone
+    c.check()
+    c.release("d")
+    c.release("e")
+    c.check()
+    assert c.prefix_hit_tokens == 8 + 4 + 8
+
+
+def test_prefix_caching_is_refused_where_it_cannot_hold():
+    with pytest.raises(ValueError):
+        CacheManager({0: FULL, 1: WIN}, 4, 8, 2, prefix_caching=True)
+    with pytest.raises(ValueError):
+        CacheManager({0: FULL, 1: STATE}, 4, 8, 2, prefix_caching=True)
+    c = CacheManager({0: FULL}, 4, 8, 2)            # off: nothing is ever claimed or published
+    c.admit("a")
+    assert c.claim_prefix("a", list(range(20))) == 0
+    _run(c, "a", list(range(20)), 20)
+    assert c.groups[0].pool.key_of(c.table("a", 0)[0]) is None
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_with_shared_prefixes_keep_the_books(seed):
+    rng = random.Random(seed)
+    c = CacheManager({0: FULL}, page_size=4, num_pages=24, max_requests=5, prefix_caching=True)
+    stems = [[rng.randrange(50) for _ in range(rng.randrange(4, 30))] for _ in range(3)]
+    live, next_id = {}, 0
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.35 and len(live) < 5:
+            toks = list(rng.choice(stems))[: rng.randrange(2, 30)] + [rng.randrange(50) for _ in range(rng.randrange(0, 6))]
+            if c.can_admit(len(toks) + 1, 64):
+                rid = next_id
+                next_id += 1
+                c.admit(rid)
+                hit = c.claim_prefix(rid, toks)
+                assert hit % 4 == 0 and hit <= len(toks) - 1
+                # what was claimed holds the same tokens under the same keys
+                live[rid] = [toks, hit]
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            toks, done = live[rid]
+            if done < len(toks):
+                upto = min(len(toks), done + rng.randrange(1, 9))
+                try:
+                    c.extend(rid, upto)
+                except OutOfPages:
+                    continue
+                c.commit(rid, upto)
+                c.publish(rid, toks)
+                live[rid][1] = upto
+            else:
+                toks.append(rng.randrange(50))       # a decoded token
+        elif live:
+            rid = rng.choice(list(live))
+            c.release(rid)
+            del live[rid]
+        c.check()
+    for rid in list(live):
+        c.release(rid)
+    c.check()
+    pool = c.groups[0].pool
+    assert pool.num_used == 0 and pool.num_free == 24

@@ -252,3 +252,34 @@ def test_n_completions_logprobs_and_stop_sequences(model_dirs):
         eng.add_request(prompt, SamplingParams(stop_strings=["x"]))      # no tokenizer in this model folder
     with pytest.raises(ValueError):
         eng.add_request(prompt, SamplingParams(n=2))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_caching_changes_no_token(model_dirs, dtype):
+    """Requests that begin like earlier ones take those requests' pages instead of computing them: the
+    tokens are the same as without (32-bit: the plain implementation's), fewer prompt tokens are computed,
+    and it still holds when pages are so few that cached ones are given up and requests are preempted."""
+    from atom_b200 import SamplingParams
+    name = "B"
+    cfg, w = _plain(model_dirs[name])
+    stem = tiny.prompts(name, [45], seed=8)[0]
+    tails = tiny.prompts(name, [3, 9, 1, 17, 6], seed=9)
+    prompts = [stem[:40] + t for t in tails] + [stem[:25], stem]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    plain_eng = _engine(model_dirs[name], dtype, pages=64, page=8)
+    want = [o["token_ids"] for o in plain_eng.generate(prompts, sp)]
+    if dtype == "float32":
+        assert want == [plain.generate_greedy(cfg, w, p, 10) for p in prompts]
+    eng = _engine(model_dirs[name], dtype, pages=64, page=8, enable_prefix_caching=True)
+    first = eng.generate(prompts[:1], sp)                    # fills the cache with the stem
+    got = first + eng.generate(prompts[1:], sp)
+    assert [o["token_ids"] for o in got] == want
+    st = eng.stats()
+    assert st["prefix_cache_hit_tokens"] >= 4 * 40 and eng.num_prompt_tokens < plain_eng.num_prompt_tokens - 150
+    assert all(g.pool.num_used == 0 for g in eng.runner.cache.groups)
+    eng.runner.cache.check()
+    # few pages, several requests at once: eviction of cached pages and preemption, and the same tokens
+    small = _engine(model_dirs[name], dtype, pages=14, page=8, enable_prefix_caching=True, max_num_seqs=3)
+    again = small.generate(prompts, sp)
+    assert [o["token_ids"] for o in again] == want
+    small.runner.cache.check()

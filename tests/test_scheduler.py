@@ -209,6 +209,27 @@ def test_sampling_params_checks():
     assert SamplingParams(stop_strings="x").stop_strings == ["x"]
 
 
+def test_a_request_that_begins_like_an_earlier_one_starts_behind_its_pages():
+    cache = CacheManager({0: FULL}, 4, 32, 4, prefix_caching=True)
+    s = Scheduler(cache, 4, 64, 64, eos_token_ids=(2,))
+    a = Sequence(list(range(10, 23)), SamplingParams(max_tokens=2), seq_id=1)        # 13 tokens: three full pages
+    s.add(a)
+    while not a.is_finished:
+        run(s, cache, s.schedule())
+    assert cache.groups[0].pool.num_cached == 3
+    b = Sequence(list(range(10, 23)) + [5, 6], SamplingParams(max_tokens=2), seq_id=2)
+    c = Sequence(list(range(10, 18)), SamplingParams(max_tokens=2), seq_id=3)         # 8 tokens: one page may be taken
+    s.add(b)
+    s.add(c)
+    st = s.schedule()
+    assert [(e.seq.seq_id, e.start, e.num_tokens, e.samples) for e in st.entries] == [(2, 12, 3, True), (3, 4, 4, True)]
+    assert b.num_computed == 12 and cache.committed(2) == 12
+    run(s, cache, st)
+    while not s.is_finished():
+        run(s, cache, s.schedule())
+    assert cache.prefix_hit_tokens == 16 and cache.groups[0].pool.num_used == 0
+
+
 def test_abort_frees_pages():
     s, cache = make()
     a = seq(9, sid=1)
