@@ -22,7 +22,7 @@ class EngineArgs:
     kv_cache_dtype: str = "bf16"
     block_size: int = 16
     max_model_len: Optional[int] = None
-    cudagraph_capture_sizes: str = "[1,2,4,8,16,32,48,64]"
+    cudagraph_capture_sizes: str = "[1,2,4,8,16,24,32,48,64,96,128,192,256,384,512]"
     load_dummy: Optional[str] = None
     max_num_batched_tokens: int = 16384
     long_prefill_token_threshold: int = 0
@@ -45,7 +45,7 @@ class EngineArgs:
         parser.add_argument("--block-size", type=int, default=16, help="KV cache block size.")
         parser.add_argument("--max-model-len", type=int, default=None,
                             help="Maximum model context length, the default is max_position_embeddings.")
-        parser.add_argument("--cudagraph-capture-sizes", type=str, default="[1,2,4,8,16,32,48,64]",
+        parser.add_argument("--cudagraph-capture-sizes", type=str, default="[1,2,4,8,16,24,32,48,64,96,128,192,256,384,512]",
                             help="Sizes to capture cudagraph. Example: [1,2,4,8,16]")
         parser.add_argument("--load_dummy", nargs="?", const="random", default=None, choices=["random"],
                             help="Use seeded random weights instead of reading the checkpoint.")

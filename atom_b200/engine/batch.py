@@ -200,10 +200,13 @@ class StepBuilder:
         return pack_layout(batch, batch, batch, widths), widths
 
     def build_fixed(self, entries: Sequence[StepEntry], targets: List[int], batch: int,
-                    table_width: int) -> StepContext:
+                    table_width: int, token_rows: Optional[Sequence[int]] = None) -> StepContext:
         """Arrays of a fixed shape for ``batch`` single-token requests (the live ones first,
         padding after them), always at the same device addresses for this ``batch``.  The
-        logits of all ``batch`` rows are computed; the caller picks the wanted ones."""
+        logits of all ``batch`` rows are computed; the caller picks the wanted ones.
+
+        token_rows: the token section carries these numbers instead of the entries' tokens
+        (the caller then replaces them on the device by tokens it gathers with them)."""
         assert len(entries) <= batch and all(len(e.tokens) == 1 for e in entries)
         (layout, total), widths = self.fixed_layout(batch, table_width)
         st = self._fixed.get(batch)
@@ -213,6 +216,9 @@ class StepBuilder:
         q_lens, q_starts, slots, _ = self._fill(host, layout, entries, targets, batch, batch, widths)
         o, n = layout["logits_rows"]
         host[o:o + n] = np.arange(batch, dtype=np.int32)
+        if token_rows is not None:
+            o, _ = layout["token_ids"]
+            host[o:o + len(entries)] = np.asarray(token_rows, dtype=np.int32)
         st.push(k, total)
         self.h2d_bytes += 4 * total
         ctx = self._context(st.dev, layout, batch, batch, batch, widths, q_lens, q_starts, slots, targets)

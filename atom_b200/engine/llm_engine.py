@@ -73,9 +73,12 @@ class LLMEngine:
         self._pending: Optional[_Pending] = None
         self.overlap_steps = not self.config.enforce_eager
         self.num_overlapped = 0
+        self.last_step_tokens = (0, 0)
         self._pin_ring = None
         self._pin_next = 0
         self._profiler = None
+        # every decode graph a batch of this engine can replay, before the first request
+        self.runner.capture_graphs(min(self.config.max_num_seqs, self.config.max_num_batched_tokens))
 
     # ------------------------------------------------------------------ profiling
 
@@ -204,33 +207,41 @@ class LLMEngine:
     def _look_ahead(self, pending: "_Pending") -> Optional["_Pending"]:
         """Launches the decode step after ``pending`` without knowing its tokens, if nothing but
         one more token per running request can happen: nobody waits, the running requests are
-        exactly those of the pending step, none of them ends with the pending token for a reason
-        the host can foresee (token count, length), and their next positions have pages."""
+        exactly those of the pending step, and their next positions have pages.  A request that
+        ends with the pending token for a reason the host can foresee (token count, length) is
+        left out of the step; the others' tokens are gathered on the device."""
         sch = self.scheduler
         seqs = [e.seq for e in pending.sched.entries]
         if sch.waiting or len(seqs) != len(sch.running) or any(a is not b for a, b in zip(seqs, sch.running)):
             return None
         if len(seqs) > sch.max_num_batched_tokens:
             return None
-        entries, sched = [], ScheduledStep()
-        for e in pending.sched.entries:
+        entries, sched, rows, going = [], ScheduledStep(), [], []
+        cache, need = self.runner.cache, {}
+        for i, e in enumerate(pending.sched.entries):
             s = e.seq
             if not e.samples or e.num_tokens != 1:
                 return None
             if s.num_output_tokens + 1 >= s.params.max_tokens or s.num_tokens + 1 >= sch.max_model_len:
-                return None
+                continue                             # its last token is the pending one
             start = e.start + 1                      # position of the token the pending step produces
-            if not self.runner.cache.can_extend(s.seq_id, start + 1):
-                return None
+            for gi, n in cache.pages_to_extend(s.seq_id, start + 1).items():
+                need[gi] = need.get(gi, 0) + n
             entries.append(StepEntry(s.seq_id, [0], (0,)))
             sched.entries.append(ScheduledEntry(s, start, 1, True))
-        if not self.runner._graph_size(entries):
+            rows.append(i)
+            going.append(s)
+        if not entries or not self.runner._graph_size(entries):
             return None
-        logits = self.runner.step(entries, device_tokens=pending.ids)
-        ids = self._sample(logits, seqs, ahead=1)
+        if any(n > cache.num_free_pages(gi) for gi, n in need.items()):
+            return None
+        logits = self.runner.step(entries, device_tokens=pending.ids,
+                                  device_token_rows=rows if len(rows) < len(seqs) else None)
+        ids = self._sample(logits, going, ahead=1)
         self.num_steps += 1
         self.num_overlapped += 1
-        return self._read_later(sched, ids, self._logprobs(logits, ids, seqs))
+        self.last_step_tokens = (0, len(entries))
+        return self._read_later(sched, ids, self._logprobs(logits, ids, going))
 
     def step(self) -> List[Sequence]:
         """schedule -> run the batch -> sample -> bookkeeping; returns what finished.
@@ -261,7 +272,10 @@ class LLMEngine:
                 sampling.append(e.seq)
         logits = self.runner.step(entries)
         self.num_steps += 1
-        self.num_prompt_tokens += sum(e.num_tokens for e in sched.entries if not (e.samples and e.num_tokens == 1))
+        n_decode = sum(1 for e in sched.entries if e.samples and e.num_tokens == 1)
+        n_prompt = sum(e.num_tokens for e in sched.entries) - n_decode
+        self.num_prompt_tokens += n_prompt
+        self.last_step_tokens = (n_prompt, n_decode)      # of the step launched last: prompt tokens, decoded tokens
         if not sampling:
             return finished + self.scheduler.postprocess(sched, [])
         ids = self._sample(logits, sampling)

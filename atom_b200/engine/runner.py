@@ -142,22 +142,29 @@ class ModelRunner:
         return targets
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             device_token_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
         """Runs one batch; returns logits [R, vocab] float32 on the device, rows in the order
         of the entries and of their ``want`` lists.  The cache then holds the new tokens.
 
         device_tokens: for a batch of single-token requests whose tokens are still on the device
-        (the sampler's output of the step before, int32 [len(entries)], in the entries' order):
-        they replace the entries' token values, which are then placeholders.  The host never
-        has to see them before this step is launched."""
+        (the sampler's output of the step before, int32, in the entries' order; or, with
+        ``device_token_rows``, entry i's token at ``device_tokens[device_token_rows[i]]``, for a
+        step that some requests of the step before have left): they replace the entries' token
+        values, which are then placeholders.  The host never has to see them before this step
+        is launched."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         targets = self._reserve(entries)
         size = self._graph_size(entries)
         if device_tokens is not None:
-            if not size or device_tokens.dtype != torch.int32 or device_tokens.numel() != len(entries):
+            rows = None if device_token_rows is None else [int(r) for r in device_token_rows]
+            n_src = device_tokens.numel()
+            if not size or device_tokens.dtype != torch.int32 or (
+                    n_src != len(entries) if rows is None
+                    else len(rows) != len(entries) or any(not 0 <= r < n_src for r in rows)):
                 raise StepError("device_tokens needs a captured decode step and one int32 token per entry")
-            logits = self._step_graph(entries, targets, size, device_tokens)
+            logits = self._step_graph(entries, targets, size, device_tokens, rows)
         elif size:
             logits = self._step_graph(entries, targets, size)
         else:
@@ -187,6 +194,22 @@ class ModelRunner:
             if b >= n:
                 return b
         return 0
+
+    def capture_graphs(self, max_batch: int) -> List[int]:
+        """Captures, ahead of the first request, the decode graphs that batches of up to
+        ``max_batch`` requests replay (the reference captures all of its sizes at start,
+        atom/model_engine/model_runner.py capture_cudagraph); without this call a size is
+        captured when a step first needs it.  Returns the sizes captured now."""
+        done = []
+        if not self.graphs_enabled:
+            return done
+        for b in self._graph_sizes:
+            if b not in self._graphs:
+                self._graphs[b] = self._capture(b)
+                done.append(b)
+            if b >= max_batch:
+                break
+        return done
 
     def _capture(self, size: int) -> "_DecodeGraph":
         """Runs a decode step of ``size`` padding rows once eagerly (loads kernels, sizes the
@@ -218,13 +241,16 @@ class ModelRunner:
         return g
 
     def _step_graph(self, entries: Sequence[StepEntry], targets: List[int], size: int,
-                    device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    device_tokens: Optional[torch.Tensor] = None,
+                    device_token_rows: Optional[List[int]] = None) -> torch.Tensor:
         g = self._graphs.get(size)
         if g is None:
             g = self._graphs[size] = self._capture(size)
-        ctx = self.builder.build_fixed(entries, targets, size, self._table_width)
-        if device_tokens is not None:
-            ctx.token_ids[: len(entries)].copy_(device_tokens)     # on the stream, after the arrays' copy
+        ctx = self.builder.build_fixed(entries, targets, size, self._table_width, device_token_rows)
+        if device_tokens is not None:          # on the stream, after the arrays' copy
+            if device_token_rows is not None:
+                device_tokens = device_tokens.index_select(0, ctx.token_ids[: len(entries)])
+            ctx.token_ids[: len(entries)].copy_(device_tokens)
         g.graph.replay()
         native.add_launches(g.num_launches)
         self.graph_replays += 1

@@ -35,13 +35,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-QWEN3_8B = dict(
-    architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096,
-    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
-    vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
-    max_position_embeddings=40960, hidden_act="silu", attention_bias=False,
-)
-WEIGHT_SEED = 4
+from atom_b200.benchmarks.sizes import SIZES  # noqa: E402  (needs ROOT on the path)
+
 PREFILL_TOKENS = 2048
 PAGE = 16
 
@@ -162,6 +157,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--model", default="8b", choices=sorted(SIZES), help="layer sizes: Qwen3-8B (default), -4B or -32B")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
@@ -185,7 +181,8 @@ def main() -> int:
     from atom_b200.engine.batch import StepEntry
 
     peaks = load_peaks()
-    cfg_d = dict(QWEN3_8B)
+    cfg_d, weight_seed = SIZES[args.model]
+    cfg_d = dict(cfg_d)
     full_layers = cfg_d["num_hidden_layers"]
     n_layers = args.layers if args.layers > 0 else full_layers
     cfg_d["num_hidden_layers"] = n_layers
@@ -202,7 +199,7 @@ def main() -> int:
 
     clocks = ClockSampler(0)
     t_setup = time.time()
-    eng = LLMEngine("", model_config=mcfg, dtype="bfloat16", load_dummy="random", seed=WEIGHT_SEED,
+    eng = LLMEngine("", model_config=mcfg, dtype="bfloat16", load_dummy="random", seed=weight_seed,
                     kv_cache_block_size=PAGE, num_kvcache_blocks=pages, max_num_seqs=max(64, max_b),
                     max_num_batched_tokens=8192, max_model_len=max(ctx_end, PREFILL_TOKENS) + 8)
     runner = eng.runner
@@ -316,11 +313,11 @@ def main() -> int:
 
     clocks.stop()
     out = {
-        "metric": "decode tokens/s (Qwen3-8B sizes, bf16, 1 B200)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tokens/s (Qwen3-{args.model.upper()} sizes, bf16, 1 B200)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_main, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "Qwen3-8B sizes, random weights (seed 4)", "layers": n_layers, "layers_of_model": full_layers,
+            "model": f"Qwen3-{args.model.upper()} sizes, random weights (seed {weight_seed})", "layers": n_layers, "layers_of_model": full_layers,
             "hidden": cfg_d["hidden_size"], "heads": cfg_d["num_attention_heads"],
             "kv_heads": cfg_d["num_key_value_heads"], "head_dim": cfg_d["head_dim"],
             "intermediate": cfg_d["intermediate_size"], "vocab": V, "global_batch": args.batch,

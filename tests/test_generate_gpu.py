@@ -201,6 +201,26 @@ def test_overlapped_decode_steps_give_the_same_tokens(model_dirs, dtype):
     assert [o["token_ids"] for o in again] == [o["token_ids"] for o in outs]
 
 
+def test_overlap_goes_on_when_requests_end_at_their_token_count(model_dirs):
+    """A request whose last token is the one in flight is left out of the step launched ahead; the
+    others' tokens are gathered on the device, so the steps stay overlapped while requests end
+    one after the other."""
+    from atom_b200 import SamplingParams
+    name = "A"
+    cfg, w = _plain(model_dirs[name])
+    prompts = tiny.prompts(name, [5, 9, 2, 14, 7], seed=12)
+    lens = [9, 5, 17, 13, 5]
+    eng = _engine(model_dirs[name], "float32", pages=64, page=8, enforce_eager=False, cudagraph_capture_sizes=[1, 2, 4, 8],
+                  max_model_len=128)
+    assert sorted(eng.runner._graphs) == [1, 2, 4, 8]          # captured before the first request
+    outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in lens])
+    for p_, n, o in zip(prompts, lens, outs):
+        assert o["token_ids"] == plain.generate_greedy(cfg, w, p_, n) and o["finish_reason"] == "max_tokens"
+    assert eng.num_overlapped >= 14          # 16 decode steps; only the first is launched with nothing in flight
+    assert all(g.pool.num_used == 0 for g in eng.runner.cache.groups)
+    eng.runner.cache.check()
+
+
 def test_profiler_hook_writes_a_trace(model_dirs, tmp_path):
     """start_profile / stop_profile (the reference's names) write a chrome trace with the engine's kernels."""
     import gzip
