@@ -529,3 +529,201 @@ def test_layers_with_a_window_beside_layers_without(tmp_path, dtype):
     assert min(used) < max(used)            # the windowed group holds fewer pages than the full one
     runner.finish("a")
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
+# ----------------------------------------------------------------------------- a toy feed-forward with routing, another position encoding
+
+
+def _register_routed():
+    """Two toys for this test, plain torch on the device, nothing of them in the framework:
+
+    * a feed-forward with routing: router logits in 32-bit, the ``top_k`` largest of ``num_experts``, their
+      softmax as weights, each chosen expert a SiLU-gated feed-forward of its own:
+          y = sum_{e in top_k(x W_r^T)} softmax_e * down_e(silu(gate_e x) * up_e x)
+    * another position encoding: rotation of the first ``rotary_dim`` < head size entries of a head only, by
+      angles  (pos / stretch + shift) * theta^(-2j/rotary_dim): a stretched and shifted table.
+    The model runs the routed feed-forward in the odd layers and the dense one in the even layers."""
+    from dataclasses import dataclass
+    from typing import Any, Dict
+
+    from atom_b200.config.model_config import ModelConfig
+    from atom_b200.models.registry import register_architecture, registered_architectures
+    from atom_b200.parts import registry
+    from atom_b200.parts.base import FeedForward, PositionEncoding
+    from atom_b200.parts.spec import LayerSpec, ModelSpec, ParamSpec, PartSpec, RunEntry
+
+    if "ToyRoutedLM" in registered_architectures():
+        return
+
+    @registry.register("ffn", "toy_routed_silu")
+    class RoutedSilu(FeedForward):
+        def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int):
+            self.H, self.I, self.E, self.k = hidden_size, intermediate_size, num_experts, top_k
+
+        def params(self):
+            return {"router.weight": ParamSpec((self.E, self.H)),
+                    "gate_up.weight": ParamSpec((self.E * 2 * self.I, self.H), rows=(2 * self.I,) * self.E),
+                    "down.weight": ParamSpec((self.E * self.H, self.I), rows=(self.H,) * self.E)}
+
+        def forward(self, x, step):
+            xf = x.float()
+            logits = xf @ self.w_router_weight.float().T
+            top, idx = logits.topk(self.k, dim=-1)
+            wts = torch.softmax(top, dim=-1)
+            gu = self.w_gate_up_weight.float().view(self.E, 2 * self.I, self.H)
+            dn = self.w_down_weight.float().view(self.E, self.H, self.I)
+            y = torch.zeros_like(xf)
+            for e in range(self.E):
+                rows, slot = (idx == e).nonzero(as_tuple=True)
+                if rows.numel():
+                    h = xf[rows] @ gu[e].T
+                    h = torch.nn.functional.silu(h[:, :self.I]) * h[:, self.I:]
+                    y.index_add_(0, rows, (h @ dn[e].T) * wts[rows, slot].unsqueeze(1))
+            return y.to(self.rt.dtype)
+
+    @registry.register("position", "toy_stretched_rotary")
+    class StretchedRotary(PositionEncoding):
+        def __init__(self, rotary_dim: int, theta: float, max_position: int, stretch: float, shift: float):
+            self.rotary_dim, self.theta, self.max_position = rotary_dim, theta, max_position
+            self.stretch, self.shift = stretch, shift
+
+        def table(self, rt):
+            d = self.rotary_dim
+            inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
+            ang = torch.outer(torch.arange(self.max_position, dtype=torch.float64) / self.stretch + self.shift, inv)
+            return torch.cat([ang.cos(), ang.sin()], dim=1).float().contiguous().to(rt.device)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        d: Any = None
+
+        def to_dict(self) -> Dict[str, Any]:
+            return dict(self.d)
+
+    def from_dict(d):
+        return RoutedConfig("ToyRoutedLM", dict(d))
+
+    def build_spec(cfg):
+        c = cfg.d
+        H, hd, nh, nkv = c["hidden_size"], c["head_dim"], c["heads"], c["kv_heads"]
+        pos = PartSpec("toy_stretched_rotary", {"rotary_dim": c["rotary_dim"], "theta": c["theta"], "max_position": 256,
+                                                "stretch": c["stretch"], "shift": c["shift"]})
+        layers = []
+        for i in range(c["layers"]):
+            p = f"l{i}"
+            mixer = PartSpec("paged_attention",
+                             dict(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd, position=pos, qk_norm=True,
+                                  norm_eps=c["eps"]),
+                             {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",),
+                              "q_norm.weight": (f"{p}.qn",), "k_norm.weight": (f"{p}.kn",)})
+            if i % 2:
+                E = c["experts"]
+                ffn = PartSpec("toy_routed_silu", {"hidden_size": H, "intermediate_size": c["expert_size"],
+                                                   "num_experts": E, "top_k": c["top_k"]},
+                               {"router.weight": (f"{p}.router",),
+                                "gate_up.weight": tuple(f"{p}.e{e}.gate_up" for e in range(E)),
+                                "down.weight": tuple(f"{p}.e{e}.down" for e in range(E))})
+            else:
+                ffn = PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": c["dense_size"]},
+                               {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})
+            norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, {"weight": (f"{p}.{n}",)})
+            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"), ffn))
+        return ModelSpec(
+            architecture=cfg.architecture, hidden_size=H, vocab_size=c["vocab_size"], max_position=256,
+            embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H}, {"weight": ("emb",)}),
+            layers=tuple(layers), run_order=tuple(RunEntry(i, i) for i in range(c["layers"])),
+            final_norm=PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, {"weight": ("norm",)}),
+            lm_head=PartSpec("lm_head", {"vocab_size": c["vocab_size"], "hidden_size": H, "tied": False},
+                             {"weight": ("head",)}))
+
+    register_architecture("ToyRoutedLM", from_dict, build_spec)
+
+
+def _routed_plain(model_dir, tokens):
+    """The toy architecture written out plainly: whole sequence, float64, no cache."""
+    c = plain.read_config(model_dir)
+    w = plain.read_tensors(model_dir)
+    H, hd, nh, nkv, eps, rd = c["hidden_size"], c["head_dim"], c["heads"], c["kv_heads"], c["eps"], c["rotary_dim"]
+    T = len(tokens)
+    inv = 1.0 / (c["theta"] ** (torch.arange(0, rd, 2, dtype=torch.float64) / rd))
+    ang = torch.outer(torch.arange(T, dtype=torch.float64) / c["stretch"] + c["shift"], inv)
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+    def rotate(x):                       # the first rd entries of every head, half-split pairs; the rest untouched
+        x1, x2, rest = x[..., :rd // 2], x[..., rd // 2:rd], x[..., rd:]
+        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin, rest), dim=-1)
+
+    r = w["emb"][torch.as_tensor(tokens)]
+    for i in range(c["layers"]):
+        p = f"l{i}"
+        a = plain.rms_norm(r, w[f"{p}.n1"], eps)
+        q = plain.rms_norm((a @ w[f"{p}.q"].T).view(T, nh, hd), w[f"{p}.qn"], eps)
+        k = plain.rms_norm((a @ w[f"{p}.k"].T).view(T, nkv, hd), w[f"{p}.kn"], eps)
+        v = (a @ w[f"{p}.v"].T).view(T, nkv, hd)
+        o = plain.causal_attention(rotate(q), rotate(k), v, hd ** -0.5)
+        r = r + o.reshape(T, nh * hd) @ w[f"{p}.o"].T
+        b = plain.rms_norm(r, w[f"{p}.n2"], eps)
+        if i % 2:
+            logits = b @ w[f"{p}.router"].T
+            y = torch.zeros_like(b)
+            for t in range(T):
+                top = torch.topk(logits[t], c["top_k"])
+                wt = torch.softmax(top.values, dim=-1)
+                for j, e in enumerate(top.indices.tolist()):
+                    y[t] += wt[j] * (plain.silu_and_mul(b[t:t + 1] @ w[f"{p}.e{e}.gate_up"].T) @ w[f"{p}.e{e}.down"].T)[0]
+            r = r + y
+        else:
+            r = r + plain.silu_and_mul(torch.cat((b @ w[f"{p}.gate"].T, b @ w[f"{p}.up"].T), dim=-1)) @ w[f"{p}.down"].T
+    return (plain.rms_norm(r, w["norm"], eps) @ w["head"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    """A feed-forward with routing and a position encoding of another kind, both defined here, are registered, chosen
+    layer by layer beside the framework's dense feed-forward, loaded by tensor name (an expert's matrices are
+    checkpoint tensors of their own) and stepped in portions beside decoded tokens, without a change to the framework."""
+    from atom_b200.config import EngineConfig, config_from_dict
+    from atom_b200.engine.batch import StepEntry
+    from atom_b200.engine.runner import ModelRunner
+    from atom_b200.weights import write_random_model
+
+    _register_routed()
+    cfg = config_from_dict({"architectures": ["ToyRoutedLM"], "hidden_size": 80, "head_dim": 32, "heads": 6, "kv_heads": 3,
+                            "layers": 4, "vocab_size": 131, "eps": 1e-5, "rotary_dim": 16, "theta": 500.0, "stretch": 2.5,
+                            "shift": 0.75, "experts": 5, "top_k": 2, "expert_size": 48, "dense_size": 112})
+    d = str(tmp_path / "routed")
+    write_random_model(d, cfg, seed=33)
+    # router rows drawn like every matrix would leave the choice of experts to differences of 1e-3: scale them up
+    # so that the plain implementation and the engine choose alike also in reduced precision
+    from safetensors.torch import load_file, save_file
+    t = load_file(os.path.join(d, "model.safetensors"))
+    for k_ in t:
+        if k_.endswith(".router"):
+            t[k_] = (t[k_].float() * 40).to(t[k_].dtype)
+    save_file(t, os.path.join(d, "model.safetensors"))
+    runner = ModelRunner(EngineConfig(model=d, dtype=dtype, kv_cache_block_size=8, num_kvcache_blocks=32,
+                                      max_num_seqs=4, enforce_eager=True))
+    rng = np.random.default_rng(4)
+    seqs = {"x": rng.integers(0, 131, 50).tolist(), "y": rng.integers(0, 131, 21).tolist()}
+    ref = {r: _routed_plain(d, s) for r, s in seqs.items()}
+    got, done = {r: [] for r in seqs}, {r: 0 for r in seqs}
+    for portions in ({"x": 19}, {"x": 2, "y": 20}, {"x": 1, "y": 1}, {"x": 27}, {"x": 1}):
+        entries = [StepEntry(r, seqs[r][done[r]:done[r] + n], list(range(n))) for r, n in portions.items()]
+        logits = runner.step(entries).cpu().numpy()
+        o = 0
+        for r, n in portions.items():
+            got[r].append(logits[o:o + n])
+            o += n
+            done[r] += n
+    runner.check_status()
+    for r in seqs:
+        assert done[r] == len(seqs[r])
+        err = np.abs(np.concatenate(got[r]) - ref[r])
+        if dtype == "float32":
+            assert err.max() < 2e-4, f"{r}: max abs error {err.max():.2e}"
+        else:
+            # a token whose second and third router logits are closer than bfloat16 resolves may take another
+            # expert: all but a few rows must agree closely
+            scale = np.abs(ref[r]).max()
+            bad = (err.max(axis=1) > 0.08 * scale).sum()
+            assert bad <= 2, f"{r}: {bad} rows off (max abs error {err.max():.2e}, scale {scale:.2f})"
