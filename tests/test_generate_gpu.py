@@ -50,7 +50,7 @@ def test_greedy_generate_fp32_equals_plain(model_dirs, name, page, chunk):
     assert all(g.pool.num_used == 0 for g in eng.runner.cache.groups)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_greedy_generate_bf16_is_plain_argmax_within_rounding(model_dirs, name):
     from atom_b200 import SamplingParams
     cfg, w = _plain(model_dirs[name])
@@ -305,7 +305,8 @@ def test_prefix_caching_changes_no_token(model_dirs, dtype):
     small.runner.cache.check()
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("B", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("B", "bfloat16"), ("D", "float32"),
+                                        ("D", "bfloat16")])
 def test_random_workload_every_feature_at_once(model_dirs, name, dtype):
     """Many requests with shared beginnings, random lengths, stop tokens and a mix of greedy and seeded
     temperature sampling, through an engine with everything on (captured decode steps launched ahead,

@@ -12,7 +12,8 @@ import torch
 
 # A and B are the two acceptance configurations; C adds what Qwen3 checkpoints may carry
 # and A/B lack: sliding-window layers, projection biases, as many kv heads as heads, a head
-# size that is no power of two.
+# size that is no power of two.  D has the head size of the large models (128), so that whole
+# requests run through the kernels made for it (tensor-memory prefill, TMA decode).
 CONFIGS: Dict[str, dict] = {
     "A": dict(
         architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=64,
@@ -34,11 +35,17 @@ CONFIGS: Dict[str, dict] = {
         sliding_window=24, use_sliding_window=True,
         layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
     ),
+    "D": dict(
+        architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=192,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=320,
+        vocab_size=517, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+        max_position_embeddings=1024, hidden_act="silu", attention_bias=False,
+    ),
 }
-SEEDS = {"A": 0, "B": 2, "C": 11}
+SEEDS = {"A": 0, "B": 2, "C": 11, "D": 13}
 # Factor on the per-head q/k norm weights: sharpens the attention so that a wrong or missing
 # key changes the output visibly instead of drowning in a near-uniform average.
-QK_SHARPEN = {"A": 1.0, "B": 2.0, "C": 1.5}
+QK_SHARPEN = {"A": 1.0, "B": 2.0, "C": 1.5, "D": 1.2}
 
 
 def write_model(name: str, model_dir: str) -> None:
