@@ -244,10 +244,10 @@ __global__ void qknorm_rope_kvwrite_bf16_kernel(
 
 // bf16, full rotation (rotary_dim == hd), hd = 16 * LPH: LPH lanes share a head, each holding
 // 8 consecutive elements of the first half and the 8 they are rotated with in the second half
-// (two 16-byte accesses); a warp takes 32 / LPH heads at a time.  A block is one token; the
-// token's angles and the norm weights stay in registers over all heads a lane group serves.
+// (two 16-byte accesses); a warp takes 32 / LPH heads at a time.  A block is one token (128 threads); the
+// token's angles and the norm weights are put into shared memory once and read from there for every head.
 template <int LPH>
-__global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
+__global__ void __launch_bounds__(128, 8) qknorm_rope_kvwrite_bf16_vec_kernel(
     __nv_bfloat16* __restrict__ qkv, int nh, int nkv, const void* __restrict__ q_w,
     const void* __restrict__ k_w, int w_dtype, float eps, const float* __restrict__ cos_sin, int max_pos,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
@@ -277,41 +277,26 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
       kv_row = (int64_t)page * nkv * page_size + (pos % page_size);
     }
   }
-  // angles of this lane's 8 column pairs
-  float cs[8], sn[8];
+  // The token's angles and the norm weights wait in shared memory: held in registers over the heads
+  // they cost 48 registers a thread, and with 120 registers an SM holds 16 warps of this kernel
+  // where 64 registers let it hold 32 (2,048 tokens: 16.1 -> 13.1 us).
+  __shared__ __align__(16) float s_cs[HD];        // cos of the HD/2 pairs' angles, then sin
+  __shared__ __align__(16) float s_w[2][HD];      // q norm weights, k norm weights (ones without a norm)
   {
     const int p = pos < max_pos ? pos : max_pos - 1;  // host checks pos < max_pos
-    const float4* c4 = reinterpret_cast<const float4*>(cos_sin + (int64_t)p * HD + 8 * l);
-    const float4* s4 = reinterpret_cast<const float4*>(cos_sin + (int64_t)p * HD + HD / 2 + 8 * l);
-    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
-    cs[0] = c0.x, cs[1] = c0.y, cs[2] = c0.z, cs[3] = c0.w, cs[4] = c1.x, cs[5] = c1.y, cs[6] = c1.z, cs[7] = c1.w;
-    sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
-  }
-  // norm weights of this lane's elements, packed as they are used: (first half, second half) per kind
-  float wq[16], wk[16];
-  // (eight consecutive weights are one or two 16-byte loads; the vectors are 16-byte aligned: checked by the launcher)
-  auto load8 = [&](const void* w, int first, float* out) {
-    if (w == nullptr) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) out[j] = 1.f;
-    } else if (w_dtype == ATOM_F32) {
-      const float4 u = *reinterpret_cast<const float4*>((const float*)w + first);
-      const float4 v = *reinterpret_cast<const float4*>((const float*)w + first + 4);
-      out[0] = u.x, out[1] = u.y, out[2] = u.z, out[3] = u.w, out[4] = v.x, out[5] = v.y, out[6] = v.z, out[7] = v.w;
-    } else {
-      const uint4 q = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)w + first);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(h[j]);
-        out[2 * j] = f.x, out[2 * j + 1] = f.y;
-      }
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+      s_cs[i] = cos_sin[(int64_t)p * HD + i];
+      s_w[0][i] = q_w != nullptr ? load_as_float(q_w, w_dtype, i) : 1.f;
+      s_w[1][i] = k_w != nullptr ? load_as_float(k_w, w_dtype, i) : 1.f;
     }
+  }
+  __syncthreads();
+  // (read again for every head: "volatile" keeps the compiler from lifting the loads out of the loop)
+  auto lds4 = [](const float* ptr, float* out) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=f"(out[0]), "=f"(out[1]), "=f"(out[2]), "=f"(out[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(ptr)));
   };
-  load8(q_w, 8 * l, wq);
-  load8(q_w, HD / 2 + 8 * l, wq + 8);
-  load8(k_w, 8 * l, wk);
-  load8(k_w, HD / 2 + 8 * l, wk + 8);
   atom::pdl_wait();      // inputs written by the kernel before this one are visible from here on
   const int stride = gridDim.y * warps * HPW;
   // every lane of a warp runs the same number of rounds (the shuffles below need all lanes)
@@ -365,18 +350,25 @@ __global__ void qknorm_rope_kvwrite_bf16_vec_kernel(
         __nv_bfloat162* ol2 = reinterpret_cast<__nv_bfloat162*>(&lo[u]);
         __nv_bfloat162* oh2 = reinterpret_cast<__nv_bfloat162*>(&hi[u]);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float y1[2], y2[2];
+        for (int j = 0; j < 2; ++j) {   // four column pairs at a time
+          float c4[4], s4[4], w1[4], w2[4];
+          lds4(s_cs + 8 * l + 4 * j, c4);
+          lds4(s_cs + HD / 2 + 8 * l + 4 * j, s4);
+          lds4(s_w[is_q ? 0 : 1] + 8 * l + 4 * j, w1);
+          lds4(s_w[is_q ? 0 : 1] + HD / 2 + 8 * l + 4 * j, w2);
+          float y1[4], y2[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i = 2 * j + e;
-            const float x1 = a[i] * rstd * (is_q ? wq[i] : wk[i]);
-            const float x2 = b[i] * rstd * (is_q ? wq[8 + i] : wk[8 + i]);
-            y1[e] = x1 * cs[i] - x2 * sn[i];
-            y2[e] = x2 * cs[i] + x1 * sn[i];
+          for (int e = 0; e < 4; ++e) {
+            const int i = 4 * j + e;
+            const float x1 = a[i] * rstd * w1[e];
+            const float x2 = b[i] * rstd * w2[e];
+            y1[e] = x1 * c4[e] - x2 * s4[e];
+            y2[e] = x2 * c4[e] + x1 * s4[e];
           }
-          ol2[j] = __floats2bfloat162_rn(y1[0], y1[1]);
-          oh2[j] = __floats2bfloat162_rn(y2[0], y2[1]);
+          ol2[2 * j] = __floats2bfloat162_rn(y1[0], y1[1]);
+          ol2[2 * j + 1] = __floats2bfloat162_rn(y1[2], y1[3]);
+          oh2[2 * j] = __floats2bfloat162_rn(y2[0], y2[1]);
+          oh2[2 * j + 1] = __floats2bfloat162_rn(y2[2], y2[3]);
         }
       }
       *reinterpret_cast<uint4*>(dst[u] + 8 * l) = lo[u];
