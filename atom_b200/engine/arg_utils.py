@@ -22,6 +22,7 @@ class EngineArgs:
     kv_cache_dtype: str = "bf16"
     block_size: int = 16
     max_model_len: Optional[int] = None
+    cudagraph_mixed_steps: bool = True
     cudagraph_capture_sizes: str = "[1,2,4,8,16,24,32,48,64,96,128,192,256,384,512]"
     load_dummy: Optional[str] = None
     max_num_batched_tokens: int = 16384
@@ -47,6 +48,8 @@ class EngineArgs:
                             help="Maximum model context length, the default is max_position_embeddings.")
         parser.add_argument("--cudagraph-capture-sizes", type=str, default="[1,2,4,8,16,24,32,48,64,96,128,192,256,384,512]",
                             help="Sizes to capture cudagraph. Example: [1,2,4,8,16]")
+        parser.add_argument("--cudagraph-mixed-steps", action=argparse.BooleanOptionalAction, default=True,
+                            help="Replay graphs for small steps that hold prompt portions too (not only for decode steps).")
         parser.add_argument("--load_dummy", nargs="?", const="random", default=None, choices=["random"],
                             help="Use seeded random weights instead of reading the checkpoint.")
         parser.add_argument("--max-num-batched-tokens", type=int, default=16384,
@@ -77,7 +80,7 @@ class EngineArgs:
             self.cudagraph_capture_sizes, str) else list(self.cudagraph_capture_sizes)
         return dict(
             dtype=self.dtype, enforce_eager=self.enforce_eager, kv_cache_block_size=self.block_size,
-            max_model_len=self.max_model_len, cudagraph_capture_sizes=sizes, load_dummy=self.load_dummy,
+            max_model_len=self.max_model_len, cudagraph_capture_sizes=sizes, cudagraph_mixed_steps=self.cudagraph_mixed_steps, load_dummy=self.load_dummy,
             max_num_batched_tokens=self.max_num_batched_tokens,
             long_prefill_token_threshold=self.long_prefill_token_threshold,
             enable_chunked_prefill=self.enable_chunked_prefill, enable_prefix_caching=self.enable_prefix_caching,

@@ -57,6 +57,10 @@ class StepContext:
     max_ctx_len: int = 0
     logits_out: Optional[torch.Tensor] = None   # where the head writes, if preallocated
     plans: Dict = field(default_factory=dict)    # launch plans that parts share within the step
+    # True while a step of a fixed shape is recorded into a graph that later steps of other makeups
+    # replay: launch plans must then hold for every batch of num_tokens tokens in num_seqs requests
+    # (the host lists above describe no particular batch)
+    plan_for_any_batch: bool = False
 
 
 def pack_layout(T: int, S: int, R: int, widths: Sequence[int]):
@@ -104,7 +108,7 @@ class StepBuilder:
         self.vocab_size = vocab_size
         self.status = status
         self._flex = _Staging(1 << 16, self.device)
-        self._fixed: Dict[int, _Staging] = {}
+        self._fixed: Dict[object, _Staging] = {}     # batch size, or (tokens, requests), -> arrays of that shape
         self.h2d_bytes = 0
 
     # ------------------------------------------------------------------ shared
@@ -224,6 +228,45 @@ class StepBuilder:
         ctx = self._context(st.dev, layout, batch, batch, batch, widths, q_lens, q_starts, slots, targets)
         # host lists describe the padded batch: padding requests bring one skipped row each
         ctx.q_lens = q_lens + [1] * (batch - len(entries))
+        return ctx
+
+    # ------------------------------------------------------------------ fixed shape, any makeup
+
+    def build_fixed_mixed(self, entries: Sequence[StepEntry], targets: List[int], tokens: int, seqs: int,
+                          table_width: int) -> StepContext:
+        """Arrays of a fixed shape for up to ``tokens`` tokens of up to ``seqs`` requests with up to
+        ``seqs`` wanted rows, portions and single tokens alike, always at the same device addresses
+        for this pair of sizes; what is beyond the live tokens and requests is padding."""
+        S, T = len(entries), sum(len(e.tokens) for e in entries)
+        assert S <= seqs and T <= tokens
+        widths = [table_width] * len(self.cache.groups)
+        layout, total = pack_layout(tokens, seqs, seqs, widths)
+        key = (tokens, seqs)
+        st = self._fixed.get(key)
+        if st is None:
+            st = self._fixed[key] = _Staging(total, self.device)
+        k, host = st.acquire()
+        q_lens, q_starts, slots, rows = self._fill(host, layout, entries, targets, seqs, tokens, widths)
+        if len(rows) > seqs:
+            raise StepError(f"{len(rows)} wanted rows in a step shaped for {seqs}")
+        o, n = layout["logits_rows"]
+        host[o:o + n] = 0
+        host[o:o + len(rows)] = rows
+        st.push(k, total)
+        self.h2d_bytes += 4 * total
+        ctx = self._context(st.dev, layout, tokens, seqs, seqs, widths, q_lens, q_starts, slots, targets)
+        ctx.q_lens = q_lens + [0] * (seqs - S)
+        return ctx
+
+    def fixed_context_mixed(self, tokens: int, seqs: int, table_width: int, max_ctx_len: int) -> StepContext:
+        """The context over the fixed-shape arrays of (tokens, seqs) without touching them, for a graph
+        capture.  ``build_fixed_mixed`` must have run once for this pair."""
+        widths = [table_width] * len(self.cache.groups)
+        layout, _ = pack_layout(tokens, seqs, seqs, widths)
+        st = self._fixed[(tokens, seqs)]
+        ctx = self._context(st.dev, layout, tokens, seqs, seqs, widths, [tokens] + [0] * (seqs - 1), [0] * seqs,
+                            [0] * seqs, [max_ctx_len] * seqs)
+        ctx.plan_for_any_batch = True
         return ctx
 
     def fixed_context(self, batch: int, table_width: int, max_ctx_len: int) -> StepContext:

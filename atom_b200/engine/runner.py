@@ -35,6 +35,15 @@ class _DecodeGraph:
     logits = None
 
 
+# Steps that are not pure decode steps replay a graph too when they are small enough to be bound by
+# the host's launches (a few hundred per step, 3.7 ms): one graph per (tokens, requests) rounded up to
+# these.  Measured at Qwen3-8B sizes, 8 decoded tokens beside a portion: 16 tokens 5.09 -> 4.88 ms,
+# 100 tokens 5.31 -> 5.09 ms; from about 128 tokens on the device is the bound and the rows of padding
+# cost more than the launches (408 tokens in a shape of 448: 7.26 -> 7.8 ms), so larger steps run eagerly.
+_MIXED_TOKENS = (16, 32, 48, 64, 80, 96, 128)
+_MIXED_SEQS = (8, 32, 64)
+
+
 class ModelRunner:
     def __init__(self, engine_config: EngineConfig, model_config: Optional[ModelConfig] = None,
                  device: str = "cuda:0"):
@@ -71,9 +80,10 @@ class ModelRunner:
         self.builder = StepBuilder(self.cache, self.device, self.spec.vocab_size, self.status)
         self.steps_run = 0
         # Decode steps (one token per request) of these batch sizes replay a captured CUDA graph.
-        self.graphs_enabled = not engine_config.enforce_eager
+        self.graphs_enabled = not engine_config.enforce_eager and self.model.graph_safe
         self._graph_sizes = sorted(set(int(b) for b in engine_config.cudagraph_capture_sizes if int(b) > 0))
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[object, "_DecodeGraph"] = {}     # batch size, or (tokens, requests), -> graph
+        self.mixed_graphs = self.graphs_enabled and engine_config.cudagraph_mixed_steps
         self._table_width = max(1, -(-self.max_model_len // self.page_size))
         self.graph_replays = 0
 
@@ -157,6 +167,7 @@ class ModelRunner:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         targets = self._reserve(entries)
         size = self._graph_size(entries)
+        shape = None if size or device_tokens is not None else self._mixed_shape(entries)
         if device_tokens is not None:
             rows = None if device_token_rows is None else [int(r) for r in device_token_rows]
             n_src = device_tokens.numel()
@@ -167,6 +178,8 @@ class ModelRunner:
             logits = self._step_graph(entries, targets, size, device_tokens, rows)
         elif size:
             logits = self._step_graph(entries, targets, size)
+        elif shape:
+            logits = self._step_mixed_graph(entries, targets, shape)
         else:
             ctx = self.builder.build(entries, targets)
             logits = self.model.forward(ctx, self.storage)
@@ -195,7 +208,56 @@ class ModelRunner:
                 return b
         return 0
 
-    def capture_graphs(self, max_batch: int) -> List[int]:
+    def _mixed_shape(self, entries: Sequence[StepEntry]):
+        """(tokens, requests) of the fixed shape that a step of prompt portions (beside decoded tokens or
+        not) replays, None if it runs eagerly: small enough, and no more wanted rows than requests."""
+        if not self.mixed_graphs:
+            return None
+        T = sum(len(e.tokens) for e in entries)
+        S = max(len(entries), sum(len(e.want) for e in entries))
+        if T > _MIXED_TOKENS[-1] or S > _MIXED_SEQS[-1]:
+            return None
+        return (next(t for t in _MIXED_TOKENS if t >= T), next(n for n in _MIXED_SEQS if n >= S))
+
+    def _capture_mixed(self, shape) -> "_DecodeGraph":
+        """As ``_capture``, for a step of ``shape`` = (tokens, requests) of any makeup: launch plans are
+        made for every batch that fits the shape, and for the longest request the engine takes."""
+        tokens, seqs = shape
+        g = _DecodeGraph()
+        g.workspace = Workspace(self.device)
+        g.logits = torch.empty((seqs, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        saved = self.rt.workspace
+        self.rt.workspace = g.workspace
+        try:
+            def run():
+                ctx = self.builder.fixed_context_mixed(tokens, seqs, self._table_width, self.max_model_len)
+                ctx.logits_out = g.logits
+                self.model.forward(ctx, self.storage)
+
+            self.builder.build_fixed_mixed([], [], tokens, seqs, self._table_width)   # all padding
+            run()
+            torch.cuda.current_stream().synchronize()
+            g.graph = torch.cuda.CUDAGraph()
+            before = native.launches
+            with torch.cuda.graph(g.graph):
+                run()
+            g.num_launches = native.launches - before
+            g.workspace.frozen = True
+        finally:
+            self.rt.workspace = saved
+        return g
+
+    def _step_mixed_graph(self, entries: Sequence[StepEntry], targets: List[int], shape) -> torch.Tensor:
+        g = self._graphs.get(shape)
+        if g is None:
+            g = self._graphs[shape] = self._capture_mixed(shape)
+        self.builder.build_fixed_mixed(entries, targets, shape[0], shape[1], self._table_width)
+        g.graph.replay()
+        native.add_launches(g.num_launches)
+        self.graph_replays += 1
+        return g.logits[: sum(len(e.want) for e in entries)]       # valid until the next step of this shape
+
+    def capture_graphs(self, max_batch: int) -> list:
         """Captures, ahead of the first request, the decode graphs that batches of up to
         ``max_batch`` requests replay (the reference captures all of its sizes at start,
         atom/model_engine/model_runner.py capture_cudagraph); without this call a size is
@@ -209,6 +271,14 @@ class ModelRunner:
                 done.append(b)
             if b >= max_batch:
                 break
+        if self.mixed_graphs:      # (a capture in the middle of serving would stall a step by ~0.1 s)
+            for n in _MIXED_SEQS:
+                for t in _MIXED_TOKENS:
+                    if (t, n) not in self._graphs:
+                        self._graphs[(t, n)] = self._capture_mixed((t, n))
+                        done.append((t, n))
+                if n >= max_batch:
+                    break
         return done
 
     def _capture(self, size: int) -> "_DecodeGraph":

@@ -48,6 +48,11 @@ class Model:
     def named_parts(self) -> Iterator[Tuple[str, Part, PartSpec]]:
         return iter(self._named)
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part says that its launches depend on a step's shape only (Part.graph_safe)."""
+        return all(part.graph_safe for _, part, _ in self._named)
+
     def cache_needs(self) -> Dict[int, CacheNeed]:
         """Cache slot -> what the mixers that run on it keep there."""
         needs: Dict[int, CacheNeed] = {}

@@ -420,6 +420,22 @@ def flash_plan(q_lens, group: int, nkv: int, max_ctx: int, sms: Optional[int] = 
     return tiles, short > 0, splits
 
 
+def flash_plan_for_any(tokens: int, seqs: int, group: int, nkv: int, max_ctx: int, sms: Optional[int] = None,
+                       long_rows: int = 0):
+    """A launch plan that holds for every batch of at most ``tokens`` tokens in at most ``seqs`` requests
+    (for a step recorded once and replayed for batches of other makeups): tile counts are upper bounds
+    (the kernels find their tile from the step's arrays; a CTA without one leaves at once), short
+    requests are always provided for, with the splits of ``seqs`` short requests."""
+    rows = tokens * group
+    n_long = min(seqs, rows // long_rows) if long_rows else 0
+    long_tiles = rows // 128 + 1 + n_long if long_rows else 0
+    tiles = rows // 64 + 1 + min(seqs, max(1, rows // 17))
+    splits = flash_plan([1] * seqs, group, nkv, max_ctx, sms)[2]
+    if long_rows:
+        return tiles, True, splits, long_tiles
+    return tiles, True, splits
+
+
 def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: torch.Tensor,
                     v_pages: torch.Tensor, block_table: torch.Tensor, cu_q: torch.Tensor,
                     ctx_len: torch.Tensor, seq_of_token: torch.Tensor, T: int, num_seqs: int, nh: int,

@@ -25,6 +25,8 @@ from .spec import CacheNeed, ParamSpec, PartSpec
 
 @register("mixer", "paged_attention")
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, qk_norm: bool = False, norm_eps: float = 0.0,
                  bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None):
@@ -93,8 +95,12 @@ class PagedAttention(Mixer):
             key = ("flash", self.nh, self.nkv, long_rows)
             plan = step.plans.get(key)
             if plan is None:
-                plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
-                                         long_rows=long_rows)
+                if step.plan_for_any_batch:
+                    plan = native.flash_plan_for_any(step.num_tokens, step.num_seqs, self.nh // self.nkv, self.nkv,
+                                                     step.max_ctx_len, long_rows=long_rows)
+                else:
+                    plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
+                                             long_rows=long_rows)
                 step.plans[key] = plan
             scratch = None
             if plan[2] > 1:

@@ -71,6 +71,11 @@ class Runtime:
 
 class Part:
     kind = "?"
+    # True if ``forward`` launches the same kernels with the same arguments for every batch of one shape:
+    # it reads the step's arrays on the device only (not the host lists q_lens / q_starts /
+    # host_state_slots), never waits for the device and allocates through the workspace.  Steps of a
+    # model whose parts all say so may be recorded into CUDA graphs.
+    graph_safe = False
 
     def params(self) -> Dict[str, ParamSpec]:
         return {}

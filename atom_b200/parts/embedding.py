@@ -18,6 +18,8 @@ from .spec import ParamSpec
 
 @register("embedding", "token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
 
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 
 @register("head", "lm_head")
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
         self.vocab_size, self.hidden_size, self.tied = vocab_size, hidden_size, tied
 

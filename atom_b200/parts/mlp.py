@@ -13,6 +13,8 @@ from .spec import ParamSpec
 
 @register("ffn", "gated_silu")
 class GatedSiluMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
 

@@ -14,6 +14,8 @@ from .spec import ParamSpec
 
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float):
         self.size, self.eps = size, eps
 

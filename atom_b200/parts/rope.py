@@ -16,6 +16,8 @@ from .registry import register
 
 @register("position", "rope_neox")
 class RotaryNeox(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, rotary_dim: int, theta: float, max_position: int):
         if rotary_dim % 2:
             raise ValueError("rotary_dim must be even")
@@ -35,5 +37,7 @@ class RotaryNeox(PositionEncoding):
 
 @register("position", "none")
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def __init__(self):
         pass

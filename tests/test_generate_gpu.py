@@ -212,7 +212,8 @@ def test_overlap_goes_on_when_requests_end_at_their_token_count(model_dirs):
     lens = [9, 5, 17, 13, 5]
     eng = _engine(model_dirs[name], "float32", pages=64, page=8, enforce_eager=False, cudagraph_capture_sizes=[1, 2, 4, 8],
                   max_model_len=128)
-    assert sorted(eng.runner._graphs) == [1, 2, 4, 8]          # captured before the first request
+    assert sorted(k for k in eng.runner._graphs if isinstance(k, int)) == [1, 2, 4, 8]     # captured before the first request
+    assert (16, 8) in eng.runner._graphs and (128, 8) in eng.runner._graphs                  # and the small steps of any makeup
     outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in lens])
     for p_, n, o in zip(prompts, lens, outs):
         assert o["token_ids"] == plain.generate_greedy(cfg, w, p_, n) and o["finish_reason"] == "max_tokens"

@@ -125,3 +125,36 @@ def test_captured_decode_steps_match_plain(model_dirs, name, dtype):
         assert err <= tol, f"{name}/{dtype}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
     assert runner.graph_replays > 50 and set(runner._graphs) >= {1, 4}
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_small_steps_of_any_makeup_replay_graphs_and_match_plain(model_dirs, name, dtype):
+    """Steps with prompt portions (beside decoded tokens or not) of up to 128 tokens replay a graph
+    recorded for their shape rounded up, whose launch plans hold for every batch of that shape: in
+    portions of changing size and mixed, with every row's logits wanted, the logits are the plain
+    implementation's."""
+    from atom_b200.config import EngineConfig
+    from atom_b200.engine.runner import ModelRunner
+
+    seqs = _seqs(name)
+    ref = plain_logits(model_dirs[name], seqs)
+    cfg = EngineConfig(model=model_dirs[name], dtype=dtype, kv_cache_block_size=PAGE[name],
+                       num_kvcache_blocks=96, max_num_seqs=8, enforce_eager=False,
+                       cudagraph_capture_sizes=[1, 2, 4], max_model_len=256)
+    runner = ModelRunner(cfg)
+    for steps in (traces.ragged(seqs), traces.mixed(seqs, max_live=4)[0], traces.tail_by_token(seqs, 32)):
+        got = traces.collect(steps, replay(runner, steps))
+        err, rid, pos = max_err(got, ref)
+        tol = _tol(dtype, ref)
+        assert err <= tol, f"{name}/{dtype}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+    shapes = [k for k in runner._graphs if isinstance(k, tuple)]
+    assert len(shapes) >= 2 and runner.graph_replays > 60, (shapes, runner.graph_replays)
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+    # the same steps with the option off run eagerly
+    off = ModelRunner(EngineConfig(model=model_dirs[name], dtype=dtype, kv_cache_block_size=PAGE[name],
+                                   num_kvcache_blocks=96, max_num_seqs=8, enforce_eager=False,
+                                   cudagraph_capture_sizes=[1, 2, 4], max_model_len=256, cudagraph_mixed_steps=False))
+    steps = traces.ragged(seqs)
+    replay(off, steps)
+    assert not [k for k in off._graphs if isinstance(k, tuple)]
