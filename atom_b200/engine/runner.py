@@ -11,11 +11,10 @@ from __future__ import annotations
 
 from typing import Dict, Hashable, List, Optional, Sequence
 
-import numpy as np
 import torch
 
 from .. import native
-from ..cache import NO_PAGE, CacheManager, OutOfPages
+from ..cache import CacheManager, OutOfPages
 from ..cache.storage import CacheStorage
 from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig, load_model_config
@@ -23,7 +22,7 @@ from ..models.model import Model
 from ..models.registry import build_model_spec
 from ..parts.base import Runtime, Workspace
 from ..weights import load_weights, random_weights_on_device
-from .batch import StepBuilder, StepContext, StepEntry, StepError
+from .batch import StepBuilder, StepEntry, StepError
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 

@@ -28,7 +28,7 @@ from __future__ import annotations
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, List, Optional, Sequence as Seq, Tuple
+from typing import Deque, List, Optional, Sequence as Seq
 
 from ..cache import CacheManager, OutOfPages
 from .sequence import Sequence, SequenceStatus

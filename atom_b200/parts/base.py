@@ -10,7 +10,7 @@ compute type, the device and a workspace of reusable activation buffers.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 

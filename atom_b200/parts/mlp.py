@@ -4,7 +4,6 @@ from __future__ import annotations
 
 from typing import Dict
 
-from .. import native
 from .base import FeedForward
 from .linear import gated_linear, linear
 from .registry import register

@@ -2,9 +2,7 @@
    r = x + r;  y = r * rsqrt(mean(r^2) + eps) * w,  computed in 32-bit on a 32-bit residual."""
 from __future__ import annotations
 
-from typing import Dict, Optional
-
-import torch
+from typing import Dict
 
 from .. import native
 from .base import Norm

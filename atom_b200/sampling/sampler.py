@@ -3,7 +3,7 @@ atom/model_ops/sampler.py:104-132) and top-k / top-p (:134-295), one kernel for 
 from __future__ import annotations
 
 import ctypes
-from typing import List, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

@@ -16,7 +16,6 @@ import torch
 from ..config.model_config import ModelConfig, save_model_config
 from ..models.model import Model
 from ..models.registry import build_model_spec
-from ..parts.spec import ParamSpec
 from .loader import expected_tensors
 
 _STD = 0.02

@@ -16,7 +16,6 @@ weights widen exactly); rotation angles are formed in float32 as the reference f
 from __future__ import annotations
 
 import json
-import math
 import os
 from typing import Dict, List, Optional, Sequence
 

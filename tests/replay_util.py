@@ -5,7 +5,6 @@ from __future__ import annotations
 from typing import Dict, List, Sequence
 
 import numpy as np
-import torch
 
 import plain_qwen3 as plain
 

@@ -1,7 +1,6 @@
 """Configuration: every key comes from config.json; bad files are refused with the key named."""
 import copy
 import json
-import os
 
 import pytest
 

@@ -6,7 +6,6 @@ product with ranges cut inside slabs, replayed from a CUDA graph with programmat
 launch: none of which the tiny configurations reach."""
 import numpy as np
 import pytest
-import torch
 
 import plain_qwen3 as plain
 

@@ -2,7 +2,6 @@
 that write them as model folders with seeded random weights."""
 from __future__ import annotations
 
-import json
 import os
 import zlib
 from typing import Dict, List
