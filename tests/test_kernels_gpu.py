@@ -332,6 +332,9 @@ TMA_DECODE_CASES = [
     (8, 2, 128, 128, 0, [1, 4, 1], [700, 300, 129], 4),                  # pages larger than a tile
     (8, 4, 128, 16, 0, [1] * 40, [40 + 13 * i for i in range(40)], 1),   # more CTAs than SMs: two CTAs an SM
     (8, 4, 128, 16, 0, [1] * 40, [40 + 13 * i for i in range(40)], 3),
+    (64, 8, 128, 16, 0, [1] * 5, [4096, 17, 300, 1, 1031], 4),           # group 8 (the 32B sizes): 8 packed rows
+    (64, 8, 128, 16, 0, [2, 1, 2], [900, 64, 33], 2),                    # group 8, two tokens: 16 packed rows
+    (32, 2, 128, 16, 0, [1] * 4, [700, 16, 129, 2000], 3),               # group 16: 16 packed rows from one token
 ]
 
 
