@@ -25,3 +25,28 @@ def test_splits_fill_one_wave_but_stay_long_enough():
     assert native.flash_plan([1] * 64, 4, 8, 4096, sms=SMS)[2] == 1
     assert 1 <= native.flash_plan([1] * 40, 4, 8, 4096, sms=SMS)[2] <= 8
     assert native.flash_plan([1] * 8, 4, 8, 1 << 20, sms=SMS)[2] <= 64
+
+
+def test_a_plan_for_any_batch_of_a_shape_covers_every_batch_of_it():
+    """A step recorded once for (tokens, requests) is replayed for batches of any makeup within that
+    shape: its tile counts must be no smaller than what any such batch needs, and it always provides
+    for short requests."""
+    import random
+    rng = random.Random(5)
+    for group, long_rows in ((1, 128), (4, 128), (8, 128), (4, 0), (16, 128), (3, 0)):
+        for tokens, seqs in ((16, 8), (48, 8), (128, 8), (128, 32), (96, 64), (128, 64)):
+            bound = native.flash_plan_for_any(tokens, seqs, group, 8, 4096, sms=SMS, long_rows=long_rows)
+            assert bound[1] is True
+            makeups = [[tokens], [1] * min(seqs, tokens), [tokens - 1, 1], [tokens // 2, tokens - tokens // 2]]
+            for _ in range(200):
+                n = rng.randint(1, min(seqs, tokens))
+                cuts = sorted(rng.sample(range(1, tokens), n - 1)) if n > 1 else []
+                lens = [b - a for a, b in zip([0] + cuts, cuts + [tokens])]
+                if rng.random() < 0.5:      # not every token of the shape is used
+                    lens = [max(0, x - rng.randint(0, 3)) for x in lens]
+                makeups.append(lens)
+            for lens in makeups:
+                plan = native.flash_plan(lens, group, 8, 4096, sms=SMS, long_rows=long_rows)
+                assert plan[0] <= bound[0], (group, long_rows, tokens, seqs, lens, plan, bound)
+                if long_rows:
+                    assert plan[3] <= bound[3], (group, long_rows, tokens, seqs, lens, plan, bound)
