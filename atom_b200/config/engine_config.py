@@ -23,7 +23,7 @@ class EngineConfig:
     # decode batch sizes whose steps replay a graph (captured at first use; a batch is padded to the next size)
     cudagraph_capture_sizes: List[int] = field(
         default_factory=lambda: [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512])
-    cudagraph_mixed_steps: bool = True    # steps with prompt portions of up to 128 tokens in all replay graphs too
+    cudagraph_mixed_steps: bool = True    # small steps with prompt portions replay graphs too (up to 128 tokens in all, more for small models)
     long_prefill_token_threshold: int = 0  # cap on one request's portion per step (0: none)
     enable_chunked_prefill: bool = True
     enable_prefix_caching: bool = False   # requests that begin like earlier ones take their pages (the reference's default is on)

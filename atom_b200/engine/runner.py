@@ -35,11 +35,14 @@ class _DecodeGraph:
 
 
 # Steps that are not pure decode steps replay a graph too when they are small enough to be bound by
-# the host's launches (a few hundred per step, 3.7 ms): one graph per (tokens, requests) rounded up to
-# these.  Measured at Qwen3-8B sizes, 8 decoded tokens beside a portion: 16 tokens 5.09 -> 4.88 ms,
-# 100 tokens 5.31 -> 5.09 ms; from about 128 tokens on the device is the bound and the rows of padding
-# cost more than the launches (408 tokens in a shape of 448: 7.26 -> 7.8 ms), so larger steps run eagerly.
-_MIXED_TOKENS = (16, 32, 48, 64, 80, 96, 128)
+# the host's launches (a few hundred per step, 3-4 ms): one graph per (tokens, requests) rounded up to
+# these.  Where the device becomes the bound, rows of padding cost more than the launches, and that
+# point lies the lower the larger the model is.  Measured with 8 decoded tokens beside a portion
+# (graph against eager): Qwen3-0.6B sizes 16 tokens 3.37 -> 1.85 ms, 400 tokens 3.07 -> 2.46 ms, even at
+# 800; 1.7B sizes 200 tokens 3.14 -> 2.63 ms, even at 350; 8B sizes 16 tokens 5.09 -> 4.88 ms, 100
+# tokens 5.31 -> 5.09 ms, 408 tokens (in a shape of 448) 7.26 -> 7.8 ms.  Hence the limit below:
+# about 600e9 / parameters tokens, at least 128.
+_MIXED_TOKENS = (16, 32, 48, 64, 80, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 640, 768, 896, 1024)
 _MIXED_SEQS = (8, 32, 64)
 
 
@@ -83,6 +86,9 @@ class ModelRunner:
         self._graph_sizes = sorted(set(int(b) for b in engine_config.cudagraph_capture_sizes if int(b) > 0))
         self._graphs: Dict[object, "_DecodeGraph"] = {}     # batch size, or (tokens, requests), -> graph
         self.mixed_graphs = self.graphs_enabled and engine_config.cudagraph_mixed_steps
+        params = self.weight_bytes / (4 if self.dtype == torch.float32 else 2)
+        limit = 128 if self.dtype == torch.float32 else max(128.0, 600e9 / max(params, 1.0))
+        self._mixed_tokens = tuple(t for t in _MIXED_TOKENS if t <= limit) or _MIXED_TOKENS[:1]
         self._table_width = max(1, -(-self.max_model_len // self.page_size))
         self.graph_replays = 0
 
@@ -214,9 +220,9 @@ class ModelRunner:
             return None
         T = sum(len(e.tokens) for e in entries)
         S = max(len(entries), sum(len(e.want) for e in entries))
-        if T > _MIXED_TOKENS[-1] or S > _MIXED_SEQS[-1]:
+        if T > self._mixed_tokens[-1] or S > _MIXED_SEQS[-1]:
             return None
-        return (next(t for t in _MIXED_TOKENS if t >= T), next(n for n in _MIXED_SEQS if n >= S))
+        return (next(t for t in self._mixed_tokens if t >= T), next(n for n in _MIXED_SEQS if n >= S))
 
     def _capture_mixed(self, shape) -> "_DecodeGraph":
         """As ``_capture``, for a step of ``shape`` = (tokens, requests) of any makeup: launch plans are
@@ -272,7 +278,7 @@ class ModelRunner:
                 break
         if self.mixed_graphs:      # (a capture in the middle of serving would stall a step by ~0.1 s)
             for n in _MIXED_SEQS:
-                for t in _MIXED_TOKENS:
+                for t in self._mixed_tokens:
                     if (t, n) not in self._graphs:
                         self._graphs[(t, n)] = self._capture_mixed((t, n))
                         done.append((t, n))
