@@ -18,6 +18,14 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   }
 }
 
+// silu(x) = x / (1 + e^-x) = x * (0.5 + 0.5 * tanh(x / 2)): one special-function operation instead of two
+// (the result is rounded to bfloat16, eight times coarser than tanh.approx's error).
+__device__ __forceinline__ float silu_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return x * fmaf(0.5f, t, 0.5f);
+}
+
 // bf16, I a multiple of 8: 16 bytes of gate and of up per thread.
 __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
                                          int64_t nvec, int I8) {
@@ -36,7 +44,7 @@ __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const 
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 g = __bfloat1622float2(gh[e]), u = __bfloat1622float2(uh[e]);
-      oh[e] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+      oh[e] = __floats2bfloat162_rn(silu_fast(g.x) * u.x, silu_fast(g.y) * u.y);
     }
     *reinterpret_cast<uint4*>(out + idx * 8) = o4;
   }
