@@ -93,6 +93,7 @@ class CacheManager:
             g.slots.append(slot)
             self.slot_group[slot] = g.index
         self.state_slots = StateSlots(max_requests)
+        self.admit_hooks = []                    # called with the state slot of every request that is admitted
         self.requests: Dict[Hashable, RequestCache] = {}
         if prefix_caching and (len(self.groups) != 1 or self.groups[0].window is not None or self.state_needs):
             raise ValueError("prefix caching needs a model whose layers all keep all keys in pages of one kind "
@@ -163,6 +164,8 @@ class CacheManager:
         for g in self.groups:
             rc.tables[g.index] = []
         self.requests[rid] = rc
+        for hook in self.admit_hooks:      # the storage clears the slot's state: a request starts from zeros
+            hook(rc.state_slot)
         return rc
 
     def extend(self, rid: Hashable, n_tokens: int) -> None:

@@ -2,7 +2,8 @@
 
 One array per page group, [slots, 2 (keys, values), pages, kv heads, page size, head size]
 in the compute type, and one array [state slots, *shape] per cache slot whose mixer keeps
-fixed-size state.  ``view(slot)`` is what a mixer gets for its run entry."""
+fixed-size state, zero when a request is admitted.  ``view(slot)`` is what a mixer gets for its
+run entry."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -28,6 +29,7 @@ class CacheStorage:
         self.manager = manager
         self.arrays = []
         self._views: Dict[int, CacheView] = {}
+        self._states = []
         ps = manager.page_size
         for g in manager.groups:
             a = torch.zeros(
@@ -41,7 +43,17 @@ class CacheStorage:
             sdt = dtype if need.state_dtype == "compute" else getattr(torch, need.state_dtype)
             st = torch.zeros((manager.state_slots.num_slots,) + tuple(need.state_shape), dtype=sdt, device=device)
             self.arrays.append(st)
+            self._states.append(st)
             self._views[slot] = CacheView(slot, state=st)
+        if self._states:
+            manager.admit_hooks.append(self.clear_state)
+
+    def clear_state(self, state_slot: int) -> None:
+        """Zeroes a request slot's rows in every state array.  Runs when a request is admitted (a
+        preempted request that comes back included), so a mixer finds zeros at a request's first
+        token whoever held the slot before."""
+        for st in self._states:
+            st[state_slot].zero_()
 
     def view(self, slot: int) -> Optional[CacheView]:
         return self._views.get(slot)

@@ -9,7 +9,9 @@ with one structure that is passed explicitly.
 one copy.  With a fixed shape (``build_fixed``) the arrays always lie at the same device
 addresses and have the same sizes, whatever the number of live requests: rows beyond the
 live ones are padding (``seq_of_token = -1``, no tokens, context length 0) that every kernel
-skips.  That is the form a captured CUDA graph replays.
+skips.  That is the form a captured CUDA graph replays.  Its block tables have rows as long as the
+longest request the engine takes, but a step fills and copies only the live requests' rows as far
+as their longest context reaches, so a step's host work and copy do not grow with ``max_model_len``.
 """
 from __future__ import annotations
 
@@ -19,6 +21,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import native
 from ..cache import NO_PAGE, CacheManager
 
 
@@ -76,29 +79,46 @@ def pack_layout(T: int, S: int, R: int, widths: Sequence[int]):
     return off, cur
 
 
-class _Staging:
-    """A device buffer with a ring of pinned host mirrors: a mirror is written again only
-    after the copy that read it has finished."""
+class _HostRing:
+    """A ring of pinned host buffers that steps fill and copy from: a buffer is written again only
+    after the copies that read it have finished.  One ring serves steps of every shape (they run one
+    after another)."""
 
-    def __init__(self, n: int, device, ring: int = 4):
-        self.n = n
-        self.dev = torch.zeros(n, dtype=torch.int32, device=device)
-        self.host = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(ring)]
+    def __init__(self, ring: int = 4):
+        self.host: List[Optional[torch.Tensor]] = [None] * ring
         self.events: List[Optional[torch.cuda.Event]] = [None] * ring
         self.next = 0
 
-    def acquire(self):
+    def acquire(self, n: int):
+        """(slot, pinned tensor of at least n int32, its numpy view)."""
         k = self.next
         self.next = (k + 1) % len(self.host)
         if self.events[k] is not None:
             self.events[k].synchronize()
-        return k, self.host[k].numpy()
+        buf = self.host[k]
+        if buf is None or buf.numel() < n:
+            buf = self.host[k] = torch.zeros(max(1 << 14, 1 << (n - 1).bit_length()), dtype=torch.int32).pin_memory()
+        return k, buf, buf.numpy()
 
-    def push(self, k: int, total: int) -> None:
-        self.dev[:total].copy_(self.host[k][:total], non_blocking=True)
+    def sent(self, k: int) -> None:
+        """The copies out of slot k have been put on the stream."""
         ev = torch.cuda.Event()
         ev.record()
         self.events[k] = ev
+
+
+class _FixedArrays:
+    """Device arrays of one fixed shape: the small per-token and per-request arrays, then one block
+    table per page group, ``width`` entries a row.  They keep their addresses for good (a captured
+    graph reads them); a step overwrites the small arrays and, of the tables, the rows of its live
+    requests as far as their longest context reaches.  What lies beyond is left over from earlier
+    steps and never read: a kernel looks up only pages below a request's context length."""
+
+    def __init__(self, tokens: int, seqs: int, num_groups: int, width: int, device):
+        self.tokens, self.seqs, self.width = tokens, seqs, width
+        self.layout, total = pack_layout(tokens, seqs, seqs, [width] * num_groups)
+        self.small = self.layout["bt0"][0] if num_groups else total      # int32 elements before the tables
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
 
 
 class StepBuilder:
@@ -107,13 +127,15 @@ class StepBuilder:
         self.device = torch.device(device)
         self.vocab_size = vocab_size
         self.status = status
-        self._flex = _Staging(1 << 16, self.device)
-        self._fixed: Dict[object, _Staging] = {}     # batch size, or (tokens, requests), -> arrays of that shape
+        self._ring = _HostRing()
+        self._flex_dev = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
+        self._fixed: Dict[object, _FixedArrays] = {}     # batch size, or (tokens, requests), -> arrays of that shape
         self.h2d_bytes = 0
 
     # ------------------------------------------------------------------ shared
 
     def _fill(self, host, layout, entries, targets, S_pad: int, T_pad: int, widths):
+        """Writes the step's arrays into ``host`` after ``layout``; tables are S_pad rows of widths[g]."""
         cache = self.cache
         S = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -153,7 +175,8 @@ class StepBuilder:
         ss[:S] = slots
         ss[S:] = 0
         for g, w in zip(cache.groups, widths):
-            bt = sec(f"bt{g.index}").reshape(S_pad, w)
+            o, n = layout[f"bt{g.index}"]
+            bt = host[o:o + n].reshape(-1, w)
             bt[:] = NO_PAGE
             for i, e in enumerate(entries):
                 t = cache.table(e.rid, g.index)
@@ -175,33 +198,76 @@ class StepBuilder:
             max_q_len=max(q_lens, default=0), max_ctx_len=max(targets, default=0),
         )
 
+    def _live_widths(self, entries) -> List[int]:
+        cache = self.cache
+        return [max(1, max((len(cache.table(e.rid, g.index)) for e in entries), default=1)) for g in cache.groups]
+
     # ------------------------------------------------------------------ any shape
 
     def build(self, entries: Sequence[StepEntry], targets: List[int]) -> StepContext:
         """Arrays sized for exactly this batch.  ``targets[i]``: tokens of request i in the
         cache after the step."""
-        cache = self.cache
         S = len(entries)
         T = sum(len(e.tokens) for e in entries)
         R = sum(len(e.want) for e in entries)
-        widths = [max(1, max(len(cache.table(e.rid, g.index)) for e in entries)) for g in cache.groups]
+        widths = self._live_widths(entries)
         layout, total = pack_layout(T, S, R, widths)
-        if total > self._flex.n:
-            self._flex = _Staging(1 << (total - 1).bit_length(), self.device)
-        k, host = self._flex.acquire()
+        if total > self._flex_dev.numel():
+            self._flex_dev = torch.zeros(1 << (total - 1).bit_length(), dtype=torch.int32, device=self.device)
+        k, pinned, host = self._ring.acquire(total)
         q_lens, q_starts, slots, rows = self._fill(host, layout, entries, targets, S, T, widths)
         o, n = layout["logits_rows"]
         host[o:o + n] = 0
         host[o:o + R] = rows
-        self._flex.push(k, total)
+        self._flex_dev[:total].copy_(pinned[:total], non_blocking=True)
+        self._ring.sent(k)
         self.h2d_bytes += 4 * total
-        return self._context(self._flex.dev, layout, T, S, R, widths, q_lens, q_starts, slots, targets)
+        return self._context(self._flex_dev, layout, T, S, R, widths, q_lens, q_starts, slots, targets)
 
     # ------------------------------------------------------------------ fixed shape
 
-    def fixed_layout(self, batch: int, table_width: int):
-        widths = [table_width] * len(self.cache.groups)
-        return pack_layout(batch, batch, batch, widths), widths
+    def _arrays(self, key, tokens: int, seqs: int, table_width: int) -> _FixedArrays:
+        fa = self._fixed.get(key)
+        if fa is None:
+            fa = self._fixed[key] = _FixedArrays(tokens, seqs, len(self.cache.groups), table_width, self.device)
+        assert fa.width == table_width
+        return fa
+
+    def _send_fixed(self, fa: _FixedArrays, entries, targets, token_rows=None, all_rows=False):
+        """Fills a host buffer with the step's small arrays (in the device layout) and, behind them, its
+        tables cut down to the live requests and their longest context; two kinds of copies bring them
+        to their places: one for the small arrays, one of rows for each table."""
+        S = len(entries)
+        live = self._live_widths(entries) if S else []
+        # host layout: the device's small arrays, then compact tables [S, live width]
+        layout = dict(fa.layout)
+        cur = fa.small
+        for g, w in zip(self.cache.groups, live):
+            layout[f"bt{g.index}"] = (cur, S * w)
+            cur += S * w
+        k, pinned, host = self._ring.acquire(cur)
+        q_lens, q_starts, slots, rows = self._fill(host, layout, entries, targets, fa.seqs, fa.tokens, live)
+        o, n = layout["logits_rows"]
+        if all_rows:
+            host[o:o + n] = np.arange(n, dtype=np.int32)
+        else:
+            if len(rows) > fa.seqs:
+                raise StepError(f"{len(rows)} wanted rows in a step shaped for {fa.seqs}")
+            host[o:o + n] = 0
+            host[o:o + len(rows)] = rows
+        if token_rows is not None:
+            o, _ = layout["token_ids"]
+            host[o:o + S] = np.asarray(token_rows, dtype=np.int32)
+        fa.dev[:fa.small].copy_(pinned[:fa.small], non_blocking=True)
+        sent = fa.small
+        for g, w in zip(self.cache.groups, live):
+            o, n = layout[f"bt{g.index}"]
+            do, _ = fa.layout[f"bt{g.index}"]
+            native.copy_rows_h2d(fa.dev[do:], fa.width, pinned[o:], w, w, S)
+            sent += n
+        self._ring.sent(k)
+        self.h2d_bytes += 4 * sent
+        return q_lens, q_starts, slots
 
     def build_fixed(self, entries: Sequence[StepEntry], targets: List[int], batch: int,
                     table_width: int, token_rows: Optional[Sequence[int]] = None) -> StepContext:
@@ -212,20 +278,10 @@ class StepBuilder:
         token_rows: the token section carries these numbers instead of the entries' tokens
         (the caller then replaces them on the device by tokens it gathers with them)."""
         assert len(entries) <= batch and all(len(e.tokens) == 1 for e in entries)
-        (layout, total), widths = self.fixed_layout(batch, table_width)
-        st = self._fixed.get(batch)
-        if st is None:
-            st = self._fixed[batch] = _Staging(total, self.device)
-        k, host = st.acquire()
-        q_lens, q_starts, slots, _ = self._fill(host, layout, entries, targets, batch, batch, widths)
-        o, n = layout["logits_rows"]
-        host[o:o + n] = np.arange(batch, dtype=np.int32)
-        if token_rows is not None:
-            o, _ = layout["token_ids"]
-            host[o:o + len(entries)] = np.asarray(token_rows, dtype=np.int32)
-        st.push(k, total)
-        self.h2d_bytes += 4 * total
-        ctx = self._context(st.dev, layout, batch, batch, batch, widths, q_lens, q_starts, slots, targets)
+        fa = self._arrays(batch, batch, batch, table_width)
+        q_lens, q_starts, slots = self._send_fixed(fa, entries, targets, token_rows, all_rows=True)
+        widths = [table_width] * len(self.cache.groups)
+        ctx = self._context(fa.dev, fa.layout, batch, batch, batch, widths, q_lens, q_starts, slots, targets)
         # host lists describe the padded batch: padding requests bring one skipped row each
         ctx.q_lens = q_lens + [1] * (batch - len(entries))
         return ctx
@@ -239,41 +295,28 @@ class StepBuilder:
         for this pair of sizes; what is beyond the live tokens and requests is padding."""
         S, T = len(entries), sum(len(e.tokens) for e in entries)
         assert S <= seqs and T <= tokens
+        fa = self._arrays((tokens, seqs), tokens, seqs, table_width)
+        q_lens, q_starts, slots = self._send_fixed(fa, entries, targets)
         widths = [table_width] * len(self.cache.groups)
-        layout, total = pack_layout(tokens, seqs, seqs, widths)
-        key = (tokens, seqs)
-        st = self._fixed.get(key)
-        if st is None:
-            st = self._fixed[key] = _Staging(total, self.device)
-        k, host = st.acquire()
-        q_lens, q_starts, slots, rows = self._fill(host, layout, entries, targets, seqs, tokens, widths)
-        if len(rows) > seqs:
-            raise StepError(f"{len(rows)} wanted rows in a step shaped for {seqs}")
-        o, n = layout["logits_rows"]
-        host[o:o + n] = 0
-        host[o:o + len(rows)] = rows
-        st.push(k, total)
-        self.h2d_bytes += 4 * total
-        ctx = self._context(st.dev, layout, tokens, seqs, seqs, widths, q_lens, q_starts, slots, targets)
+        ctx = self._context(fa.dev, fa.layout, tokens, seqs, seqs, widths, q_lens, q_starts, slots, targets)
         ctx.q_lens = q_lens + [0] * (seqs - S)
         return ctx
 
     def fixed_context_mixed(self, tokens: int, seqs: int, table_width: int, max_ctx_len: int) -> StepContext:
         """The context over the fixed-shape arrays of (tokens, seqs) without touching them, for a graph
-        capture.  ``build_fixed_mixed`` must have run once for this pair."""
+        capture; launch plans are made for requests of up to ``max_ctx_len`` tokens."""
+        fa = self._arrays((tokens, seqs), tokens, seqs, table_width)
         widths = [table_width] * len(self.cache.groups)
-        layout, _ = pack_layout(tokens, seqs, seqs, widths)
-        st = self._fixed[(tokens, seqs)]
-        ctx = self._context(st.dev, layout, tokens, seqs, seqs, widths, [tokens] + [0] * (seqs - 1), [0] * seqs,
+        ctx = self._context(fa.dev, fa.layout, tokens, seqs, seqs, widths, [tokens] + [0] * (seqs - 1), [0] * seqs,
                             [0] * seqs, [max_ctx_len] * seqs)
         ctx.plan_for_any_batch = True
         return ctx
 
     def fixed_context(self, batch: int, table_width: int, max_ctx_len: int) -> StepContext:
         """The context over the fixed-shape arrays of ``batch`` without touching them: what a
-        graph capture records its launches against.  ``build_fixed`` must have run once."""
-        (layout, _), widths = self.fixed_layout(batch, table_width)
-        st = self._fixed[batch]
-        ctx = self._context(st.dev, layout, batch, batch, batch, widths, [1] * batch, [0] * batch,
-                            [0] * batch, [max_ctx_len] * batch)
-        return ctx
+        graph capture records its launches against; launch plans are made for requests of up to
+        ``max_ctx_len`` tokens."""
+        fa = self._arrays(batch, batch, batch, table_width)
+        widths = [table_width] * len(self.cache.groups)
+        return self._context(fa.dev, fa.layout, batch, batch, batch, widths, [1] * batch, [0] * batch,
+                             [0] * batch, [max_ctx_len] * batch)

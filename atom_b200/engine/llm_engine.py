@@ -15,7 +15,7 @@ import torch
 from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
-from .batch import StepEntry
+from .batch import StepEntry, StepError
 from .runner import ModelRunner
 from .scheduler import ScheduledEntry, ScheduledStep, Scheduler
 from .sequence import Sequence
@@ -37,9 +37,10 @@ class _Pending:
     """A launched step: its schedule, the sampled ids on the device, their pinned host copy
     (in flight) and the event that marks the copy's end."""
 
-    def __init__(self, sched, ids, host, event, lp_host=None):
+    def __init__(self, sched, ids, host, event, lp_host=None, flags_host=None):
         self.sched, self.ids, self.host, self.event = sched, ids, host, event
         self.lp_host = lp_host      # pinned copy of the tokens' log-probabilities, if some request wants them
+        self.flags_host = flags_host    # pinned copy of the kernels' fault flags as they stood after the step
 
 
 class LLMEngine:
@@ -62,6 +63,7 @@ class LLMEngine:
         )
         self.sampler = Sampler(self.runner.device, self.config.seed)
         self._seqs: Dict[int, Sequence] = {}
+        self._next_seq_id = 0     # per engine: a second engine of the process gives the same ids, hence the same default seeds
         self.num_steps = 0
         self.num_prompt_tokens = 0
         self.num_generated_tokens = 0
@@ -149,7 +151,8 @@ class LLMEngine:
                     stops.append([int(t) for t in toks])
         out = []
         for i in range(params.n):
-            seq = Sequence(ids, params, stop_token_sequences=stops, sibling_index=i)
+            seq = Sequence(ids, params, self._next_seq_id, stop_token_sequences=stops, sibling_index=i)
+            self._next_seq_id += 1
             self._seqs[seq.seq_id] = seq
             self.scheduler.add(seq)
             out.append(seq.seq_id)
@@ -180,29 +183,44 @@ class LLMEngine:
         return self.sampler.logprobs(logits, ids)
 
     def _read_later(self, sched: ScheduledStep, ids: torch.Tensor, lps: Optional[torch.Tensor] = None) -> "_Pending":
-        """Starts the copy of the sampled ids to pinned host memory; the host waits for it later."""
-        if self._pin_ring is None or self._pin_ring[0].numel() < 2 * ids.numel():
-            self._pin_ring = [torch.empty(max(2 * ids.numel(), 128), dtype=torch.int32).pin_memory() for _ in range(4)]
-        self._pin_next = (self._pin_next + 1) % 4      # a buffer is read two calls later at most
+        """Starts the copy of the sampled ids (and of the kernels' fault flags) to pinned host memory;
+        the host waits for it later."""
         n = ids.numel()
-        host = self._pin_ring[self._pin_next][:n]
+        if self._pin_ring is None or self._pin_ring[0].numel() < 2 * n + 2:
+            self._pin_ring = [torch.empty(max(2 * n + 2, 128), dtype=torch.int32).pin_memory() for _ in range(4)]
+        self._pin_next = (self._pin_next + 1) % 4      # a buffer is read two calls later at most
+        buf = self._pin_ring[self._pin_next]
+        host = buf[:n]
         host.copy_(ids, non_blocking=True)
         lp_host = None
         if lps is not None:
-            lp_host = self._pin_ring[self._pin_next][n:2 * n].view(torch.float32)
+            lp_host = buf[n:2 * n].view(torch.float32)
             lp_host.copy_(lps, non_blocking=True)
+        flags_host = buf[2 * n:2 * n + 2]
+        flags_host.copy_(self.runner.flags, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        return _Pending(sched, ids, host, ev, lp_host)
+        return _Pending(sched, ids, host, ev, lp_host, flags_host)
 
     def _resolve(self, pending: "_Pending") -> List[Sequence]:
-        """Waits for a launched step's tokens and does its bookkeeping."""
+        """Waits for a launched step's tokens, raises if a kernel of the step (or of one before it)
+        reported a fault, and does the step's bookkeeping."""
         pending.event.synchronize()
+        self.runner.raise_for_flags(pending.flags_host.tolist())
         tokens = pending.host.tolist()
         lps = pending.lp_host.tolist() if pending.lp_host is not None else None
-        self.d2h_bytes += 4 * len(tokens) * (2 if lps is not None else 1)
+        self.d2h_bytes += 4 * len(tokens) * (2 if lps is not None else 1) + 8
         self.num_generated_tokens += len(tokens)
         return self.scheduler.postprocess(pending.sched, tokens, lps)
+
+    def _abandon(self, *scheds: Optional[ScheduledStep]) -> None:
+        """A kernel of a step reported a fault: what the step's requests have in the cache is not to be
+        trusted (and a step launched ahead of it has moved them on without the scheduler's knowledge).
+        They end with reason "fault" and give everything back; the engine goes on with the others."""
+        for sched in scheds:
+            for e in (sched.entries if sched is not None else ()):
+                if not e.seq.is_finished:
+                    self.scheduler.abort(e.seq.seq_id, reason="fault")
 
     def _look_ahead(self, pending: "_Pending") -> Optional["_Pending"]:
         """Launches the decode step after ``pending`` without knowing its tokens, if nothing but
@@ -252,7 +270,11 @@ class LLMEngine:
         if self._pending is not None:
             pending, self._pending = self._pending, None
             ahead = self._look_ahead(pending) if self.overlap_steps else None
-            finished = self._resolve(pending)
+            try:
+                finished = self._resolve(pending)
+            except StepError:
+                self._abandon(pending.sched, ahead.sched if ahead is not None else None)
+                raise
             if ahead is not None:
                 self._pending = ahead
                 return finished
@@ -284,11 +306,11 @@ class LLMEngine:
         if self.overlap_steps and pure_decode and self.runner._graph_size(entries):
             self._pending = self._read_later(sched, ids, lps)
             return finished
-        tokens = ids.tolist()
-        lp_list = lps.tolist() if lps is not None else None
-        self.d2h_bytes += 4 * len(tokens) * (2 if lps is not None else 1)
-        self.num_generated_tokens += len(tokens)
-        return finished + self.scheduler.postprocess(sched, tokens, lp_list)
+        try:
+            return finished + self._resolve(self._read_later(sched, ids, lps))
+        except StepError:
+            self._abandon(sched)
+            raise
 
     # ------------------------------------------------------------------ whole requests
 

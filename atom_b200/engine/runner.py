@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import native
@@ -30,7 +31,6 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class _DecodeGraph:
     num_launches = 0
     graph = None
-    workspace = None
     logits = None
 
 
@@ -69,52 +69,95 @@ class ModelRunner:
         self.max_model_len = min(engine_config.max_model_len or self.spec.max_position, self.spec.max_position)
         self.page_size = engine_config.kv_cache_block_size
 
-        needs = self.model.cache_needs()
-        probe = CacheManager(needs, self.page_size, 1, 1)
-        num_pages = engine_config.num_kvcache_blocks
-        if num_pages <= 0:
-            num_pages = self._pages_from_free_memory(probe)
-        self.cache = CacheManager(needs, self.page_size, num_pages, engine_config.max_num_seqs,
-                                  prefix_caching=engine_config.enable_prefix_caching)
-        self.storage = CacheStorage(self.cache, self.dtype, self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self.builder = StepBuilder(self.cache, self.device, self.spec.vocab_size, self.status)
-        self.steps_run = 0
         # Decode steps (one token per request) of these batch sizes replay a captured CUDA graph.
         self.graphs_enabled = not engine_config.enforce_eager and self.model.graph_safe
         self._graph_sizes = sorted(set(int(b) for b in engine_config.cudagraph_capture_sizes if int(b) > 0))
-        self._graphs: Dict[object, "_DecodeGraph"] = {}     # batch size, or (tokens, requests), -> graph
+        self._graphs: Dict[object, "_DecodeGraph"] = {}     # (batch size | (tokens, requests), plan signature) -> graph
+        self._graph_keys: Dict[object, object] = {}         # (shape, context class) -> key into _graphs
         self.mixed_graphs = self.graphs_enabled and engine_config.cudagraph_mixed_steps
         params = self.weight_bytes / (4 if self.dtype == torch.float32 else 2)
         limit = 128 if self.dtype == torch.float32 else max(128.0, 600e9 / max(params, 1.0))
         self._mixed_tokens = tuple(t for t in _MIXED_TOKENS if t <= limit) or _MIXED_TOKENS[:1]
         self._table_width = max(1, -(-self.max_model_len // self.page_size))
         self.graph_replays = 0
+        # All graphs share one workspace and one logits buffer: steps run one after another.
+        self._graph_ws = Workspace(self.device, keep_outgrown=True)
+        self._graph_logits: Optional[torch.Tensor] = None
+        self.memory: Dict[str, int] = {"weights": self.weight_bytes}
+
+        needs = self.model.cache_needs()
+        self.flags = native.device_flags(self.device)
+        self.status = native.status_flag(self.device)
+        num_pages = engine_config.num_kvcache_blocks
+        if num_pages <= 0:
+            num_pages = self._pages_from_free_memory(needs)
+        self.cache = CacheManager(needs, self.page_size, num_pages, engine_config.max_num_seqs,
+                                  prefix_caching=engine_config.enable_prefix_caching)
+        self.storage = CacheStorage(self.cache, self.dtype, self.device)
+        self.memory["cache"] = self.storage.bytes()
+        self.builder = StepBuilder(self.cache, self.device, self.spec.vocab_size, self.status)
+        self.steps_run = 0
 
     # ------------------------------------------------------------------ sizing
 
-    def _pages_from_free_memory(self, probe: CacheManager) -> int:
-        """Pages per group from the memory that is left: the reference's rule
-        (atom/model_engine/model_runner.py:1591-1611) without its warm-up measurement; the
-        activations of the largest step are estimated from the token budget instead."""
-        free, total = torch.cuda.mem_get_info(self.device)
+    def _largest_step(self) -> List[int]:
+        """Token counts of the requests of the largest step the scheduler can make."""
+        budget = min(self.cfg.max_num_batched_tokens, self.cfg.max_num_seqs * self.max_model_len)
+        lens = []
+        while budget > 0 and len(lens) < self.cfg.max_num_seqs:
+            n = min(budget, self.max_model_len)
+            lens.append(n)
+            budget -= n
+        return lens
+
+    def _graph_memory_bound(self, eager_ws_bytes: int, largest_tokens: int) -> int:
+        """Device memory that the graphs captured after the cache is made will take: their shared logits
+        and workspace, the fixed-shape step arrays, and the graph objects themselves."""
+        if not self.graphs_enabled:
+            return 0
+        max_batch = min(self.cfg.max_num_seqs, self.cfg.max_num_batched_tokens)
+        sizes = [b for b in self._graph_sizes if b < max_batch] + [next((b for b in self._graph_sizes if b >= max_batch), 0)]
+        rows = max(sizes + ([_MIXED_SEQS[-1]] if self.mixed_graphs else []))
+        tokens = max(sizes + ([self._mixed_tokens[-1]] if self.mixed_graphs else []))
+        logits = rows * self.spec.vocab_size * 4
+        workspace = int(eager_ws_bytes * min(1.0, 1.25 * tokens / max(largest_tokens, 1))) + (64 << 20)
+        groups = max(1, len({n.group_key() for n in self.model.cache_needs().values() if n.kind == "pages"}))
+        shapes = [(b, b) for b in sizes if b]
+        if self.mixed_graphs:
+            shapes += [(t, n) for n in _MIXED_SEQS for t in self._mixed_tokens]
+        arrays = sum(4 * (3 * t + 4 * n + 16 + groups * n * self._table_width) for t, n in shapes)
+        objects = (128 << 20) + len(shapes) * 3 * (1 << 20)
+        return logits + workspace + arrays + objects
+
+    def _pages_from_free_memory(self, needs) -> int:
+        """Pages per group from the memory that is left after a warm-up step of the largest size the
+        scheduler can make (the reference measures the same way, after a warm-up prefill, and takes
+        an estimate for its graphs off: atom/model_engine/model_runner.py:1584-1611).  The warm-up
+        runs against a cache of its own, just large enough, which is given back; the activation
+        buffers it sized stay, so later steps allocate nothing."""
+        lens = self._largest_step()
+        pages = sum(-(-n // self.page_size) for n in lens) + 1
+        probe = CacheManager(needs, self.page_size, pages, len(lens))
         per_page = CacheStorage.bytes_per_page(probe, self.dtype)
         if per_page == 0:
             return 1
-        es = 4 if self.dtype == torch.float32 else 2
-        # Every matrix product of a layer writes one [tokens, out] buffer; buffers are shared
-        # between layers, so the widest layer decides.
-        per_layer: Dict[str, int] = {}
-        for path, part, _ in self.model.named_parts():
-            if path.startswith("layers."):
-                key = path.split(".")[1]
-                per_layer[key] = per_layer.get(key, 0) + sum(
-                    ps.shape[0] for ps in part.params().values() if ps.role == "matrix")
-        widest = max(per_layer.values(), default=0) + 4 * self.spec.hidden_size
-        act = self.cfg.max_num_batched_tokens * (widest * es * 3 // 2 + self.spec.hidden_size * 8)
-        logits = min(self.cfg.max_num_seqs, self.cfg.max_num_batched_tokens) * self.spec.vocab_size * 4 * 2
-        budget = total * self.cfg.gpu_memory_utilization - (total - free) - act - logits - 0.02 * total
+        storage = CacheStorage(probe, self.dtype, self.device)
+        builder = StepBuilder(probe, self.device, self.spec.vocab_size, self.status)
+        entries = [StepEntry(("warm-up", i), [0] * n, (n - 1,)) for i, n in enumerate(lens)]
+        for e in entries:
+            probe.admit(e.rid)
+            probe.extend(e.rid, len(e.tokens))
+        with torch.no_grad():
+            self.model.forward(builder.build(entries, [len(e.tokens) for e in entries]), storage)
+        torch.cuda.synchronize(self.device)
+        self.check_status()
+        ws_bytes = self.rt.workspace.bytes()
+        del storage, builder, probe
+        torch.cuda.empty_cache()
+        free, total = torch.cuda.mem_get_info(self.device)
+        reserve = self._graph_memory_bound(ws_bytes, sum(lens))
+        self.memory.update(activations=ws_bytes, graph_reserve=reserve, in_use_before_cache=total - free)
+        budget = total * self.cfg.gpu_memory_utilization - (total - free) - reserve
         n = int(budget // per_page)
         if n < 1:
             raise RuntimeError("no device memory left for the cache")
@@ -122,19 +165,33 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
 
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        """Everything about a step that can be refused is refused here, before a page is taken: a
+        step that raises StepError leaves the cache as it was."""
+        seen = set()
+        V = self.spec.vocab_size
+        for e in entries:
+            if e.rid in seen:
+                raise StepError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.rid!r} brings no tokens")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its {n} tokens")
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.ndim != 1 or toks.min() < 0 or toks.max() >= V:
+                raise StepError(f"request {e.rid!r}: token id outside [0, {V})")
+            e.tokens = toks       # (the arrays are built from this copy)
+
     def _reserve(self, entries: Sequence[StepEntry]) -> List[int]:
         """Admits new requests and takes the pages this step needs; all or nothing."""
         cache = self.cache
         need_total: Dict[int, int] = {}
         new_slots = 0
         targets = []
-        seen = set()
         for e in entries:
-            if e.rid in seen:
-                raise StepError(f"request {e.rid!r} appears twice in one step")
-            seen.add(e.rid)
-            if len(e.tokens) == 0:
-                raise StepError(f"request {e.rid!r} brings no tokens")
             known = e.rid in cache.requests
             start = cache.committed(e.rid) if known else 0
             target = start + len(e.tokens)
@@ -170,9 +227,10 @@ class ModelRunner:
         is launched."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        targets = self._reserve(entries)
+        self._validate(entries)
         size = self._graph_size(entries)
-        shape = None if size or device_tokens is not None else self._mixed_shape(entries)
+        if size and any(tuple(e.want) not in ((), (0,)) for e in entries):
+            size = 0          # (a row wanted twice: the general path takes any list)
         if device_tokens is not None:
             rows = None if device_token_rows is None else [int(r) for r in device_token_rows]
             n_src = device_tokens.numel()
@@ -180,6 +238,9 @@ class ModelRunner:
                     n_src != len(entries) if rows is None
                     else len(rows) != len(entries) or any(not 0 <= r < n_src for r in rows)):
                 raise StepError("device_tokens needs a captured decode step and one int32 token per entry")
+        targets = self._reserve(entries)
+        shape = None if size or device_tokens is not None else self._mixed_shape(entries)
+        if device_tokens is not None:
             logits = self._step_graph(entries, targets, size, device_tokens, rows)
         elif size:
             logits = self._step_graph(entries, targets, size)
@@ -198,7 +259,7 @@ class ModelRunner:
         """Bytes of step metadata copied host -> device so far."""
         return self.builder.h2d_bytes
 
-    # ------------------------------------------------------------------ captured decode steps
+    # ------------------------------------------------------------------ captured steps
 
     def _graph_size(self, entries: Sequence[StepEntry]) -> int:
         """The captured batch size a step replays, 0 if it runs eagerly: every request brings
@@ -224,85 +285,62 @@ class ModelRunner:
             return None
         return (next(t for t in self._mixed_tokens if t >= T), next(n for n in _MIXED_SEQS if n >= S))
 
-    def _capture_mixed(self, shape) -> "_DecodeGraph":
-        """As ``_capture``, for a step of ``shape`` = (tokens, requests) of any makeup: launch plans are
-        made for every batch that fits the shape, and for the longest request the engine takes."""
-        tokens, seqs = shape
-        g = _DecodeGraph()
-        g.workspace = Workspace(self.device)
-        g.logits = torch.empty((seqs, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        saved = self.rt.workspace
-        self.rt.workspace = g.workspace
-        try:
-            def run():
-                ctx = self.builder.fixed_context_mixed(tokens, seqs, self._table_width, self.max_model_len)
-                ctx.logits_out = g.logits
-                self.model.forward(ctx, self.storage)
+    def _context_class(self, longest: int) -> int:
+        """Launch plans of a captured step are made for a longest context; steps replay the graph of
+        the class their own longest context falls into: 256, 1024, 4096, ... up to max_model_len."""
+        c = 256
+        while c < longest:
+            c *= 4
+        return min(c, max(self.max_model_len, 1))
 
-            self.builder.build_fixed_mixed([], [], tokens, seqs, self._table_width)   # all padding
-            run()
-            torch.cuda.current_stream().synchronize()
-            g.graph = torch.cuda.CUDAGraph()
-            before = native.launches
-            with torch.cuda.graph(g.graph):
-                run()
-            g.num_launches = native.launches - before
-            g.workspace.frozen = True
-        finally:
-            self.rt.workspace = saved
+    @property
+    def graph_shapes(self) -> set:
+        """Shapes (batch sizes and (tokens, requests) pairs) that have a captured graph."""
+        return {k[0] for k in self._graphs}
+
+    def _fixed_context(self, shape, ctx_class: int):
+        if isinstance(shape, tuple):
+            return self.builder.fixed_context_mixed(shape[0], shape[1], self._table_width, ctx_class)
+        return self.builder.fixed_context(shape, self._table_width, ctx_class)
+
+    def _graph_for(self, shape, longest: int) -> "_DecodeGraph":
+        """The graph of ``shape`` (a batch size, or (tokens, requests)) for steps whose longest context is
+        ``longest``, captured now if no step has needed it yet.  Context classes whose launch plans come
+        out equal share one graph."""
+        cls = self._context_class(longest)
+        key = self._graph_keys.get((shape, cls))
+        if key is None:
+            key = self._graph_keys[(shape, cls)] = (shape, self.model.plan_signature(self._fixed_context(shape, cls)))
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = self._capture(shape, cls)
         return g
 
-    def _step_mixed_graph(self, entries: Sequence[StepEntry], targets: List[int], shape) -> torch.Tensor:
-        g = self._graphs.get(shape)
-        if g is None:
-            g = self._graphs[shape] = self._capture_mixed(shape)
-        self.builder.build_fixed_mixed(entries, targets, shape[0], shape[1], self._table_width)
-        g.graph.replay()
-        native.add_launches(g.num_launches)
-        self.graph_replays += 1
-        return g.logits[: sum(len(e.want) for e in entries)]       # valid until the next step of this shape
-
-    def capture_graphs(self, max_batch: int) -> list:
-        """Captures, ahead of the first request, the decode graphs that batches of up to
-        ``max_batch`` requests replay (the reference captures all of its sizes at start,
-        atom/model_engine/model_runner.py capture_cudagraph); without this call a size is
-        captured when a step first needs it.  Returns the sizes captured now."""
-        done = []
-        if not self.graphs_enabled:
-            return done
-        for b in self._graph_sizes:
-            if b not in self._graphs:
-                self._graphs[b] = self._capture(b)
-                done.append(b)
-            if b >= max_batch:
-                break
-        if self.mixed_graphs:      # (a capture in the middle of serving would stall a step by ~0.1 s)
-            for n in _MIXED_SEQS:
-                for t in self._mixed_tokens:
-                    if (t, n) not in self._graphs:
-                        self._graphs[(t, n)] = self._capture_mixed((t, n))
-                        done.append((t, n))
-                if n >= max_batch:
-                    break
-        return done
-
-    def _capture(self, size: int) -> "_DecodeGraph":
-        """Runs a decode step of ``size`` padding rows once eagerly (loads kernels, sizes the
-        buffers), then records the same launches into a graph.  The graph has its own
-        activation buffers and logits, so steps of other shapes cannot move them."""
+    def _capture(self, shape, ctx_class: int) -> "_DecodeGraph":
+        """Runs a step of ``shape`` made of padding alone once eagerly (loads kernels, sizes the
+        buffers), then records the same launches into a graph.  Graphs write their activations to a
+        workspace and their logits to a buffer that all graphs of this runner share."""
+        mixed = isinstance(shape, tuple)
+        rows = shape[1] if mixed else shape
         g = _DecodeGraph()
-        g.workspace = Workspace(self.device)
-        g.logits = torch.empty((size, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        if self._graph_logits is None or self._graph_logits.shape[0] < rows:
+            max_batch = min(self.cfg.max_num_seqs, self.cfg.max_num_batched_tokens)
+            most = max([b for b in self._graph_sizes if b <= max(rows, max_batch)] + [rows] +
+                       ([_MIXED_SEQS[-1]] if self.mixed_graphs else []))
+            self._graph_logits = torch.empty((most, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        g.logits = self._graph_logits
         saved = self.rt.workspace
-        self.rt.workspace = g.workspace
+        self.rt.workspace = self._graph_ws
         try:
             def run():
-                # launch plans are made for the longest request the engine takes
-                ctx = self.builder.fixed_context(size, self._table_width, self.max_model_len)
+                ctx = self._fixed_context(shape, ctx_class)
                 ctx.logits_out = g.logits
                 self.model.forward(ctx, self.storage)
 
-            self.builder.build_fixed([], [], size, self._table_width)   # all rows padding
+            if mixed:
+                self.builder.build_fixed_mixed([], [], shape[0], shape[1], self._table_width)   # all padding
+            else:
+                self.builder.build_fixed([], [], shape, self._table_width)
             run()
             torch.cuda.current_stream().synchronize()
             g.graph = torch.cuda.CUDAGraph()
@@ -310,17 +348,59 @@ class ModelRunner:
             with torch.cuda.graph(g.graph):
                 run()
             g.num_launches = native.launches - before     # own kernels recorded in the graph
-            g.workspace.frozen = True
         finally:
             self.rt.workspace = saved
         return g
 
+    def capture_graphs(self, max_batch: int) -> list:
+        """Captures, ahead of the first request, the graphs that steps of up to ``max_batch`` requests
+        replay (the reference captures all of its sizes at start, atom/model_engine/model_runner.py
+        capture_cudagraph), for every context class up to max_model_len; without this call a graph is
+        captured when a step first needs it (which stalls that step by ~0.1 s).  The largest shapes
+        come first, so that the shared buffers are sized once.  Returns the keys captured now."""
+        done = []
+        if not self.graphs_enabled:
+            return done
+        free0 = torch.cuda.mem_get_info(self.device)[0]
+        shapes: list = []
+        for b in self._graph_sizes:
+            shapes.append(b)
+            if b >= max_batch:
+                break
+        if self.mixed_graphs:
+            for n in _MIXED_SEQS:
+                shapes += [(t, n) for t in self._mixed_tokens]
+                if n >= max_batch:
+                    break
+        classes, c = [], 256
+        while True:
+            classes.append(self._context_class(c))
+            if c >= self.max_model_len:
+                break
+            c *= 4
+        shapes.sort(key=lambda sh: (sh[0] if isinstance(sh, tuple) else sh), reverse=True)
+        for sh in shapes:
+            for c in sorted(set(classes), reverse=True):
+                n = len(self._graphs)
+                self._graph_for(sh, c)
+                if len(self._graphs) > n:
+                    done.append((sh, c))
+        torch.cuda.synchronize(self.device)
+        self.memory["graphs"] = free0 - torch.cuda.mem_get_info(self.device)[0]
+        return done
+
+    def _step_mixed_graph(self, entries: Sequence[StepEntry], targets: List[int], shape) -> torch.Tensor:
+        g = self._graph_for(shape, max(targets))
+        self.builder.build_fixed_mixed(entries, targets, shape[0], shape[1], self._table_width)
+        g.graph.replay()
+        native.add_launches(g.num_launches)
+        self.graph_replays += 1
+        return g.logits[: sum(len(e.want) for e in entries)]       # valid until the next captured step
+
     def _step_graph(self, entries: Sequence[StepEntry], targets: List[int], size: int,
                     device_tokens: Optional[torch.Tensor] = None,
                     device_token_rows: Optional[List[int]] = None) -> torch.Tensor:
-        g = self._graphs.get(size)
-        if g is None:
-            g = self._graphs[size] = self._capture(size)
+        g = self._graph_for(size, max(targets))
         ctx = self.builder.build_fixed(entries, targets, size, self._table_width, device_token_rows)
         if device_tokens is not None:          # on the stream, after the arrays' copy
             if device_token_rows is not None:
@@ -329,14 +409,9 @@ class ModelRunner:
         g.graph.replay()
         native.add_launches(g.num_launches)
         self.graph_replays += 1
-        rows = []
-        for i, e in enumerate(entries):
-            for w in e.want:
-                if w != 0:
-                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its 1 token")
-                rows.append(i)
+        rows = [i for i, e in enumerate(entries) if len(e.want)]
         if rows == list(range(len(entries))):
-            return g.logits[: len(entries)]       # valid until the next step of this size
+            return g.logits[: len(entries)]       # valid until the next captured step
         if not rows:
             return g.logits[:0]
         return g.logits[torch.tensor(rows, device=self.device)]
@@ -347,9 +422,16 @@ class ModelRunner:
             self.cache.release(rid)
 
     def check_status(self) -> None:
-        """Raises if a kernel met a position without a page (synchronises the device)."""
-        self._status_host.copy_(self.status)
-        torch.cuda.current_stream().synchronize()
-        if int(self._status_host[0]) != 0:
-            raise StepError("a kernel found a token position without a cache page")
-        native.check_error_flags()
+        """Raises if a kernel met a position without a page or gave up a bounded wait since the
+        last check (synchronises the device)."""
+        try:
+            native.check_error_flags()
+        except native.NativeError as e:
+            raise StepError(str(e)) from e
+
+    def raise_for_flags(self, values: Sequence[int]) -> None:
+        """``values``: a host copy of ``self.flags`` taken after a step.  Raises, and clears the device
+        flags, if one is set: the step's results (and the cache) are not to be trusted."""
+        if any(values):
+            self.flags.zero_()
+            raise StepError("; ".join(m for m, x in zip(native.FLAG_MESSAGES, values) if x))

@@ -78,29 +78,26 @@ class Scheduler:
     def is_finished(self) -> bool:
         return not self.waiting and not self.running
 
-    def abort(self, seq_id: int) -> Optional[Sequence]:
+    def abort(self, seq_id: int, reason: str = "aborted") -> Optional[Sequence]:
         for q in (self.running, self.waiting):
             for s in list(q):
                 if s.seq_id == seq_id:
                     q.remove(s)
                     if seq_id in self.cache.requests:
                         self.cache.release(seq_id)
-                    self._finish(s, "aborted", release=False)
+                    self._finish(s, reason, release=False)
                     return s
         return None
 
     # ------------------------------------------------------------------ one step
 
     def _unschedulable_reason(self, seq: Sequence) -> Optional[str]:
-        # The request must be able to grow to its last token.
-        final = seq.num_prompt_tokens + seq.params.max_tokens
         if seq.num_tokens > self.max_model_len:
             return f"unschedulable: {seq.num_tokens} tokens exceed max_model_len {self.max_model_len}"
         if not self.cache.fits_at_all(seq.num_tokens + 1, self.portion_cap):
             return "unschedulable: the request needs more cache pages than the pool has"
         if not self.enable_chunked_prefill and seq.num_tokens > self.max_num_batched_tokens:
             return "unschedulable: the prompt exceeds max_num_batched_tokens and portions are off"
-        del final
         return None
 
     def _preempt(self, seq: Sequence, step: ScheduledStep) -> None:

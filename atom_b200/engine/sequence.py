@@ -16,13 +16,10 @@ class SequenceStatus(enum.Enum):
 
 
 class Sequence:
-    _next_id = 0
-
-    def __init__(self, prompt_token_ids: List[int], params: SamplingParams, seq_id: Optional[int] = None,
+    def __init__(self, prompt_token_ids: List[int], params: SamplingParams, seq_id: int,
                  stop_token_sequences: Optional[List[List[int]]] = None, sibling_index: int = 0):
-        if seq_id is None:
-            seq_id = Sequence._next_id
-            Sequence._next_id += 1
+        # The id comes from whoever owns the request (an engine counts its own requests from 0): it
+        # feeds the default random seed, so it must not depend on what else ran in the process.
         self.seq_id = seq_id
         self.token_ids: List[int] = list(prompt_token_ids)
         self.num_prompt_tokens = len(self.token_ids)

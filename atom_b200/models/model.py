@@ -86,6 +86,16 @@ class Model:
             part.bind(own, rt)
         if getattr(self.lm_head, "tied", False):
             self.lm_head.tie(self.embedding)
+        for _, part, _ in self._named:
+            part.after_load()
+
+    def plan_signature(self, step) -> tuple:
+        """What the parts' launch plans for ``step`` are, as one hashable value: two steps of one shape
+        with equal signatures launch the same kernels with the same arguments."""
+        step.plans.clear()
+        for _, part, _ in self._named:
+            part.launch_plan(step)
+        return tuple(sorted(step.plans.items(), key=repr))
 
     # ------------------------------------------------------------------ compute
 

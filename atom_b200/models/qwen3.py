@@ -119,6 +119,15 @@ class Qwen3Config(ModelConfig):
                         "is not a positive int"
                     )
             layer_types = tuple(layer_types)
+        if layer_types is None and d.get("use_sliding_window") is True and window is not None:
+            # The older spelling (a window from layer 'max_window_layers' on) is resolved by the
+            # library that reads config.json for the reference, which itself looks at
+            # 'layer_types' alone (atom/models/llama.py:187-191).  Running such a file with full
+            # attention in every layer would be silently wrong, so it is refused.
+            raise ConfigError(
+                "config.json: 'use_sliding_window' is true but 'layer_types' is missing; name the layers "
+                "that use the window in 'layer_types' ('max_window_layers' alone is not read)"
+            )
         if layer_types is None or "sliding_attention" not in layer_types:
             window = None
 
@@ -254,6 +263,9 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
         ),
         # atom/model_loader/weight_names.py:171 drops rotary inv_freq buffers.
         ignored_tensors=(r".*rotary_emb\.inv_freq$",),
+        # Tied checkpoints often carry the output matrix as well; it must then be the embedding
+        # table (the reference aliases the two, atom/models/qwen3.py:339-340).
+        duplicate_tensors=(("lm_head.weight", "model.embed_tokens.weight"),) if cfg.tie_word_embeddings else (),
         eos_token_ids=cfg.eos_token_ids,
     )
 

@@ -71,6 +71,8 @@ _SIGNATURES = {
     "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i64, _vp],
     "atom_gemm_smallm_scratch_bytes": [_i],
     "atom_gemm_smallm_supports": [_i, _i, _i, _i64],
+    "atom_set_option": [_i, _i],
+    "atom_copy_rows_h2d": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
 }
 
 
@@ -90,6 +92,42 @@ def declare(name: str, args) -> None:
         fn = getattr(_lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
+
+
+# Choices the launch code otherwise makes by itself (csrc/common.cuh, ATOM_OPT_*): for measurements
+# and for tests of both sides of a choice.  They hold for launches made after the call; a captured
+# graph keeps what it was recorded with.
+OPTIONS = {"pdl": 0, "decode_tma": 1, "decode_ktw": 2, "gemm_row_tile": 3, "gemm_cut": 4}
+_option_values = {}
+
+
+def set_option(name: str, value: int) -> None:
+    """Sets an option in every loaded library of the package (and in those loaded later)."""
+    key = OPTIONS[name]
+    _option_values[key] = int(value)
+    if lib().atom_set_option(key, int(value)) != 0:
+        raise NativeError(f"option {name!r} was refused")
+    for l in _flash_libs.values():
+        l.atom_flash_set_option(key, int(value))
+
+
+def reset_options() -> None:
+    for name, default in (("pdl", 1), ("decode_tma", 1), ("decode_ktw", 0), ("gemm_row_tile", 0), ("gemm_cut", -1)):
+        set_option(name, default)
+    _option_values.clear()
+
+
+def copy_rows_h2d(dst: torch.Tensor, dst_pitch: int, src: torch.Tensor, src_pitch: int, row_elems: int,
+                  rows: int) -> None:
+    """rows x row_elems elements from pinned host memory (rows src_pitch elements apart) to the device
+    (rows dst_pitch elements apart), asynchronously on the current stream."""
+    es = dst.element_size()
+    assert dst.is_cuda and not src.is_cuda and src.element_size() == es     # (src: pinned memory)
+    assert rows == 0 or (dst.numel() >= (rows - 1) * dst_pitch + row_elems and src.numel() >= (rows - 1) * src_pitch + row_elems)
+    code = lib().atom_copy_rows_h2d(dst.data_ptr(), dst_pitch * es, src.data_ptr(), src_pitch * es, row_elems * es,
+                                    rows, _stream())
+    if code != 0:
+        raise NativeError(f"copy_rows_h2d: {_ERR.get(code, code)}")
 
 
 def _check(code: int, name: str, own: bool = True) -> None:
@@ -263,16 +301,30 @@ def gemm_bf16(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
            own=False)
 
 
-_error_flags = {}
+_device_flags = {}
+
+
+def device_flags(device: torch.device) -> torch.Tensor:
+    """Two device ints that kernels raise and the host reads after a step (0: all well):
+    [0] a bounded wait ran out, [1] a token position had no cache page."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    f = _device_flags.get(key)
+    if f is None:
+        f = _device_flags[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return f
 
 
 def error_flag(device: torch.device) -> torch.Tensor:
-    """A device int that kernels with bounded waits set when a wait ran out (0: all well)."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    f = _error_flags.get(key)
-    if f is None:
-        f = _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return f
+    """The device int that kernels with bounded waits set when a wait ran out."""
+    return device_flags(device)[0:1]
+
+
+def status_flag(device: torch.device) -> torch.Tensor:
+    """The device int that kernels set when they meet a token position without a cache page."""
+    return device_flags(device)[1:2]
+
+
+FLAG_MESSAGES = ("a kernel's bounded wait ran out", "a kernel found a token position without a cache page")
 
 
 def flash_has_tc(hd: int) -> bool:
@@ -281,14 +333,16 @@ def flash_has_tc(hd: int) -> bool:
 
 
 def check_error_flags() -> None:
-    """Raises if a kernel gave up a bounded wait (synchronises the device)."""
-    for hd, l in _flash_libs.items():
+    """Raises if a kernel gave up a bounded wait or met a position without a page (synchronises the
+    device); the flags are cleared, so the next check speaks of what ran after this one."""
+    for f in _device_flags.values():
+        v = f.tolist()
+        if any(v):
+            f.zero_()
+            raise NativeError("; ".join(m for m, x in zip(FLAG_MESSAGES, v) if x))
+    for hd, l in _flash_libs.items():      # (a device on which the library still uses its own flag)
         if l.atom_flash_take_error() != 0:
             raise NativeError(f"a bounded wait of the attention kernels (head size {hd}) ran out")
-    for f in _error_flags.values():
-        if int(f.item()) != 0:
-            f.zero_()
-            raise NativeError("a kernel's bounded wait ran out (device error flag set)")
 
 
 SMALL_M = 8     # rows up to which the weight-streaming product beats the library's (measured)
@@ -368,6 +422,16 @@ def flash_lib(hd: int):
                 l.atom_flash_has_tc.restype = ctypes.c_int
                 if l.atom_flash_head_dim() != hd:
                     raise NativeBuildError(f"{path} was built for another head size")
+                # bounded waits of this library report into the device's shared flag word, which the
+                # engine reads back with every step's tokens (other devices keep the library's own flag)
+                l.atom_flash_set_option.argtypes = [_i, _i]
+                l.atom_flash_set_option.restype = ctypes.c_int
+                for k, v in _option_values.items():
+                    l.atom_flash_set_option(k, v)
+                l.atom_flash_set_error_flag.argtypes = [_vp]
+                l.atom_flash_set_error_flag.restype = ctypes.c_int
+                if torch.cuda.is_available():
+                    l.atom_flash_set_error_flag(error_flag(torch.device("cuda", torch.cuda.current_device())).data_ptr())
                 _flash_libs[hd] = l
     return l
 

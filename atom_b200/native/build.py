@@ -142,10 +142,13 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str], 
     hdr = _headers_hash()
     if not srcs:
         raise NativeBuildError(f"no .cu sources under {CSRC}")
+    # An object is named <source>.<defines>.<hash>.o, so that the objects of older versions of
+    # the same source and variant can be told from those of other variants and removed.
+    tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items())) or "core"
     objs, todo = [], []
     for s in srcs:
         key = _source_key(s, hdr, flags)
-        obj = os.path.join(bdir, f"{os.path.splitext(s)[0]}.{key}.o")
+        obj = os.path.join(bdir, f"{os.path.splitext(s)[0]}.{tag}.{key}.o")
         objs.append(obj)
         if not os.path.isfile(obj):
             todo.append((s, obj))
@@ -186,15 +189,7 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str], 
         if todo:
             with concurrent.futures.ThreadPoolExecutor(workers) as ex:
                 list(ex.map(compile_one, todo))
-        # Remove objects of older versions of these sources.
-        keep = {os.path.basename(o) for o in objs}
-        stems = {os.path.splitext(x)[0] for x in srcs}
-        for f in os.listdir(bdir):
-            if f.endswith(".o") and f not in keep and f.split(".")[0] in stems and len(stems) > 1:
-                try:
-                    os.remove(os.path.join(bdir, f))
-                except OSError:
-                    pass
+        _prune(bdir, srcs, tag, {os.path.basename(o) for o in objs})
         tmp = lib + f".tmp{os.getpid()}"
         cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
         _run([nvcc, "-shared", "-o", tmp] + objs + ["-L", cuda_lib] + link_libs, "link")
@@ -206,6 +201,22 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str], 
     if verbose:
         _log(f"built {lib_name} in {time.time() - t0:.1f} s")
     return lib
+
+
+def _prune(bdir: str, srcs: Sequence[str], tag: str, keep: set) -> None:
+    """Removes the objects of older versions of these sources in this variant, and objects
+    named in an older scheme (<source>.<hash>.o) whatever they belonged to."""
+    stems = {os.path.splitext(x)[0] for x in srcs}
+    for f in os.listdir(bdir):
+        if not f.endswith(".o") or f in keep:
+            continue
+        parts = f.split(".")
+        stale = (len(parts) == 4 and parts[0] in stems and parts[1] == tag) or len(parts) == 3
+        if stale:
+            try:
+                os.remove(os.path.join(bdir, f))
+            except OSError:
+                pass
 
 
 # Head sizes whose attention variant the build check compiles ahead of use.

@@ -1013,18 +1013,27 @@ namespace atom {
 namespace flash {
 // Raised by a kernel of this library whose bounded wait ran out.
 static __device__ int g_error_flag;
+static int* g_error_addr[64] = {};      // per device: the caller's flag if it gave one, else this library's own
 static int* error_flag_address() {
-  static int* addr[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (addr[dev] == nullptr && cudaGetSymbolAddress((void**)&addr[dev], g_error_flag) != cudaSuccess) {
+  if (g_error_addr[dev] == nullptr && cudaGetSymbolAddress((void**)&g_error_addr[dev], g_error_flag) != cudaSuccess) {
     (void)cudaGetLastError();
     return nullptr;
   }
-  return addr[dev];
+  return g_error_addr[dev];
 }
 }  // namespace flash
 }  // namespace atom
+
+// From now on the kernels launched on the current device raise ``flag`` (a device int that outlives
+// them) instead of the library's own word; nullptr goes back to the library's own.
+ATOM_EXPORT int atom_flash_set_error_flag(int* flag) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return ATOM_ERR_LAUNCH;
+  atom::flash::g_error_addr[dev] = flag;
+  return ATOM_OK;
+}
 
 // Reads and clears the error flag of this library on the current device (synchronises): 0 if all is well.
 ATOM_EXPORT int atom_flash_take_error() {
@@ -1037,6 +1046,9 @@ ATOM_EXPORT int atom_flash_take_error() {
   }
   return v;
 }
+
+// Sets one of the ATOM_OPT_* options (common.cuh) in this library.
+ATOM_EXPORT int atom_flash_set_option(int key, int value) { return atom::set_option(key, value); }
 
 // 1 if this library has the tcgen05 kernel for long portions (head size 128).
 ATOM_EXPORT int atom_flash_has_tc() {
@@ -1169,7 +1181,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
     bool tma_done = false;
 #if ATOM_HD % 64 == 0
     // One TMA box per page needs pages of a power of two >= 8 tokens and the size of the page matrices.
-    static const bool tma_off = [] { const char* e = getenv("ATOM_DECODE_TMA"); return e != nullptr && e[0] == '0'; }();
+    const bool tma_off = atom::options().v[ATOM_OPT_DECODE_TMA] == 0;
     const uint64_t page_rows = (uint64_t)num_pages * nkv * page_size;
     if (!tma_off && p.page_shift >= 3 && num_pages > 0 && page_rows < 0x7fffffffull && p.error != nullptr) {
       // 32-key warp tiles where every CTA has an SM to itself (and they fit), else 16-key tiles and two CTAs an SM.
@@ -1180,7 +1192,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
           return ATOM_ERR_LAUNCH;
       }
-      static const int forced = [] { const char* e = getenv("ATOM_DECODE_KTW"); return e ? atoi(e) : 0; }();
+      const int forced = atom::options().v[ATOM_OPT_DECODE_KTW];
       const bool wide = decode_tma_fits(32) && (forced == 32 || (forced != 16 && (int64_t)num_seqs * nkv * num_splits <= sms));
       const int ktw = wide ? 32 : 16;
       const uint32_t box_rows = page_size < ktw ? page_size : ktw;

@@ -88,18 +88,35 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 //   * every path through a kernel passes pdl_wait() before it ends (in at least one thread of
 //     every CTA that could otherwise be the last to finish: simplest, before every early
 //     return), so that a completed grid means that everything before it has completed too.
-// Set ATOM_PDL=0 in the environment for plain launches.
+// Option ATOM_OPT_PDL = 0 gives plain launches.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-inline bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("ATOM_PDL");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return v != 0;
+// ------------------------------------------------------------------ options for measurements and tests
+// Choices that the launch code otherwise makes by itself, overridable per process so that both sides
+// of a choice can be measured and tested in one run.  Every library built from these sources has its
+// own copy, set through its exported set-option function (the Python binding sets all of them).  The
+// environment is never read.
+#define ATOM_OPT_PDL 0            // 1 (default): programmatic dependent launch; 0: plain launches
+#define ATOM_OPT_DECODE_TMA 1     // 1 (default): decode attention through TMA where it applies; 0: cp.async kernel
+#define ATOM_OPT_DECODE_KTW 2     // 0 (default): warp tile of the TMA decode kernel by occupancy; 16 or 32: forced
+#define ATOM_OPT_GEMM_ROW_TILE 3  // 0 (default): row tile of the streaming product by shape; 1, 2, 4: forced
+#define ATOM_OPT_GEMM_CUT 4       // -1 (default): ranges cut inside slabs where a CTA streams much; 0 never; 1 always
+#define ATOM_OPT_COUNT 5
+struct Options {
+  int v[ATOM_OPT_COUNT] = {1, 1, 0, 0, -1};
+};
+inline Options& options() {
+  static Options o;
+  return o;
 }
+inline int set_option(int key, int value) {
+  if (key < 0 || key >= ATOM_OPT_COUNT) return ATOM_ERR_ARG;
+  options().v[key] = value;
+  return ATOM_OK;
+}
+
+inline bool pdl_enabled() { return options().v[ATOM_OPT_PDL] != 0; }
 
 template <typename... KArgs, typename... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

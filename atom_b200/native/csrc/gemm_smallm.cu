@@ -548,10 +548,10 @@ static int launch_mt(const Params& p, const void* X, int64_t lda, const void* W,
                      cudaStream_t stream) {
   const int G = sm_count();
   int rt = 2;
-  static const int forced = [] { const char* e = getenv("ATOM_GEMM_RT"); return e ? atoi(e) : 0; }();
+  const int forced = atom::options().v[ATOM_OPT_GEMM_ROW_TILE];
   // Ranges cut inside slabs pay where a CTA streams much (the settling of a shared slab costs a few
   // microseconds of its consumers' time): measured better from about half a megabyte of W per CTA.
-  static const int mode = [] { const char* e = getenv("ATOM_GEMM_STREAMK"); return e ? atoi(e) : -1; }();
+  const int mode = atom::options().v[ATOM_OPT_GEMM_CUT];
   const double w_bytes_per_cta = 2.0 * (p.gated ? 2.0 : 1.0) * p.N * (double)p.K / G;
   const bool cut = mode < 0 ? w_bytes_per_cta >= 512.0 * 1024 : mode != 0;
   if (!cut) scratch = nullptr;

@@ -83,25 +83,32 @@ class PagedAttention(Mixer):
         self.attend(o, qkv, step, cache, bt)
         return linear(o, self.w_o_weight, None, ws.get("attn.out", (T, self.hidden_size), dt))
 
+    def launch_plan(self, step):
+        """The attention kernels' plan for this step: tile counts and the number of splits along the
+        keys, from the step's shape and its longest context.  Layers of equal sizes share it."""
+        if not native.flash_supports(self.hd, self.rt.dtype):
+            return None
+        if self._long_rows is None:
+            self._long_rows = native.LONG_ROWS if (not self.window and native.flash_has_tc(self.hd)) else 0
+        long_rows = self._long_rows
+        key = ("flash", self.nh, self.nkv, long_rows)
+        plan = step.plans.get(key)
+        if plan is None:
+            if step.plan_for_any_batch:
+                plan = native.flash_plan_for_any(step.num_tokens, step.num_seqs, self.nh // self.nkv, self.nkv,
+                                                 step.max_ctx_len, long_rows=long_rows)
+            else:
+                plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
+                                         long_rows=long_rows)
+            step.plans[key] = plan
+        return plan
+
     def attend(self, o, qkv, step, cache, bt) -> None:
         """Chooses the attention kernel for this step's tokens: the tensor-core kernel for
         bfloat16 and head sizes in steps of 16, else the 32-bit kernel that takes any size."""
         if native.flash_supports(self.hd, qkv.dtype):
             T = o.shape[0]
-            # the plan depends on the step's shape and on these sizes: layers that share them share it
-            if self._long_rows is None:
-                self._long_rows = native.LONG_ROWS if (not self.window and native.flash_has_tc(self.hd)) else 0
-            long_rows = self._long_rows
-            key = ("flash", self.nh, self.nkv, long_rows)
-            plan = step.plans.get(key)
-            if plan is None:
-                if step.plan_for_any_batch:
-                    plan = native.flash_plan_for_any(step.num_tokens, step.num_seqs, self.nh // self.nkv, self.nkv,
-                                                     step.max_ctx_len, long_rows=long_rows)
-                else:
-                    plan = native.flash_plan(step.q_lens, self.nh // self.nkv, self.nkv, step.max_ctx_len,
-                                             long_rows=long_rows)
-                step.plans[key] = plan
+            plan = self.launch_plan(step)
             scratch = None
             if plan[2] > 1:
                 n = native.flash_scratch_elems(T, self.nh, self.hd, plan[2])

@@ -24,11 +24,19 @@ class Workspace:
     step asks for it.  Shapes depend on the number of tokens in the step only.
     """
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, keep_outgrown: bool = False):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._views: Dict[Tuple, torch.Tensor] = {}    # (tag, dtype, shape) -> the view handed out last time
         self.frozen = False  # set while a CUDA graph holds pointers into the buffers
+        # keep_outgrown: a buffer that has to grow is replaced but stays allocated, because captured
+        # graphs hold its address (the workspace that all graphs of a runner share: steps run one after
+        # another, so graphs of different shapes can use the same buffers).
+        self.keep_outgrown = keep_outgrown
+        self._outgrown = []
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in list(self._buffers.values()) + self._outgrown)
 
     def get(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A view of the buffer ``tag``.  zero: the buffer is zero when it is first made (or
@@ -45,6 +53,8 @@ class Workspace:
         if buf is None or buf.numel() < n:
             if self.frozen and buf is not None:
                 raise RuntimeError(f"workspace buffer '{tag}' would move while a graph holds it")
+            if self.keep_outgrown and buf is not None:
+                self._outgrown.append(buf)
             make = torch.zeros if zero else torch.empty
             buf = make(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
@@ -85,6 +95,19 @@ class Part:
         for k, v in tensors.items():
             setattr(self, "w_" + k.replace(".", "_"), v)
 
+    def launch_plan(self, step) -> None:
+        """Makes the launch plans this part will use for ``step`` and leaves them in ``step.plans``
+        (key -> plan, both hashable).  The runner calls it on a step context that describes a shape
+        and a longest context, without running anything, to tell apart the captured graphs that such
+        steps need: steps whose plans are equal replay the same graph.  A part whose launches depend
+        on the step's shape alone has nothing to do."""
+
+    def after_load(self) -> None:
+        """Called once, after every part of the model has its tensors: the place to lay a
+        parameter out anew for a kernel (another order of rows, a padded copy, a descriptor).
+        It must not change what the part computes.  (The reference's
+        process_weights_after_loading, atom/model_loader/loader.py:354-360.)"""
+
 
 class Norm(Part):
     """``add_norm``: residual (+= delta), returns the normalised rows in the compute type."""
@@ -104,7 +127,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    """Mixes information along the sequence.  ``cache_need`` says what it keeps per request."""
+    """Mixes information along the sequence.  ``cache_need`` says what it keeps per request.
+
+    State kept in a slot (``cache_need`` of kind "state") is all zeros when a request brings its first
+    token: the storage clears the slot at admission, also for a preempted request that is computed
+    again.  Pages are not cleared; a mixer reads only positions its request has written."""
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None

@@ -82,6 +82,9 @@ class ModelSpec:
     lm_head: PartSpec
     # Regular expressions of checkpoint tensor names that are neither read nor reported.
     ignored_tensors: Tuple[str, ...] = ()
+    # (name, other): a checkpoint tensor that the model does not read but that may be present when it
+    # is, element for element, the tensor ``other``; present and different is a loading error.
+    duplicate_tensors: Tuple[Tuple[str, str], ...] = ()
     eos_token_ids: Tuple[int, ...] = ()
 
 

@@ -6,7 +6,10 @@ layout of atom/model_ops/linear.py:1830-1863 and :1252-1285).  Types: matrices a
 the compute type (bfloat16, or float32 in the 32-bit mode); a vector stored in 32-bit stays
 32-bit; integer tables become int32.  Anything that does not fit is reported in ONE error
 that lists missing tensors, unexpected tensors and wrong shapes together (the reference only
-warns, atom/model_loader/loading_core.py:411-468).
+warns, atom/model_loader/loading_core.py:411-468).  A tensor that the spec names as a duplicate
+of another (the output matrix of a tied model) may be present if it equals that other tensor.
+After the tensors are bound, every part's ``after_load`` runs once (the reference's
+process_weights_after_loading, atom/model_loader/loader.py:354-360).
 """
 from __future__ import annotations
 
@@ -35,6 +38,10 @@ class WeightError(RuntimeError):
         if wrong:
             lines.append(f"  wrong shapes ({len(wrong)}): " + "; ".join(wrong))
         super().__init__("\n".join(lines))
+
+
+class WeightFileError(RuntimeError):
+    """A checkpoint file cannot be read at all (cut off, or not safetensors)."""
 
 
 def expected_tensors(model: Model) -> Dict[str, Tuple[str, str, int, Tuple[int, ...], ParamSpec]]:
@@ -90,15 +97,24 @@ def load_weights(model: Model, model_dir: str, compute: torch.dtype, device) -> 
     ignored = [re.compile(p) for p in model.spec.ignored_tensors]
     handles, where = [], {}
     for f in _checkpoint_files(model_dir):
-        h = safe_open(f, framework="pt", device="cpu")
+        try:
+            h = safe_open(f, framework="pt", device="cpu")
+        except Exception as e:       # a cut-off or foreign file: say which one
+            raise WeightFileError(f"{f}: not a readable safetensors file ({e})") from e
         handles.append(h)
         for k in h.keys():
             where[k] = h
     missing = sorted(n for n in want if n not in where)
+    duplicates = {n: other for n, other in model.spec.duplicate_tensors if n not in want}
     unexpected = sorted(
-        n for n in where if n not in want and not any(p.match(n) for p in ignored)
+        n for n in where if n not in want and n not in duplicates and not any(p.match(n) for p in ignored)
     )
     wrong, stored_dtypes = [], {}
+    for n, other in duplicates.items():
+        if n in where and other in where:
+            a, b = where[n].get_tensor(n), where[other].get_tensor(other)
+            if a.shape != b.shape or a.dtype != b.dtype or not torch.equal(a, b):
+                wrong.append(f"{n}: the model uses {other} in its place, but the file's {n} differs from it")
     for n, (key, _, _, shape, _) in want.items():
         if n in where:
             sl = where[n].get_slice(n)

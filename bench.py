@@ -15,7 +15,11 @@ decode step of the whole batch.  Printed, as ONE JSON line:
   prefill    one prompt of 2,048 tokens through one step (logits of its last token);
   roofline   bytes the decode step has to read (every weight once, the cache of the live
              requests) / its time, against the measured copy bandwidth;
-  points     decode at batch 1 and 64.
+  points     decode at batch 1 and 64; prefill of 512, 8,192 and 32,768 tokens and decode at contexts
+             of 1k, 16k and 32k tokens, each with its share of the peak (``_frac``).
+
+The engine is set up as a user gets it: ``max_model_len`` is the model's max_position_embeddings
+(40,960 for these sizes) and the cache pool is sized by the engine from the memory that is left.
 
 Every weight matrix of the model (tens of GB) is read in every step, far more than the
 126 MB L2 holds, so consecutive timed steps do not find their inputs in L2.
@@ -161,6 +165,12 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the further points: prefill of 512 / 8,192 / 32,768 tokens, decode at contexts 1k / 16k / 32k")
+    ap.add_argument("--max-model-len", type=int, default=0,
+                    help="longest request the engine takes (default: the model's max_position_embeddings)")
+    ap.add_argument("--num-kvcache-blocks", type=int, default=-1,
+                    help="cache pages (default -1: sized by the engine from the memory that is left)")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
 
@@ -195,13 +205,19 @@ def main() -> int:
     ctx_start = ctx_end - (W + K)
     assert ctx_start >= 1, "context too short for warm-up + steps"
     max_b = max(batches)
-    pages = max_b * (-(-ctx_end // PAGE) + 1) + 2 * (-(-PREFILL_TOKENS // PAGE)) + 8
+    max_model_len = args.max_model_len or cfg_d["max_position_embeddings"]
+    sweep_prefill = [] if args.no_sweep else [n for n in (512, 8192, 32768) if n <= max_model_len]
+    sweep_ctx = [] if args.no_sweep else [c for c in (1024, 16384, 32768) if c <= max_model_len and c != ctx_end]
+    assert max(ctx_end, PREFILL_TOKENS) <= max_model_len, "--context beyond --max-model-len"
 
     clocks = ClockSampler(0)
     t_setup = time.time()
+    # The engine as a user gets it: requests as long as the model allows, the cache sized from the memory
+    # that is left after a warm-up step, graphs for every batch size captured at start.
     eng = LLMEngine("", model_config=mcfg, dtype="bfloat16", load_dummy="random", seed=weight_seed,
-                    kv_cache_block_size=PAGE, num_kvcache_blocks=pages, max_num_seqs=max(64, max_b),
-                    max_num_batched_tokens=8192, max_model_len=max(ctx_end, PREFILL_TOKENS) + 8)
+                    kv_cache_block_size=PAGE, num_kvcache_blocks=args.num_kvcache_blocks,
+                    max_num_seqs=max(64, max_b), max_num_batched_tokens=max([8192] + sweep_prefill),
+                    max_model_len=max_model_len)
     runner = eng.runner
     rng = np.random.default_rng(8)
     sp_greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
@@ -210,38 +226,42 @@ def main() -> int:
         return torch.cuda.Event(enable_timing=True)
 
     # ---------------------------------------------------------------- prefill of 2,048 tokens
-    prompt = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
-    times = []
-    for i in range(3 + 5):
-        torch.cuda.synchronize()
-        a, b = ev(), ev()
-        t0 = time.time()
-        a.record()
-        runner.step([StepEntry("p", prompt, (PREFILL_TOKENS - 1,))])
-        b.record()
-        torch.cuda.synchronize()
-        if i >= 3:
-            times.append(a.elapsed_time(b))
-            clocks.window(t0, time.time())
-        runner.finish("p")
-    prefill_ms = statistics.median(times)
-    pf_flops = flops(PREFILL_TOKENS, PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2, 1)
+    def prefill_run(n_tokens, warm=3, reps=5):
+        """Median device time of one step that runs a prompt of n_tokens whole (logits of its last token)."""
+        prompt = rng.integers(0, V, size=n_tokens).tolist()
+        times = []
+        for i in range(warm + reps):
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            t0 = time.time()
+            a.record()
+            runner.step([StepEntry("p", prompt, (n_tokens - 1,))])
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                times.append(a.elapsed_time(b))
+                clocks.window(t0, time.time())
+            runner.finish("p")
+        ms = statistics.median(times)
+        fl = flops(n_tokens, n_tokens * (n_tokens + 1) / 2, 1)
+        return ms, fl / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+
+    prefill_ms, pf_frac = prefill_run(PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 3),
-               "frac": round(pf_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "ms": round(prefill_ms, 3), "frac": round(pf_frac, 4)}
 
     # ---------------------------------------------------------------- decode, timed on the device
-    def fill(b):
-        """b requests whose caches hold ctx_start tokens, by running their prompts."""
+    def fill(b, start):
+        """b requests whose caches hold ``start`` tokens, by running their prompts."""
         ids = [f"d{i}" for i in range(b)]
         for rid in ids:
-            toks = rng.integers(0, V, size=ctx_start).tolist()
-            for s in range(0, ctx_start, 4096):
+            toks = rng.integers(0, V, size=start).tolist()
+            for s in range(0, start, 4096):
                 runner.step([StepEntry(rid, toks[s:s + 4096], ())])
         return ids
 
-    def decode_run(b):
-        ids = fill(b)
+    def decode_run(b, start=None):
+        ids = fill(b, ctx_start if start is None else start)
         toks = rng.integers(0, V, size=(W + K, b))
         params, seeds = [sp_greedy] * b, [0] * b
         launches0 = 0
@@ -280,6 +300,17 @@ def main() -> int:
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
     points = {f"decode_b{b}": round(b / (results[b][0] * 1e-3), 1) for b in batches if b != args.batch}
+    # further points: other prompt lengths (tokens/s and share of the burst peak), other contexts at the
+    # main batch (tokens/s and share of copy bandwidth)
+    for n in sweep_prefill:
+        ms, frac = prefill_run(n, warm=2, reps=3)
+        points[f"prefill_{n}"] = round(n / (ms * 1e-3), 1)
+        points[f"prefill_{n}_frac"] = round(frac, 4)
+    for c in sweep_ctx:
+        ms, _ = decode_run(args.batch, c - (W + K))
+        points[f"decode_b{args.batch}_ctx{c}"] = round(args.batch / (ms * 1e-3), 1)
+        bytes_c = weight_bytes + args.batch * (c - K / 2.0) * kv_per_token
+        points[f"decode_b{args.batch}_ctx{c}_frac"] = round(bytes_c / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
 
     # ---------------------------------------------------------------- end to end through LLMEngine
     e2e = None
@@ -324,6 +355,7 @@ def main() -> int:
             "seq_len": ctx_end, "page_size": PAGE, "kv_cache": "bf16", "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (all weights read every step)",
             "cuda_graphs": bool(getattr(runner, "graphs_enabled", False)),
+            "max_model_len": runner.max_model_len, "kv_pages": runner.cache.groups[0].pool.num_pages,
         },
         "e2e": e2e, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
         "clocks": clocks.summary(), "weight_gb": round(weight_bytes / 1e9, 2),

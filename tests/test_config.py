@@ -63,6 +63,8 @@ def test_rope_parameters_block():
     (lambda d: d.update(num_hidden_layers=0), "num_hidden_layers"),
     (lambda d: d.update(layer_types=["full_attention"]), "layer_types"),
     (lambda d: d.update(layer_types=["sliding_attention", "full_attention"]), "sliding_window"),
+    # the older spelling of a window (from layer max_window_layers on) is refused, not run as full attention
+    (lambda d: d.update(use_sliding_window=True, sliding_window=32, max_window_layers=1), "layer_types"),
 ])
 def test_bad_config_names_the_key(mutate, needle):
     raw = copy.deepcopy(tiny.CONFIGS["A"])
@@ -70,6 +72,16 @@ def test_bad_config_names_the_key(mutate, needle):
     with pytest.raises(ConfigError) as e:
         config_from_dict(raw)
     assert needle in str(e.value)
+
+
+def test_window_keys_without_effect_are_taken():
+    """use_sliding_window false (or no window at all) beside max_window_layers: full attention, as written."""
+    raw = copy.deepcopy(tiny.CONFIGS["A"])
+    raw.update(use_sliding_window=False, sliding_window=32, max_window_layers=1)
+    cfg = config_from_dict(raw)
+    assert cfg.sliding_window is None and cfg.layer_types is None
+    raw.update(use_sliding_window=True, sliding_window=None)
+    assert config_from_dict(raw).sliding_window is None
 
 
 def test_missing_file(tmp_path):

@@ -212,8 +212,8 @@ def test_overlap_goes_on_when_requests_end_at_their_token_count(model_dirs):
     lens = [9, 5, 17, 13, 5]
     eng = _engine(model_dirs[name], "float32", pages=64, page=8, enforce_eager=False, cudagraph_capture_sizes=[1, 2, 4, 8],
                   max_model_len=128)
-    assert sorted(k for k in eng.runner._graphs if isinstance(k, int)) == [1, 2, 4, 8]     # captured before the first request
-    assert (16, 8) in eng.runner._graphs and (128, 8) in eng.runner._graphs                  # and the small steps of any makeup
+    assert sorted(k for k in eng.runner.graph_shapes if isinstance(k, int)) == [1, 2, 4, 8]     # captured before the first request
+    assert (16, 8) in eng.runner.graph_shapes and (128, 8) in eng.runner.graph_shapes                  # and the small steps of any makeup
     outs = eng.generate(prompts, [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in lens])
     for p_, n, o in zip(prompts, lens, outs):
         assert o["token_ids"] == plain.generate_greedy(cfg, w, p_, n) and o["finish_reason"] == "max_tokens"
@@ -364,7 +364,7 @@ def test_many_requests_decode_together_from_a_large_captured_batch(model_dirs, n
     prompts = [rng.integers(0, cfg["vocab_size"], int(rng.integers(1, 12))).tolist() for _ in range(70)]
     sp = SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True)
     eng = _engine(model_dirs[name], dtype, pages=400, page=8, max_model_len=64, enforce_eager=False, max_num_seqs=128)
-    assert 96 in eng.runner._graphs and 128 in eng.runner._graphs and 192 not in eng.runner._graphs
+    assert 96 in eng.runner.graph_shapes and 128 in eng.runner.graph_shapes and 192 not in eng.runner.graph_shapes
     outs = eng.generate(prompts, sp)
     assert eng.runner.graph_replays >= 5 and eng.num_overlapped >= 4
     eager = _engine(model_dirs[name], dtype, pages=400, page=8, max_model_len=64).generate(prompts, sp)

@@ -257,3 +257,45 @@ def test_many_requests_tiny_pool_all_finish():
     assert all(q.is_finished and q.num_output_tokens == q.params.max_tokens for q in seqs)
     assert cache.num_free_pages(0) == 12 and cache.state_slots.num_free == 4
     assert s.num_preemptions > 0
+
+
+def test_portions_off_takes_a_prompt_whole_or_not_at_all():
+    """enable_chunked_prefill=False (the reference's switch, atom/model_engine/scheduler.py:1765-1767):
+    a prompt is scheduled only in a step that has room for all of it; a prompt longer than the token
+    budget can never run and is refused with a reason; decoding goes on meanwhile."""
+    cache = CacheManager({0: FULL}, 4, 64, 4)
+    s = Scheduler(cache, 4, 20, 200, eos_token_ids=(2,), enable_chunked_prefill=False)
+    a, b, c, d = seq(12, sid=1), seq(15, sid=2), seq(25, sid=3), seq(6, sid=4)
+    for q in (a, b, c, d):
+        s.add(q)
+    st = s.schedule()
+    # a fits (12 of 20); b (15) does not fit beside it and is not cut: it waits, and nothing behind it is taken
+    assert [(e.seq.seq_id, e.start, e.num_tokens, e.samples) for e in st.entries] == [(1, 0, 12, True)]
+    run(s, cache, st)
+    st = s.schedule()
+    # a decodes (1), b runs whole (15): 16 of 20; c (25 > 20) is refused with a reason; d (6) no longer fits
+    assert [(e.seq.seq_id, e.start, e.num_tokens) for e in st.entries] == [(1, 12, 1), (2, 0, 15)]
+    assert [q.seq_id for q in st.rejected] == [3] and "max_num_batched_tokens" in c.finish_reason
+    run(s, cache, st)
+    st = s.schedule()
+    assert [(e.seq.seq_id, e.start, e.num_tokens) for e in st.entries] == [(1, 13, 1), (2, 15, 1), (4, 0, 6)]
+    run(s, cache, st)
+    assert all(e.samples for e in st.entries)
+
+
+def test_portions_off_recomputes_a_preempted_request_whole():
+    cache = CacheManager({0: FULL}, 4, 6, 4)
+    s = Scheduler(cache, 4, 16, 200, eos_token_ids=(2,), enable_chunked_prefill=False)
+    a, b = seq(7, sid=1, max_tokens=12), seq(8, sid=2, max_tokens=12)
+    s.add(a)
+    s.add(b)
+    run(s, cache, s.schedule())                     # both prompts: 2 + 2 pages... a grows first
+    while not s.num_preemptions:
+        run(s, cache, s.schedule())
+    assert b.status == SequenceStatus.WAITING and b.num_computed == 0
+    n = b.num_tokens
+    while b.status == SequenceStatus.WAITING:
+        st = s.schedule()
+        run(s, cache, st)
+    e = next(e for e in st.entries if e.seq is b)
+    assert (e.start, e.num_tokens) == (0, n)        # what it had, prompt and generated tokens, in one step

@@ -88,15 +88,78 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(model_dirs, tmp_pat
     assert "missing" in msg and "unexpected" in msg and "wrong shapes" in msg and "inv_freq" not in msg
 
 
-def test_tied_model_refuses_a_separate_head(model_dirs, tmp_path):
+def _with_head(model_dirs, tmp_path, head):
     d = str(tmp_path)
     raw = load_file(os.path.join(model_dirs["A"], "model.safetensors"))
-    raw["lm_head.weight"] = raw["model.embed_tokens.weight"].clone()
+    raw["lm_head.weight"] = head(raw["model.embed_tokens.weight"])
     save_file(raw, os.path.join(d, "model.safetensors"))
     os.link(os.path.join(model_dirs["A"], "config.json"), os.path.join(d, "config.json"))
+    return d, raw
+
+
+def test_tied_model_takes_a_head_that_equals_the_embedding(model_dirs, tmp_path):
+    """A tied checkpoint that carries the output matrix as well loads, and uses the embedding table."""
+    d, raw = _with_head(model_dirs, tmp_path, lambda e: e.clone())
+    w = load_weights(_model(d), d, torch.bfloat16, "cpu")
+    assert "lm_head.weight" not in w
+    assert torch.equal(w["embedding.weight"], raw["model.embed_tokens.weight"])
+
+
+def test_tied_model_refuses_a_head_that_differs(model_dirs, tmp_path):
+    def other(e):
+        e = e.clone()
+        e[3, 5] += 1.0
+        return e
+
+    d, _ = _with_head(model_dirs, tmp_path, other)
     with pytest.raises(WeightError) as e:
         load_weights(_model(d), d, torch.bfloat16, "cpu")
-    assert e.value.unexpected == ["lm_head.weight"]
+    assert not e.value.unexpected and len(e.value.wrong_shape) == 1
+    assert "lm_head.weight" in e.value.wrong_shape[0] and "model.embed_tokens.weight" in e.value.wrong_shape[0]
+
+
+def test_untied_model_still_needs_its_own_head(model_dirs):
+    m = _model(model_dirs["B"])
+    assert m.spec.duplicate_tensors == () and "lm_head.weight" in expected_tensors(m)
+
+
+def test_cut_off_file_is_named(model_dirs, tmp_path):
+    from atom_b200.weights import WeightFileError
+    d = str(tmp_path)
+    with open(os.path.join(model_dirs["A"], "model.safetensors"), "rb") as f:
+        data = f.read()
+    with open(os.path.join(d, "model.safetensors"), "wb") as f:
+        f.write(data[: len(data) // 2])
+    os.link(os.path.join(model_dirs["A"], "config.json"), os.path.join(d, "config.json"))
+    with pytest.raises(WeightFileError) as e:
+        load_weights(_model(d), d, torch.bfloat16, "cpu")
+    assert "model.safetensors" in str(e.value)
+
+
+def test_after_load_runs_once_per_part_and_changes_nothing(model_dirs):
+    """The hook that lets a part lay its tensors out anew is called once for every part after all are
+    bound; the built-in parts leave their tensors as loaded."""
+    from atom_b200.parts.base import Part, Runtime, Workspace
+    d = model_dirs["B"]
+    m = _model(d)
+    w = load_weights(m, d, torch.bfloat16, "cpu")
+    before = {k: v.clone() for k, v in w.items()}
+    calls = []
+    orig = Part.after_load
+
+    def spy(self):
+        assert m.rt is not None and hasattr(m.lm_head, "w_weight")     # everything is bound by now
+        calls.append(self)
+        return orig(self)
+
+    Part.after_load = spy
+    try:
+        m.bind(w, Runtime(torch.bfloat16, torch.device("cpu"), Workspace(torch.device("cpu"))))
+    finally:
+        Part.after_load = orig
+    parts = [p for _, p, _ in m.named_parts()]
+    assert len(calls) == len(parts) and {id(c) for c in calls} == {id(p) for p in parts}
+    assert all(torch.equal(before[k], w[k]) for k in w)
 
 
 def test_missing_shard_named_by_index(model_dirs, tmp_path):
