@@ -126,7 +126,9 @@ class ModelRunner:
         if self.mixed_graphs:
             shapes += [(t, n) for n in _MIXED_SEQS for t in self._mixed_tokens]
         arrays = sum(4 * (3 * t + 4 * n + 16 + groups * n * self._table_width) for t, n in shapes)
-        objects = (128 << 20) + len(shapes) * 3 * (1 << 20)
+        # a captured step of a few hundred kernels was measured at 3-5 MB of device memory; a shape has
+        # one graph per context class whose launch plans differ (about two on average)
+        objects = (128 << 20) + len(shapes) * 2 * 5 * (1 << 20)
         return logits + workspace + arrays + objects
 
     def _pages_from_free_memory(self, needs) -> int:

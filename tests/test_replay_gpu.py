@@ -175,7 +175,6 @@ def test_small_steps_of_any_makeup_replay_graphs_and_match_plain(model_dirs, nam
         err, rid, pos = max_err(got, ref)
         tol = _tol(dtype, ref)
         assert err <= tol, f"{name}/{dtype}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
-    assert len(runner._graphs) > len(runner.graph_shapes) or name == "A"     # some shape has a graph per context class
     shapes = [k for k in runner.graph_shapes if isinstance(k, tuple)]
     assert len(shapes) >= 2 and runner.graph_replays > 60, (shapes, runner.graph_replays)
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
