@@ -2,7 +2,7 @@
 pool per group of cache slots with the same need, and a state slot per request.
 
 Cache slots (one per run-order entry that writes a cache) are grouped by what their mixer
-keeps: (kv heads, head size, window).  A group has its own pool and its own block table
+keeps: (the arrays it holds per token, window).  A group has its own pool and its own block table
 per request; all slots of a group share the table (page id p means page p of every slot's
 storage in that group).  A group with a window gives pages back as soon as every position
 on them is further back than any later query can look.
@@ -40,8 +40,7 @@ class CacheGroup:
     index: int
     key: Tuple
     window: Optional[int]
-    num_kv_heads: int
-    head_dim: int
+    entries: Tuple                   # the CacheEntry arrays every slot of the group holds per token
     slots: List[int]                 # cache slots (run-order cache ids) stored in this group
     pool: PagePool = None            # type: ignore
 
@@ -85,7 +84,7 @@ class CacheManager:
             k = need.group_key()
             g = by_key.get(k)
             if g is None:
-                g = CacheGroup(len(self.groups), k, need.window, need.num_kv_heads, need.head_dim, [])
+                g = CacheGroup(len(self.groups), k, need.window, need.entries, [])
                 n = num_pages[k] if isinstance(num_pages, dict) else num_pages
                 g.pool = PagePool(n)
                 by_key[k] = g

@@ -1,12 +1,13 @@
 """Device arrays behind the cache manager's accounting.
 
-One array per page group, [slots, 2 (keys, values), pages, kv heads, page size, head size]
-in the compute type, and one array [state slots, *shape] per cache slot whose mixer keeps
-fixed-size state, zero when a request is admitted.  ``view(slot)`` is what a mixer gets for its
-run entry."""
+For every page group one array per entry that its mixers declare (CacheNeed.entries):
+[slots, pages, *shape with the page's tokens before the last axis], e.g. keys and values of
+(kv heads, head size) each as [slots, pages, kv heads, page size, head size].  And one array
+[state slots, *shape] per cache slot whose mixer keeps fixed-size state, zero when a request is
+admitted.  ``view(slot)`` is what a mixer gets for its run entry."""
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Optional
 
 import torch
@@ -19,9 +20,24 @@ class CacheView:
     slot: int
     group: int = -1                       # page group (index into StepContext.block_tables)
     page_size: int = 0
-    k_pages: Optional[torch.Tensor] = None   # [pages, kv heads, page size, head size]
-    v_pages: Optional[torch.Tensor] = None
+    pages: Dict[str, torch.Tensor] = field(default_factory=dict)   # entry name -> [pages, ..., page size, last]
     state: Optional[torch.Tensor] = None     # [state slots, *shape]
+
+    @property
+    def k_pages(self) -> Optional[torch.Tensor]:   # [pages, kv heads, page size, head size]
+        return self.pages.get("k")
+
+    @property
+    def v_pages(self) -> Optional[torch.Tensor]:
+        return self.pages.get("v")
+
+
+def _entry_dtype(entry, compute: torch.dtype) -> torch.dtype:
+    return compute if entry.dtype == "compute" else getattr(torch, entry.dtype)
+
+
+def _page_shape(entry, page_size: int):
+    return tuple(entry.shape[:-1]) + (page_size, entry.shape[-1])
 
 
 class CacheStorage:
@@ -32,13 +48,14 @@ class CacheStorage:
         self._states = []
         ps = manager.page_size
         for g in manager.groups:
-            a = torch.zeros(
-                (len(g.slots), 2, g.pool.num_pages, g.num_kv_heads, ps, g.head_dim),
-                dtype=dtype, device=device,
-            )
-            self.arrays.append(a)
+            per_entry = {}
+            for e in g.entries:
+                a = torch.zeros((len(g.slots), g.pool.num_pages) + _page_shape(e, ps),
+                                dtype=_entry_dtype(e, dtype), device=device)
+                self.arrays.append(a)
+                per_entry[e.name] = a
             for i, slot in enumerate(g.slots):
-                self._views[slot] = CacheView(slot, g.index, ps, a[i, 0], a[i, 1])
+                self._views[slot] = CacheView(slot, g.index, ps, {n: a[i] for n, a in per_entry.items()})
         for slot, need in manager.state_needs.items():
             sdt = dtype if need.state_dtype == "compute" else getattr(torch, need.state_dtype)
             st = torch.zeros((manager.state_slots.num_slots,) + tuple(need.state_shape), dtype=sdt, device=device)
@@ -66,7 +83,12 @@ class CacheStorage:
 
     @staticmethod
     def bytes_per_page(manager: CacheManager, dtype: torch.dtype) -> int:
-        es = torch.empty((), dtype=dtype).element_size()
-        return sum(
-            len(g.slots) * 2 * g.num_kv_heads * manager.page_size * g.head_dim * es for g in manager.groups
-        )
+        """Bytes that one more page in every group costs."""
+        total = 0
+        for g in manager.groups:
+            for e in g.entries:
+                n = manager.page_size
+                for d in e.shape:
+                    n *= d
+                total += len(g.slots) * n * torch.empty((), dtype=_entry_dtype(e, dtype)).element_size()
+        return total

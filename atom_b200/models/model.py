@@ -23,18 +23,16 @@ class Model:
         self.blocks = []
         self._named: List[Tuple[str, Part, PartSpec]] = [("embedding", self.embedding, spec.embedding)]
         for i, ls in enumerate(spec.layers):
-            mixer_norm = registry.build("norm", ls.mixer_norm)
-            mixer = registry.build("mixer", ls.mixer)
-            ffn_norm = registry.build("norm", ls.ffn_norm)
-            ffn = registry.build("ffn", ls.ffn)
-            self.blocks.append(registry.lookup("arrangement", ls.arrangement)(mixer_norm, mixer, ffn_norm, ffn))
-            p = f"layers.{i}"
-            self._named += [
-                (f"{p}.mixer_norm", mixer_norm, ls.mixer_norm),
-                (f"{p}.mixer", mixer, ls.mixer),
-                (f"{p}.ffn_norm", ffn_norm, ls.ffn_norm),
-                (f"{p}.ffn", ffn, ls.ffn),
-            ]
+            arrangement = registry.lookup("arrangement", ls.arrangement)
+            slots = arrangement.slots          # name -> part category ("norm", "mixer", "ffn", ...)
+            absent = [n for n in slots if n not in ls.parts and n not in arrangement.optional]
+            extra = [n for n in ls.parts if n not in slots]
+            if absent or extra:
+                raise ValueError(f"layer {i}: arrangement '{ls.arrangement}' has the parts {sorted(slots)}; "
+                                 f"missing {absent}, not known {extra}")
+            built = {n: registry.build(slots[n], ls.parts[n]) for n in slots if n in ls.parts}
+            self.blocks.append(arrangement(**built))
+            self._named += [(f"layers.{i}.{n}", built[n], ls.parts[n]) for n in slots if n in built]
         self.final_norm = registry.build("norm", spec.final_norm)
         self.lm_head = registry.build("head", spec.lm_head)
         self._named += [("final_norm", self.final_norm, spec.final_norm), ("lm_head", self.lm_head, spec.lm_head)]
@@ -58,7 +56,8 @@ class Model:
         needs: Dict[int, CacheNeed] = {}
         writers: Dict[int, int] = {}
         for e in self.spec.run_order:
-            need = self.blocks[e.layer].mixer.cache_need()
+            mixer = getattr(self.blocks[e.layer], "mixer", None)   # a layer may have none
+            need = mixer.cache_need() if mixer is not None else None
             if need is None:
                 continue
             if e.cache in needs and needs[e.cache] != need:

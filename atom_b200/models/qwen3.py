@@ -235,13 +235,12 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
         )
         norm_args = {"size": H, "eps": cfg.rms_norm_eps}
         layers.append(
-            LayerSpec(
-                arrangement="prenorm",
-                mixer_norm=PartSpec("rmsnorm", norm_args, {"weight": (f"{p}.input_layernorm.weight",)}),
-                mixer=mixer,
-                ffn_norm=PartSpec("rmsnorm", norm_args, {"weight": (f"{p}.post_attention_layernorm.weight",)}),
-                ffn=ffn,
-            )
+            LayerSpec("prenorm", {
+                "mixer_norm": PartSpec("rmsnorm", norm_args, {"weight": (f"{p}.input_layernorm.weight",)}),
+                "mixer": mixer,
+                "ffn_norm": PartSpec("rmsnorm", norm_args, {"weight": (f"{p}.post_attention_layernorm.weight",)}),
+                "ffn": ffn,
+            })
         )
     return ModelSpec(
         architecture=cfg.architecture,

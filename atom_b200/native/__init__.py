@@ -63,6 +63,7 @@ _SIGNATURES = {
     "atom_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "atom_qknorm_rope_kvwrite": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _vp,
                                  _vp, _i, _i, _vp, _vp, _i64, _vp, _vp],
+    "atom_qk_headnorm": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _vp],
     "atom_paged_attention_generic": [_vp, _vp, _i64, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i,
                                      _i, _i, _f, _i, _vp],
     "atom_gemm_f32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _vp],
@@ -246,6 +247,17 @@ def qknorm_rope_kvwrite(qkv: torch.Tensor, nh: int, nkv: int, hd: int,
         float(eps), _ptr(cos_sin), rotary_dim, max_pos, positions.data_ptr(), seq_of_token.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages),
         num_pages, status.data_ptr(), _stream()), "qknorm_rope_kvwrite")
+
+
+def qk_headnorm(qkv: torch.Tensor, nh: int, nkv: int, hd: int, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                eps: float, seq_of_token: torch.Tensor) -> None:
+    """Per-head RMSNorm of the q and k heads of the packed [T, (nh+2nkv)*hd] projection, in place."""
+    _cuda(qkv, q_weight, k_weight, seq_of_token)
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * hd
+    assert k_weight.dtype == q_weight.dtype and q_weight.numel() == hd and k_weight.numel() == hd
+    _check(lib().atom_qk_headnorm(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[0], nh, nkv, hd,
+                                  q_weight.data_ptr(), k_weight.data_ptr(), dtype_code(q_weight.dtype), float(eps),
+                                  seq_of_token.data_ptr(), _stream()), "qk_headnorm")
 
 
 def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, q_stride: int,

@@ -377,6 +377,30 @@ __global__ void __launch_bounds__(128, 8) qknorm_rope_kvwrite_bf16_vec_kernel(
   }
 }
 
+// Per-head RMSNorm of the query and key heads in place, nothing else: for a mixer whose position
+// encoding is not a table of angles and runs between the norm and the cache write.
+template <typename T>
+__global__ void qk_headnorm_kernel(T* __restrict__ qkv, int nh, int nkv, int hd, const void* __restrict__ q_w,
+                                   const void* __restrict__ k_w, int w_dtype, float eps,
+                                   const int* __restrict__ seq_of_token) {
+  atom::pdl_trigger();
+  atom::pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (head >= nh + nkv || seq_of_token[t] < 0) return;
+  const void* w = head < nh ? q_w : k_w;
+  T* x = qkv + ((int64_t)t * (nh + 2 * nkv) + head) * hd;
+  float ss = 0.f;
+  for (int i = lane; i < hd; i += 32) {
+    const float v = to_float(x[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)hd + eps);
+  for (int i = lane; i < hd; i += 32) x[i] = from_float<T>(to_float(x[i]) * rstd * load_as_float(w, w_dtype, i));
+}
+
 }  // namespace atom
 
 // qkv: [T, (nh + 2 nkv) * hd] of `dtype`, q part rewritten in place.
@@ -449,5 +473,25 @@ ATOM_EXPORT int atom_qknorm_rope_kvwrite(void* qkv, int dtype, int T, int nh, in
   } else {
     return ATOM_ERR_ARG;
   }
+  return atom::check_launch();
+}
+
+// Per-head RMSNorm of the q and k heads of qkv [T, (nh + 2 nkv) * hd] in place (v untouched, no rotation,
+// no cache write).
+ATOM_EXPORT int atom_qk_headnorm(void* qkv, int dtype, int T, int nh, int nkv, int hd, const void* q_w,
+                                 const void* k_w, int w_dtype, float eps, const int* seq_of_token,
+                                 cudaStream_t stream) {
+  if (T <= 0) return ATOM_OK;
+  if (nh <= 0 || nkv <= 0 || hd <= 0 || q_w == nullptr || k_w == nullptr) return ATOM_ERR_ARG;
+  const int warps = 4;
+  dim3 grid(T, (nh + nkv + warps - 1) / warps);
+  if (dtype == ATOM_F32)
+    atom::launch_pdl(atom::qk_headnorm_kernel<float>, grid, dim3(warps * 32), 0, stream, (float*)qkv, nh, nkv, hd,
+                     q_w, k_w, w_dtype, eps, seq_of_token);
+  else if (dtype == ATOM_BF16)
+    atom::launch_pdl(atom::qk_headnorm_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, stream,
+                     (__nv_bfloat16*)qkv, nh, nkv, hd, q_w, k_w, w_dtype, eps, seq_of_token);
+  else
+    return ATOM_ERR_ARG;
   return atom::check_launch();
 }

@@ -17,7 +17,7 @@ import torch
 
 from .. import native
 from . import registry
-from .base import Mixer
+from .base import Mixer, PositionEncoding
 from .linear import linear
 from .registry import register
 from .spec import CacheNeed, ParamSpec, PartSpec
@@ -25,7 +25,9 @@ from .spec import CacheNeed, ParamSpec, PartSpec
 
 @register("mixer", "paged_attention")
 class PagedAttention(Mixer):
-    graph_safe = True
+    @property
+    def graph_safe(self) -> bool:      # its own launches are; the position encoding answers for itself
+        return self.position.graph_safe
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, qk_norm: bool = False, norm_eps: float = 0.0,
@@ -71,14 +73,24 @@ class PagedAttention(Mixer):
         qkv = linear(x, self.w_qkv_weight, getattr(self, "w_qkv_bias", None),
                      ws.get("attn.qkv", (T, (nh + 2 * nkv) * hd), dt))
         bt = step.block_tables[cache.group]
-        native.qknorm_rope_kvwrite(
-            qkv, nh, nkv, hd,
-            self.w_q_norm_weight if self.qk_norm else None,
-            self.w_k_norm_weight if self.qk_norm else None,
-            self.norm_eps, self._table, self.position.rotary_dim,
-            step.positions, step.seq_of_token, bt, cache.page_size,
-            cache.k_pages if writes_cache else None, cache.v_pages if writes_cache else None,
-            step.status)
+        qw = self.w_q_norm_weight if self.qk_norm else None
+        kw = self.w_k_norm_weight if self.qk_norm else None
+        kp = cache.k_pages if writes_cache else None
+        vp = cache.v_pages if writes_cache else None
+        if self._table is not None or type(self.position).apply is PositionEncoding.apply:
+            # one kernel: norm, rotation by the table's rows, cache write
+            native.qknorm_rope_kvwrite(
+                qkv, nh, nkv, hd, qw, kw, self.norm_eps, self._table,
+                self.position.rotary_dim if self._table is not None else 0,
+                self.position.rows_of(step), step.seq_of_token, bt, cache.page_size, kp, vp, step.status)
+        else:
+            # a position encoding of its own making: norm, then the part's ``apply``, then the write
+            if self.qk_norm:
+                native.qk_headnorm(qkv, nh, nkv, hd, qw, kw, self.norm_eps, step.seq_of_token)
+            self.position.apply(qkv[:, :nh * hd].view(T, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), step)
+            if kp is not None:
+                native.qknorm_rope_kvwrite(qkv, nh, nkv, hd, None, None, 0.0, None, 0, step.positions,
+                                           step.seq_of_token, bt, cache.page_size, kp, vp, step.status)
         o = ws.get("attn.o", (T, nh * hd), dt)
         self.attend(o, qkv, step, cache, bt)
         return linear(o, self.w_o_weight, None, ws.get("attn.out", (T, self.hidden_size), dt))

@@ -118,12 +118,27 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Gives the mixer what it needs to encode positions (for rotary kinds: a table)."""
+    """Encodes positions into queries and keys.  Two forms, a kind chooses one:
+
+    * a table of angles: ``table(rt)`` gives [rows, rotary_dim] float32 (cos of every pair's angle,
+      then sin) and ``rows_of(step)`` the table row of every token of the step (the token's position
+      unless the kind says otherwise: an offset per request, a position that is not the index in the
+      sequence).  The mixer hands both to its fused kernel.
+    * anything else: ``table`` gives None and ``apply(q, k, step)`` changes the normalised queries
+      [T, heads, head] and keys [T, kv heads, head] in place, between the mixer's norm and its
+      cache write.
+    """
 
     rotary_dim = 0
 
     def table(self, rt: Runtime) -> Optional[torch.Tensor]:
         return None
+
+    def rows_of(self, step) -> torch.Tensor:
+        return step.positions
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, step) -> None:
+        """Only called when ``table`` gives None.  The default encodes nothing."""
 
 
 class Mixer(Part):

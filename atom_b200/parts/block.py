@@ -1,5 +1,11 @@
 """Arrangements of a layer's parts around the residual stream.
 
+An arrangement declares the parts it is put together from: ``slots`` maps each part's name in
+the layer to its category in the registries (the model builds exactly these from the layer's
+spec and hands them to the constructor by name); names listed in ``optional`` may be left out
+of a layer.  The part named ``mixer``, if there is one, is the one whose cache the run entry's
+cache slot holds.
+
 "prenorm" is the one of atom/models/qwen3.py:248-258: the residual is a running 32-bit
 sum; each sub-block's output is added to it inside the next norm's kernel:
    r += delta;  a = norm1(r);  m = mixer(a);  r += m;  b = norm2(r);  delta' = ffn(b).
@@ -11,6 +17,9 @@ from .registry import register
 
 @register("arrangement", "prenorm")
 class PreNormBlock:
+    slots = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
+    optional = ()
+
     def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 

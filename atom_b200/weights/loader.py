@@ -45,19 +45,23 @@ class WeightFileError(RuntimeError):
 
 
 def expected_tensors(model: Model) -> Dict[str, Tuple[str, str, int, Tuple[int, ...], ParamSpec]]:
-    """checkpoint tensor name -> (parameter key, param name, row offset, expected shape, spec)."""
+    """checkpoint tensor name -> (parameter key, param name, offset along the parameter's stack_dim,
+    expected shape, spec)."""
     out: Dict[str, Tuple[str, str, int, Tuple[int, ...], ParamSpec]] = {}
     for path, part, pspec in model.named_parts():
         for name, ps in part.params().items():
             srcs = pspec.sources.get(name)
             if srcs is None:
                 raise ValueError(f"{path}.{name}: the architecture names no checkpoint tensor for it")
-            rows = ps.rows if ps.rows is not None else (ps.shape[0],)
-            if len(rows) != len(srcs) or sum(rows) != ps.shape[0]:
-                raise ValueError(f"{path}.{name}: {len(srcs)} source tensors for row split {rows}")
+            d = ps.stack_dim
+            if not 0 <= d < len(ps.shape):
+                raise ValueError(f"{path}.{name}: stack_dim {d} for a tensor of shape {ps.shape}")
+            rows = ps.rows if ps.rows is not None else (ps.shape[d],)
+            if len(rows) != len(srcs) or sum(rows) != ps.shape[d]:
+                raise ValueError(f"{path}.{name}: {len(srcs)} source tensors for the split {rows} of axis {d}")
             off = 0
             for src, r in zip(srcs, rows):
-                out[src] = (f"{path}.{name}", name, off, (r,) + tuple(ps.shape[1:]), ps)
+                out[src] = (f"{path}.{name}", name, off, tuple(ps.shape[:d]) + (r,) + tuple(ps.shape[d + 1:]), ps)
                 off += r
     return out
 
@@ -135,7 +139,8 @@ def load_weights(model: Model, model_dir: str, compute: torch.dtype, device) -> 
     for n, (key, _, off, shape, ps) in want.items():
         t = where[n].get_tensor(n)
         dst = out[key]
-        dst[off : off + shape[0]].copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
+        d = ps.stack_dim
+        dst.narrow(d, off, shape[d]).copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t)
     return out
 
 

@@ -257,3 +257,33 @@ def test_random_orders_with_shared_prefixes_keep_the_books(seed):
     c.check()
     pool = c.groups[0].pool
     assert pool.num_used == 0 and pool.num_free == 24
+
+
+def test_groups_follow_the_declared_entries_and_storage_allocates_them():
+    """A mixer names what it keeps per token; slots that keep the same arrays share a group and a block
+    table, others get a pool of their own, and the storage allocates exactly the declared arrays with the
+    page's tokens before the last axis."""
+    import torch
+
+    from atom_b200.cache.storage import CacheStorage
+    from atom_b200.parts.spec import CacheEntry
+
+    latent = CacheNeed("pages", entries=(CacheEntry("latent", (12,), "float32"),))
+    kv_unequal = CacheNeed("pages", entries=(CacheEntry("k", (2, 24)), CacheEntry("v", (2, 16))))
+    assert FULL.entries == (CacheEntry("k", (2, 16)), CacheEntry("v", (2, 16)))
+    m = CacheManager({0: FULL, 1: latent, 2: FULL, 3: kv_unequal, 4: latent}, page_size=8, num_pages=5, max_requests=2)
+    assert [g.slots for g in m.groups] == [[0, 2], [1, 4], [3]]
+    st = CacheStorage(m, torch.bfloat16, "cpu")
+    v0, v1, v3 = st.view(0), st.view(1), st.view(3)
+    assert v0.k_pages.shape == (5, 2, 8, 16) and v0.v_pages.dtype == torch.bfloat16 and v0.group == 0
+    assert set(v1.pages) == {"latent"} and v1.pages["latent"].shape == (5, 8, 12) and v1.k_pages is None
+    assert v1.pages["latent"].dtype == torch.float32 and v1.group == 1
+    assert v3.pages["k"].shape == (5, 2, 8, 24) and v3.pages["v"].shape == (5, 2, 8, 16)
+    assert st.view(2).k_pages.data_ptr() != v0.k_pages.data_ptr()
+    per_page = 2 * (2 * 2 * 16 * 8 * 2) + 2 * (12 * 8 * 4) + (2 * 24 + 2 * 16) * 8 * 2
+    assert CacheStorage.bytes_per_page(m, torch.bfloat16) == per_page
+    assert st.bytes() == 5 * per_page
+    with pytest.raises(ValueError):
+        CacheNeed("pages")
+    with pytest.raises(ValueError):
+        CacheNeed("pages", entries=(CacheEntry("a", (4,)), CacheEntry("a", (4,))))

@@ -27,13 +27,13 @@ def test_roundtrip_and_spec(name, tmp_path):
     assert len(spec.layers) == raw["num_hidden_layers"]
     assert [e.layer for e in spec.run_order] == list(range(raw["num_hidden_layers"]))
     for i, layer in enumerate(spec.layers):
-        a = layer.mixer.args
+        a = layer.parts["mixer"].args
         assert (a["num_heads"], a["num_kv_heads"], a["head_dim"]) == (
             raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"])
         assert a["norm_eps"] == raw["rms_norm_eps"] and a["position"].args["theta"] == raw["rope_theta"]
         want_window = raw["sliding_window"] if raw.get("layer_types", ["full_attention"] * 99)[i] == "sliding_attention" else None
         assert a["window"] == want_window
-        assert layer.ffn.args["intermediate_size"] == raw["intermediate_size"]
+        assert layer.parts["ffn"].args["intermediate_size"] == raw["intermediate_size"]
     assert spec.lm_head.args["tied"] == raw["tie_word_embeddings"]
 
 

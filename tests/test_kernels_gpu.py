@@ -167,6 +167,29 @@ def test_qknorm_rope_kvwrite(native, dtype, nh, nkv, hd, rd, page, use_norm, q_l
     assert float(kp.float().abs().sum(dim=(1, 3))[untouched].sum()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,T", [(3, 1, 16, 5), (5, 5, 48, 33), (32, 8, 128, 4), (6, 2, 200, 7)])
+def test_qk_headnorm(native, dtype, nh, nkv, hd, T):
+    """Per-head RMSNorm of the q and k heads in place; v heads and padding rows are not touched."""
+    eps = 3e-6
+    qkv = _rand((T, (nh + 2 * nkv) * hd), dtype, 31)
+    before = qkv.clone()
+    qw = (_rand((hd,), torch.float32, 32) * 0.1 + 1).to(dtype)
+    kw = (_rand((hd,), torch.float32, 33) * 0.1 + 1).to(dtype)
+    sot = torch.zeros(T, dtype=torch.int32, device=DEV)
+    sot[T - 1] = -1                                   # a padding row
+    native.qk_headnorm(qkv, nh, nkv, hd, qw, kw, eps, sot)
+    x = before.double().view(T, nh + 2 * nkv, hd)
+    w = torch.cat([qw.double().expand(nh, hd), kw.double().expand(nkv, hd)])
+    want = x.clone()
+    want[:, :nh + nkv] = x[:, :nh + nkv] * torch.rsqrt(x[:, :nh + nkv].pow(2).mean(-1, keepdim=True) + eps) * w
+    want[T - 1] = x[T - 1]
+    got = qkv.view(T, nh + 2 * nkv, hd)
+    torch.testing.assert_close(got.float(), want.to(dtype).float(), **_tol(dtype))
+    assert torch.equal(got[:, nh + nkv:], before.view(T, nh + 2 * nkv, hd)[:, nh + nkv:])
+    assert torch.equal(got[T - 1], before.view(T, nh + 2 * nkv, hd)[T - 1])
+
+
 # ----------------------------------------------------------------------------- attention
 
 

@@ -338,9 +338,9 @@ def _register_toy():
                                       qk_norm=False),
                                  {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",)})
             norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": cfg.eps}, {"weight": (f"{p}.{n}",)})
-            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"),
-                                    PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": cfg.intermediate_size},
-                                             {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})))
+            ffn = PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": cfg.intermediate_size},
+                           {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})
+            layers.append(LayerSpec("prenorm", dict(mixer_norm=norm("n1"), mixer=mixer, ffn_norm=norm("n2"), ffn=ffn)))
         return ModelSpec(
             architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, max_position=512,
             embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": H}, {"weight": ("emb",)}),
@@ -463,9 +463,9 @@ def _register_hybrid():
                                   window=window),
                              {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",)})
             norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": (f"{p}.{n}",)})
-            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"),
-                                    PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 2 * H},
-                                             {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})))
+            ffn = PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": 2 * H},
+                           {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})
+            layers.append(LayerSpec("prenorm", dict(mixer_norm=norm("n1"), mixer=mixer, ffn_norm=norm("n2"), ffn=ffn)))
         return ModelSpec(
             architecture=cfg.architecture, hidden_size=H, vocab_size=cfg.vocab_size, max_position=1024,
             embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": H}, {"weight": ("emb",)}),
@@ -627,7 +627,7 @@ def _register_routed():
                 ffn = PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": c["dense_size"]},
                                {"gate_up.weight": (f"{p}.gate", f"{p}.up"), "down.weight": (f"{p}.down",)})
             norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, {"weight": (f"{p}.{n}",)})
-            layers.append(LayerSpec("prenorm", norm("n1"), mixer, norm("n2"), ffn))
+            layers.append(LayerSpec("prenorm", dict(mixer_norm=norm("n1"), mixer=mixer, ffn_norm=norm("n2"), ffn=ffn)))
         return ModelSpec(
             architecture=cfg.architecture, hidden_size=H, vocab_size=c["vocab_size"], max_position=256,
             embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H}, {"weight": ("emb",)}),
@@ -727,3 +727,235 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
             scale = np.abs(ref[r]).max()
             bad = (err.max(axis=1) > 0.08 * scale).sum()
             assert bad <= 2, f"{r}: {bad} rows off (max abs error {err.max():.2e}, scale {scale:.2f})"
+
+
+# ----------------------------------------------------------------------------- four norms, one cached row per token, positions on a grid
+
+
+def _register_sandwich():
+    """Three things a layer of the built-in kind does not have, each defined here and none of it in the
+    framework (toys for this test; plain torch on the device):
+
+    * an arrangement with four norms, "toy_sandwich": a norm before and a norm after the mixer and the same
+      around the feed-forward, the second of each applied to the sub-block's output before it joins the
+      residual stream; the feed-forward and its norms may be absent from a layer:
+          r += delta;  m = post_mixer(mixer(pre_mixer(r)));  r += m;  delta' = post_ffn(ffn(pre_ffn(r)))
+    * a mixer that keeps ONE row of ``rank`` numbers per token in pages (not keys and values per head):
+          c_t = W_c x_t;  q_t = W_q x_t;  p = softmax_{j <= t}(q_t . c_j / sqrt(rank));  y_t = W_o sum_j p_j c_j
+      with a side-by-side parameter ``qc.weight`` = [W_q | W_c]^T stacked along dim 1 of the checkpoint;
+    * a position encoding that is no table of angles by position: tokens lie on a grid ``width`` wide, the
+      first half of a head is rotated by the row's angle and the second half by the column's.
+    """
+    from atom_b200.config.model_config import ModelConfig
+    from atom_b200.models.registry import register_architecture, registered_architectures
+    from atom_b200.parts import registry
+    from atom_b200.parts.base import Mixer, PositionEncoding
+    from atom_b200.parts.spec import CacheEntry, CacheNeed, LayerSpec, ModelSpec, ParamSpec, PartSpec, RunEntry
+
+    if "ToySandwichLM" in registered_architectures():
+        return
+
+    @registry.register("arrangement", "toy_sandwich")
+    class Sandwich:
+        slots = {"pre_mixer": "norm", "mixer": "mixer", "post_mixer": "norm",
+                 "pre_ffn": "norm", "ffn": "ffn", "post_ffn": "norm"}
+        optional = ("pre_ffn", "ffn", "post_ffn")
+
+        def __init__(self, pre_mixer, mixer, post_mixer, pre_ffn=None, ffn=None, post_ffn=None):
+            self.pre_mixer, self.mixer, self.post_mixer = pre_mixer, mixer, post_mixer
+            self.pre_ffn, self.ffn, self.post_ffn = pre_ffn, ffn, post_ffn
+
+        def run(self, residual, delta, step, cache, writes_cache):
+            a = self.pre_mixer.add_norm(residual, delta, "sw.pre_mixer")
+            m = self.mixer.forward(a, step, cache, writes_cache)
+            m = self.post_mixer.add_norm(m.float(), None, "sw.post_mixer")
+            if self.ffn is None:
+                return m
+            b = self.pre_ffn.add_norm(residual, m, "sw.pre_ffn")
+            f = self.ffn.forward(b, step)
+            return self.post_ffn.add_norm(f.float(), None, "sw.post_ffn")
+
+    @registry.register("mixer", "toy_latent_rows")
+    class LatentRows(Mixer):
+        def __init__(self, hidden_size: int, rank: int):
+            self.H, self.r = hidden_size, rank
+
+        def params(self):
+            return {"qc.weight": ParamSpec((self.H, 2 * self.r), rows=(self.r, self.r), stack_dim=1),
+                    "o.weight": ParamSpec((self.H, self.r))}
+
+        def cache_need(self):
+            return CacheNeed("pages", entries=(CacheEntry("latent", (self.r,), "float32"),))
+
+        def forward(self, x, step, cache, writes_cache):
+            qc = x.float() @ self.w_qc_weight.float()
+            q, c = qc[:, :self.r], qc[:, self.r:]
+            pages = cache.pages["latent"]                 # [pages, page size, rank]
+            assert pages.shape[1:] == (cache.page_size, self.r) and pages.dtype == torch.float32
+            table = step.block_tables[cache.group]
+            y = torch.empty_like(q)
+            t = 0
+            for i, n in enumerate(step.q_lens):
+                start = step.q_starts[i]
+                pos = torch.arange(start + n, device=x.device)
+                where = table[i, pos // cache.page_size].long() * cache.page_size + pos % cache.page_size
+                flat = pages.view(-1, self.r)
+                if writes_cache:
+                    flat[where[start:]] = c[t:t + n]
+                rows = flat[where]                          # the request's rows, old and new
+                s = (q[t:t + n] @ rows.T) * self.r ** -0.5
+                s = s.masked_fill(pos[None, :] > pos[start:, None], float("-inf"))
+                y[t:t + n] = torch.softmax(s, dim=-1) @ rows
+                t += n
+            return (y @ self.w_o_weight.float().T).to(self.rt.dtype)
+
+    @registry.register("position", "toy_grid_rotary")
+    class GridRotary(PositionEncoding):
+        def __init__(self, head_dim: int, width: int, theta: float):
+            self.hd, self.width, self.theta = head_dim, width, theta
+
+        def apply(self, q, k, step):
+            pos = step.positions.long()
+            half = self.hd // 2
+            inv = 1.0 / (self.theta ** (torch.arange(0, half, 2, dtype=torch.float32, device=q.device) / half))
+            for x in (q, k):
+                for part, p in ((x[..., :half], pos // self.width), (x[..., half:], pos % self.width)):
+                    ang = p.float()[:, None] * inv[None, :]
+                    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+                    a, b = part[..., :half // 2].float().clone(), part[..., half // 2:].float().clone()
+                    part[..., :half // 2] = (a * cos - b * sin).to(x.dtype)
+                    part[..., half // 2:] = (b * cos + a * sin).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class SandwichConfig(ModelConfig):
+        d: Any = None
+
+        def to_dict(self) -> Dict[str, Any]:
+            return dict(self.d)
+
+    def from_dict(d):
+        return SandwichConfig("ToySandwichLM", tuple(sorted(d.items())))
+
+    def build_spec(cfg):
+        c = dict(cfg.d)
+        H = c["hidden_size"]
+        grid = PartSpec("toy_grid_rotary", {"head_dim": c["head_dim"], "width": c["grid_width"], "theta": 100.0})
+        layers = []
+        for i in range(c["num_hidden_layers"]):
+            p = f"l{i}"
+            norm = lambda n: PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, {"weight": (f"{p}.{n}",)})
+            if i % 2 == 0:
+                mixer = PartSpec("toy_latent_rows", {"hidden_size": H, "rank": c["rank"]},
+                                 {"qc.weight": (f"{p}.wq", f"{p}.wc"), "o.weight": (f"{p}.wo",)})
+            else:
+                mixer = PartSpec("paged_attention",
+                                 dict(hidden_size=H, num_heads=c["heads"], num_kv_heads=1, head_dim=c["head_dim"],
+                                      position=grid, qk_norm=True, norm_eps=c["eps"]),
+                                 {"qkv.weight": (f"{p}.q", f"{p}.k", f"{p}.v"), "o.weight": (f"{p}.o",),
+                                  "q_norm.weight": (f"{p}.qn",), "k_norm.weight": (f"{p}.kn",)})
+            parts = {"pre_mixer": norm("n1"), "mixer": mixer, "post_mixer": norm("n2")}
+            if i != 1:                                # layer 1 has no feed-forward at all
+                parts.update({"pre_ffn": norm("n3"), "post_ffn": norm("n4"),
+                              "ffn": PartSpec("gated_silu", {"hidden_size": H, "intermediate_size": c["inter"]},
+                                              {"gate_up.weight": (f"{p}.gate", f"{p}.up"),
+                                               "down.weight": (f"{p}.down",)})})
+            layers.append(LayerSpec("toy_sandwich", parts))
+        return ModelSpec(
+            architecture=cfg.architecture, hidden_size=H, vocab_size=c["vocab_size"], max_position=256,
+            embedding=PartSpec("token_embedding", {"vocab_size": c["vocab_size"], "hidden_size": H}, {"weight": ("emb",)}),
+            layers=tuple(layers), run_order=tuple(RunEntry(i, i) for i in range(c["num_hidden_layers"])),
+            final_norm=PartSpec("rmsnorm", {"size": H, "eps": c["eps"]}, {"weight": ("norm",)}),
+            lm_head=PartSpec("lm_head", {"vocab_size": c["vocab_size"], "hidden_size": H, "tied": False},
+                             {"weight": ("head",)}))
+
+    register_architecture("ToySandwichLM", from_dict, build_spec)
+
+
+_SANDWICH = {"architectures": ["ToySandwichLM"], "hidden_size": 48, "num_hidden_layers": 4, "vocab_size": 83,
+             "inter": 56, "eps": 1e-5, "rank": 12, "heads": 3, "head_dim": 16, "grid_width": 5}
+
+
+def _sandwich_plain(model_dir, tokens):
+    """The toy architecture written out plainly: whole sequence, float64, no cache."""
+    c = plain.read_config(model_dir)
+    w = plain.read_tensors(model_dir)
+    H, eps, r, nh, hd, gw = c["hidden_size"], c["eps"], c["rank"], c["heads"], c["head_dim"], c["grid_width"]
+    T = len(tokens)
+    pos = torch.arange(T)
+    causal = pos[None, :] > pos[:, None]
+
+    def grid_rotate(x):                                   # [T, heads, hd]
+        half = hd // 2
+        inv = 1.0 / (100.0 ** (torch.arange(0, half, 2, dtype=torch.float64) / half))
+        out = x.clone()
+        for sl, p in ((slice(0, half), pos // gw), (slice(half, hd), pos % gw)):
+            ang = p.double()[:, None] * inv[None, :]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            a, b = x[..., sl][..., :half // 2], x[..., sl][..., half // 2:]
+            out[..., sl] = torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1)
+        return out
+
+    res = w["emb"][torch.as_tensor(tokens)]
+    for i in range(c["num_hidden_layers"]):
+        p = f"l{i}"
+        a = plain.rms_norm(res, w[f"{p}.n1"], eps)
+        if i % 2 == 0:
+            q, lat = a @ w[f"{p}.wq"], a @ w[f"{p}.wc"]
+            s = ((q @ lat.T) * r ** -0.5).masked_fill(causal, float("-inf"))
+            m = (torch.softmax(s, dim=-1) @ lat) @ w[f"{p}.wo"].T
+        else:
+            q = plain.rms_norm((a @ w[f"{p}.q"].T).view(T, nh, hd), w[f"{p}.qn"], eps)
+            k = plain.rms_norm((a @ w[f"{p}.k"].T).view(T, 1, hd), w[f"{p}.kn"], eps)
+            v = (a @ w[f"{p}.v"].T).view(T, 1, hd)
+            o = plain.causal_attention(grid_rotate(q), grid_rotate(k), v, hd ** -0.5)
+            m = o.reshape(T, nh * hd) @ w[f"{p}.o"].T
+        res = res + plain.rms_norm(m, w[f"{p}.n2"], eps)
+        if i != 1:
+            b = plain.rms_norm(res, w[f"{p}.n3"], eps)
+            gu = torch.cat((b @ w[f"{p}.gate"].T, b @ w[f"{p}.up"].T), dim=-1)
+            res = res + plain.rms_norm(plain.silu_and_mul(gu) @ w[f"{p}.down"].T, w[f"{p}.n4"], eps)
+    return (plain.rms_norm(res, w["norm"], eps) @ w["head"].T).numpy()
+
+
+def test_toy_arrangement_with_four_norms_latent_cache_rows_and_grid_positions(tmp_path):
+    """Registered here, built from a random-weights folder and stepped through ModelRunner without a change
+    to the package: an arrangement of its own (four norms; a layer without feed-forward), a mixer whose pages
+    hold one 32-bit row per token beside attention layers whose pages hold keys and values (two page groups
+    with block tables of their own), a parameter stacked side by side, and a position encoding applied
+    between the mixer's norm and its cache write.  Portions beside single tokens, pages used again."""
+    from atom_b200.config import EngineConfig, config_from_dict
+    from atom_b200.engine.batch import StepEntry
+    from atom_b200.engine.runner import ModelRunner
+    from atom_b200.weights import write_random_model
+
+    _register_sandwich()
+    d = str(tmp_path / "sandwich")
+    write_random_model(d, config_from_dict(_SANDWICH), seed=33)
+    runner = ModelRunner(EngineConfig(model=d, dtype="float32", kv_cache_block_size=8, num_kvcache_blocks=10,
+                                      max_num_seqs=3, enforce_eager=True))
+    assert len(runner.cache.groups) == 2
+    assert sorted(tuple(e.name for e in g.entries) for g in runner.cache.groups) == [("k", "v"), ("latent",)]
+    rng = np.random.default_rng(5)
+    seqs = {"x": rng.integers(0, 83, 37).tolist(), "y": rng.integers(0, 83, 22).tolist(),
+            "z": rng.integers(0, 83, 30).tolist()}
+    ref = {r: _sandwich_plain(d, t) for r, t in seqs.items()}
+    got, done = {r: [] for r in seqs}, {r: 0 for r in seqs}
+    # 10 pages of 8 tokens in each group: x (37) and y (22) hold 8, z (30) needs 4: two of them were y's
+    plan = [{"x": 13}, {"x": 2, "y": 19}, {"x": 1, "y": 1}, {"x": 20, "y": 2}, {"x": 1, "z": 9}, {"z": 19}, {"z": 2}]
+    for portions in plan:
+        entries = [StepEntry(r, seqs[r][done[r]:done[r] + n], list(range(n))) for r, n in portions.items()]
+        logits = runner.step(entries).cpu().numpy()
+        o = 0
+        for r, n in portions.items():
+            got[r].append(logits[o:o + n])
+            o += n
+            done[r] += n
+            if done[r] == len(seqs[r]):
+                runner.finish(r)
+    runner.check_status()
+    runner.cache.check()
+    for r in seqs:
+        assert done[r] == len(seqs[r])
+        err = np.abs(np.concatenate(got[r]) - ref[r]).max()
+        assert err < 2e-4, f"{r}: max abs error {err:.2e}"
+    assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups)

@@ -170,3 +170,40 @@ def test_missing_shard_named_by_index(model_dirs, tmp_path):
         json.dump({"weight_map": {"a": "model-00001-of-00002.safetensors"}}, f)
     with pytest.raises(FileNotFoundError):
         load_weights(_model(d), d, torch.bfloat16, "cpu")
+
+
+def test_parameter_stacked_side_by_side_and_parts_named_by_the_arrangement(tmp_path):
+    """A parameter may be several checkpoint tensors side by side (ParamSpec.stack_dim = 1), and a layer's
+    parts are those its arrangement declares: the toy architecture of tests/test_parts_gpu.py has four
+    norms in a layer, and a layer without a feed-forward."""
+    import test_parts_gpu as toys
+    from atom_b200.config import config_from_dict
+    from atom_b200.parts.spec import LayerSpec
+
+    toys._register_sandwich()
+    d = str(tmp_path)
+    write_random_model(d, config_from_dict(toys._SANDWICH), seed=1)
+    m = _model(d)
+    raw = load_file(os.path.join(d, "model.safetensors"))
+    w = load_weights(m, d, torch.bfloat16, "cpu")
+    assert torch.equal(w["layers.0.mixer.qc.weight"], torch.cat([raw["l0.wq"], raw["l0.wc"]], dim=1))
+    assert raw["l0.wq"].shape == (48, 12)
+    names = {n for n, _, _ in m.named_parts()}
+    assert {"layers.0.pre_mixer", "layers.0.post_mixer", "layers.0.pre_ffn", "layers.0.post_ffn"} <= names
+    assert "layers.1.ffn" not in names and "layers.1.post_mixer" in names
+    # a wrong width of one of the side-by-side tensors is a shape error that names it
+    raw["l0.wc"] = torch.zeros(48, 11, dtype=torch.bfloat16)
+    save_file(raw, os.path.join(d, "model.safetensors"))
+    with pytest.raises(WeightError) as e:
+        load_weights(m, d, torch.bfloat16, "cpu")
+    assert "l0.wc" in str(e.value) and "[48, 12]" in str(e.value)
+    # a layer that lacks a part its arrangement needs, or names one it does not know, is refused
+    spec = m.spec
+    broken = {k: v for k, v in spec.layers[0].parts.items() if k != "post_mixer"}
+    with pytest.raises(ValueError, match="post_mixer"):
+        Model(type(spec)(**{**spec.__dict__, "layers": (LayerSpec("toy_sandwich", broken),),
+                            "run_order": spec.run_order[:1]}))
+    with pytest.raises(ValueError, match="gate_norm"):
+        Model(type(spec)(**{**spec.__dict__, "layers": (
+            LayerSpec("prenorm", {**spec.layers[0].parts, "gate_norm": spec.final_norm}),),
+            "run_order": spec.run_order[:1]}))
