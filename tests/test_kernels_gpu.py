@@ -571,3 +571,51 @@ def test_gemm_smallm_refuses_other_sizes(native):
     assert not native.gemm_smallm_supports(17, 64, 64, 64)
     assert not native.gemm_smallm_supports(4, 64, 96, 96)      # K no multiple of 64
     assert not native.gemm_smallm_supports(4, 64, 64, 100)     # leading dimension no multiple of 8
+
+
+# ----------------------------------------------------------------------------- both sides of every launch choice
+
+
+@pytest.mark.parametrize("name,value", [("pdl", 0), ("decode_tma", 0), ("decode_ktw", 16), ("decode_ktw", 32),
+                                        ("gemm_row_tile", 1), ("gemm_row_tile", 2), ("gemm_row_tile", 4),
+                                        ("gemm_cut", 0), ("gemm_cut", 1)])
+def test_forced_launch_choices_give_the_same_results(native, name, value):
+    """The launch code chooses between kernels and tilings by itself (dependent launch, the TMA decode kernel
+    and its warp tile, the streaming product's row tile, ranges cut inside slabs); ``set_option`` forces a
+    side.  Each forced side is checked against the dense references, so no path runs only at sizes the
+    default happens to send there."""
+    try:
+        native.set_option(name, value)
+        # decode attention: 16 packed rows, several splits, a request shorter than a page
+        nh, nkv, hd, page = 16, 4, 128, 16
+        q_lens, ctx_lens = [1, 2, 1, 1], [1000, 130, 7, 2049]
+        q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=91)
+        want = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, hd ** -0.5, 0)
+        got = _run_attention(native, "flash", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, hd ** -0.5, 0,
+                             force_splits=3)
+        assert (got - want).abs().max().item() <= 2e-2
+        # the streaming product: plain with bias, and gated; sizes with whole and with shared slabs
+        for M, N, K, gated in ((8, 4096, 12288, False), (3, 1000, 576, False), (5, 2048, 1024, True)):
+            if name == "gemm_row_tile" and gated and value % 2:
+                continue                     # (a gated slab holds gate and up rows: an even row tile)
+            a = _rand((M, K), torch.bfloat16, 92)
+            w = _rand(((2 if gated else 1) * N, K), torch.bfloat16, 93, 0.3)
+            bias = None if gated else _rand((N,), torch.bfloat16, 94)
+            out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+            native.gemm_smallm(out, a, w, bias, gated=gated)
+            acc = a.double() @ w.double().T
+            ref = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:] if gated else acc + bias.double()
+            torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=2e-2 * math.sqrt(K / 96))
+        # a small kernel chain under the same launch mode: norm, then rows gathered
+        x = _rand((5, 320), torch.bfloat16, 95)
+        res = _rand((5, 320), torch.float32, 96)
+        wn = (_rand((320,), torch.float32, 97) * 0.1 + 1).to(torch.bfloat16)
+        out = torch.empty((5, 320), dtype=torch.bfloat16, device=DEV)
+        r0 = res.clone()
+        native.add_rmsnorm(out, res, x, wn, 1e-6, None, 5)
+        rr = r0.double() + x.double()
+        ref = rr * torch.rsqrt(rr.pow(2).mean(-1, keepdim=True) + 1e-6) * wn.double()
+        torch.testing.assert_close(out.double(), ref, rtol=2e-2, atol=2e-2)
+        native.check_error_flags()
+    finally:
+        native.reset_options()

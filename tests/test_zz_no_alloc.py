@@ -5,7 +5,8 @@ host program that owns the memory pool, a real-time loop that must not enter the
 so ``atom_flash_attention_static`` takes its split-K scratch from an array compiled into the
 library.  Here it is called twice in a row, with different shapes so that the second call
 finds the first one's leftovers in the shared array, and its output is compared with the
-regular entry point's, which gets its scratch from the caller.  A call that would need more
+regular entry point's, which gets its scratch from the caller, and with a dense float reference.
+A call that would need more
 scratch than the array holds must be refused before anything runs.
 
 This file is collected last, so a run that stops at the first failure has run all others.
@@ -24,10 +25,11 @@ SCRATCH_FLOATS = 2 * 1024 * 1024
 
 
 def _case(q_lens, ctx_lens, nh, nkv, hd, page, seed):
-    from test_kernels_gpu import _paged_case
+    from test_kernels_gpu import _paged_case, _ref_attention
 
-    q, kp, vp, bt, _ = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed)
+    q, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed)
     T = sum(q_lens)
+    _case.dense_ref = _ref_attention(q, dense, q_lens, ctx_lens, nh, nkv, hd ** -0.5, 0)   # [T, nh, hd], dense float reference
     d = lambda x: x.to(DEV).contiguous()
     cu = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=DEV)
     ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
@@ -70,6 +72,9 @@ def test_static_scratch_entry_point_matches_regular(hd):
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+        # and against the dense reference that shares no kernel with either entry point
+        ref = _case.dense_ref.reshape(T, nh * hd)
+        assert (got.float().cpu() - ref).abs().max().item() <= 2e-2
 
     # beyond the array's size: refused, nothing written
     T_big = SCRATCH_FLOATS // (nh * 64 * (hd + 2)) + 1
