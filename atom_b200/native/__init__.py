@@ -72,6 +72,9 @@ _SIGNATURES = {
     "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i64, _vp],
     "atom_gemm_smallm_scratch_bytes": [_i],
     "atom_gemm_smallm_supports": [_i, _i, _i, _i64],
+    "atom_gemm_rows": [_vp, _i, _vp, _vp],
+    "atom_gemm_rows_grid": [],
+    "atom_gemm_rows_supports": [_i, _i, _i, _i64],
     "atom_set_option": [_i, _i],
     "atom_copy_rows_h2d": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
 }
@@ -394,6 +397,67 @@ def gemm_smallm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optio
         out.data_ptr(), dtype_code(out.dtype), out.stride(0), a.data_ptr(), a.stride(0), w.data_ptr(),
         _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, M, N, K, int(gated),
         error_flag(out.device).data_ptr(), scratch.data_ptr(), scratch.numel(), _stream()), "gemm_smallm")
+
+
+class _RowsOpC(ctypes.Structure):
+    """csrc/gemm_rows.h: AtomRowsOp."""
+    _fields_ = [("X", _vp), ("lda", _i64), ("W", _vp), ("out", _vp), ("out_dtype", _i), ("ldc", _i64),
+                ("bias", _vp), ("bias_dtype", _i), ("N", _i), ("K", _i), ("gated", _i),
+                ("ssq_in", _vp), ("ssq_parts", _i), ("norm_size", _i), ("norm_eps", _f),
+                ("residual", _vp), ("norm_w", _vp), ("norm_w_dtype", _i), ("xout", _vp), ("ssq_out", _vp)]
+
+
+ROWS_M = 8      # rows up to which the row-sharing product is used (it takes 16)
+
+
+def gemm_rows_grid() -> int:
+    """CTAs of a ``gemm_rows`` launch: a residual product writes one part of the rows' sums of squares per CTA."""
+    return int(lib().atom_gemm_rows_grid())
+
+
+def gemm_rows_supports(M: int, N: int, K: int, lda: int) -> bool:
+    return bool(lib().atom_gemm_rows_supports(M, N, K, lda))
+
+
+def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+              bias: Optional[torch.Tensor] = None, gated: bool = False, ssq_in: Optional[torch.Tensor] = None,
+              norm_size: int = 0, norm_eps: float = 0.0, residual: Optional[torch.Tensor] = None,
+              norm_w: Optional[torch.Tensor] = None, xout: Optional[torch.Tensor] = None,
+              ssq_out: Optional[torch.Tensor] = None) -> None:
+    """out[M, N] = x[M, K] w[N, K]^T for at most 16 rows of bf16 x, with one of the epilogues of
+    csrc/gemm_rows.h: plain (+ bias; out bf16 or float32); ``gated`` (w = [gate ; up] of 2N rows);
+    ``residual`` (float32 [M, N], += product in place, with ``xout`` = bf16(residual * norm_w) and the CTAs'
+    sums of squares in ``ssq_out`` [gemm_rows_grid(), 16]).  ``ssq_in`` (such sums, of ``norm_size`` columns):
+    every output row is first multiplied by its rstd."""
+    M, K = x.shape
+    res = residual is not None
+    N = residual.shape[1] if res else out.shape[1]
+    _cuda(x, w, out, bias, ssq_in, residual, norm_w, xout, ssq_out)
+    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous() and x.stride(1) == 1
+    assert w.shape[0] == (2 * N if gated else N)
+    c = _RowsOpC()
+    if res:
+        assert residual.dtype == torch.float32 and residual.is_contiguous() and residual.shape[0] == M
+        assert xout.dtype == torch.bfloat16 and xout.is_contiguous() and xout.shape == residual.shape
+        assert ssq_out.dtype == torch.float32 and ssq_out.shape == (gemm_rows_grid(), 16) and ssq_out.is_contiguous()
+        assert norm_w.numel() == N and norm_w.is_contiguous()
+    else:
+        assert out.shape[0] == M and out.stride(1) == 1
+    if ssq_in is not None:
+        assert ssq_in.dtype == torch.float32 and ssq_in.is_contiguous() and ssq_in.shape[-1] == 16
+    c.X, c.lda, c.W = x.data_ptr(), x.stride(0), w.data_ptr()
+    c.out = _ptr(out)
+    c.out_dtype = dtype_code(out.dtype) if out is not None else BF16
+    c.ldc = out.stride(0) if out is not None else 0
+    c.bias, c.bias_dtype = _ptr(bias), (dtype_code(bias.dtype) if bias is not None else F32)
+    c.N, c.K, c.gated = N, K, int(gated)
+    c.ssq_in = _ptr(ssq_in)
+    c.ssq_parts = ssq_in.numel() // 16 if ssq_in is not None else 0
+    c.norm_size, c.norm_eps = int(norm_size), float(norm_eps)
+    c.residual, c.norm_w = _ptr(residual), _ptr(norm_w)
+    c.norm_w_dtype = dtype_code(norm_w.dtype) if norm_w is not None else F32
+    c.xout, c.ssq_out = _ptr(xout), _ptr(ssq_out)
+    _check(lib().atom_gemm_rows(ctypes.byref(c), M, error_flag(x.device).data_ptr(), _stream()), "gemm_rows")
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

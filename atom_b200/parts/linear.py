@@ -1,8 +1,11 @@
 """Matrix product y = x W^T (+ b) with weights [out, in], as atom/model_ops/linear.py:946-965.
 
-bfloat16: for more than 8 rows the GEMM library, as the reference does (tgemm.mm,
-linear.py:960); for up to 8 rows (decode) the framework's weight-streaming kernel.  Both
-accumulate in 32-bit.  float32: the framework's own FMA kernel, never a reduced-precision mode.
+bfloat16: for many rows the GEMM library, as the reference does (tgemm.mm, linear.py:960); for
+few rows (decode) the framework's weight-streaming kernels: the one that shares out rows of W
+among the CTAs (``native.gemm_rows``, up to ``native.ROWS_M`` rows, K a multiple of 64), else
+the one that shares out slabs and k ranges (``native.gemm_smallm``, up to ``native.SMALL_M``
+rows).  All accumulate in 32-bit.  float32: the framework's own FMA kernel, never a
+reduced-precision mode.
 """
 from __future__ import annotations
 
@@ -20,9 +23,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         if b is not None and b.dtype != torch.float32:
             b = b.float()
         native.gemm_f32(out, x, weight, b)
+    elif x.shape[0] <= native.ROWS_M and native.gemm_rows_supports(
+            x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
+        native.gemm_rows(x, weight, out, bias)            # few rows: the product is a read of W
     elif x.shape[0] <= native.SMALL_M and native.gemm_smallm_supports(
             x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
-        native.gemm_smallm(out, x, weight, bias)          # few rows: the product is a read of W
+        native.gemm_smallm(out, x, weight, bias)
     else:
         native.gemm_bf16(out, x, weight)
         if bias is not None:
@@ -36,6 +42,9 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scrat
     ``scratch(M, 2I)`` and the activation kernel."""
     M, K = x.shape
     I = weight.shape[0] // 2
+    if x.dtype == torch.bfloat16 and M <= native.ROWS_M and native.gemm_rows_supports(M, I, K, x.stride(0)):
+        native.gemm_rows(x, weight, out, gated=True)
+        return out
     if (x.dtype == torch.bfloat16 and M <= native.SMALL_M
             and native.gemm_smallm_supports(M, I, K, x.stride(0))):
         native.gemm_smallm(out, x, weight, None, gated=True)

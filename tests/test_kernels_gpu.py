@@ -573,6 +573,106 @@ def test_gemm_smallm_refuses_other_sizes(native):
     assert not native.gemm_smallm_supports(4, 64, 64, 100)     # leading dimension no multiple of 8
 
 
+# ----------------------------------------------------------------------------- few-row product that shares out rows of W
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 389, 64), (3, 130, 320), (8, 4096, 4096), (9, 1000, 576), (16, 77, 1024),
+                                   (7, 301, 192), (4, 200, 448), (13, 9600, 2112), (2, 2500, 512), (5, 151, 12288),
+                                   (8, 10007, 128), (6, 151936, 64)])
+def test_gemm_rows(native, out_dtype, M, N, K):
+    """Fewer rows of W than CTAs, one sub-slab, several sub-slabs of a height that is no multiple of 16,
+    a last sub-slab that is shorter, k of one chunk and of many stages; both token tiles."""
+    a, w = _rand((M, K), torch.bfloat16, 30), _rand((N, K), torch.bfloat16, 31)
+    bias = _rand((N,), torch.bfloat16 if N % 4 == 1 else torch.float32, 32) if N % 2 else None
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    assert native.gemm_rows_supports(M, N, K, K)
+    native.gemm_rows(a, w, out, bias)
+    native.check_error_flags()
+    want = a.float() @ w.float().T + (bias.float() if bias is not None else 0)
+    torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 160, 128), (7, 1001, 320), (8, 12288, 4096), (12, 112, 64), (16, 333, 1024),
+                                   (3, 5000, 192)])
+def test_gemm_rows_gated(native, M, I, K):
+    a, w = _rand((M, K), torch.bfloat16, 33), _rand((2 * I, K), torch.bfloat16, 34, 0.3)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    native.gemm_rows(a, w, out, gated=True)
+    native.check_error_flags()
+    gu = a.double() @ w.double().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    torch.testing.assert_close(out.double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
+
+
+def test_gemm_rows_strided_input_and_output(native):
+    """X and the output may be column ranges of wider arrays (the leading dimensions are passed on)."""
+    M, N, K = 5, 700, 256
+    big_a = _rand((M, K + 64), torch.bfloat16, 50)
+    w = _rand((N, K), torch.bfloat16, 51)
+    big_out = torch.full((M, N + 24), float("nan"), dtype=torch.float32, device=DEV)
+    native.gemm_rows(big_a[:, 64:], w, big_out[:, 8:8 + N])
+    native.check_error_flags()
+    torch.testing.assert_close(big_out[:, 8:8 + N], big_a[:, 64:].float() @ w.float().T, rtol=2e-3, atol=5e-3)
+    assert torch.isnan(big_out[:, :8]).all() and torch.isnan(big_out[:, 8 + N:]).all()
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(native):
+    """A row's result does not depend on the rows beside it: bit-equal whatever the number of rows."""
+    N, K = 520, 1088
+    a, w = _rand((16, K), torch.bfloat16, 35), _rand((N, K), torch.bfloat16, 36)
+    outs = {}
+    for m in (1, 5, 8, 9, 16):
+        outs[m] = torch.empty((m, N), dtype=torch.float32, device=DEV)
+        native.gemm_rows(a[:m], w, outs[m])
+    native.check_error_flags()
+    for m in (1, 5, 8, 9):
+        assert torch.equal(outs[m], outs[16][:m])
+    torch.testing.assert_close(outs[16], a.float() @ w.float().T, rtol=2e-3, atol=5e-3)
+
+
+@pytest.mark.parametrize("M,H,I,wdtype", [(8, 4096, 12288, torch.bfloat16), (3, 320, 960, torch.float32),
+                                          (1, 64, 192, torch.float32), (11, 1088, 2112, torch.bfloat16)])
+def test_gemm_rows_norm_without_a_pass_of_its_own(native, M, H, I, wdtype):
+    """A product in residual mode followed by a product that multiplies its rows by rstd is the residual
+    add, the RMSNorm and the product of the plain formulas:  r += a Wo^T;  y = RMSNorm(r; w) W2^T.
+    Checked against float64 for a plain second product with a bias and for a gated one; the residual
+    stream itself must be the exact 32-bit sum of the old residual and the product."""
+    eps = 1e-5
+    G = native.gemm_rows_grid()
+    a = _rand((M, I), torch.bfloat16, 60)
+    wo = _rand((H, I), torch.bfloat16, 61, I ** -0.5)
+    res0 = _rand((M, H), torch.float32, 62)
+    nw = (_rand((H,), torch.float32, 63) * 0.2 + 1).to(wdtype)
+    w2 = _rand((2 * I, H), torch.bfloat16, 64, H ** -0.5)
+    bias = _rand((2 * I,), torch.float32, 65)
+    res = res0.clone()
+    xw = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ssq = torch.full((G, 16), float("nan"), dtype=torch.float32, device=DEV)
+    native.gemm_rows(a, wo, residual=res, norm_w=nw, xout=xw, ssq_out=ssq)
+    plain = torch.full((M, 2 * I), float("nan"), dtype=torch.float32, device=DEV)
+    gated = torch.full((M, I), float("nan"), dtype=torch.float32, device=DEV)
+    native.gemm_rows(xw, w2, plain, bias, ssq_in=ssq, norm_size=H, norm_eps=eps)
+    native.gemm_rows(xw, w2, gated, gated=True, ssq_in=ssq, norm_size=H, norm_eps=eps)
+    native.check_error_flags()
+    r = res0.double() + a.double() @ wo.double().T
+    torch.testing.assert_close(res.double(), r, rtol=1e-5, atol=2e-5 * math.sqrt(I / 96))
+    torch.testing.assert_close(ssq[:, :M].double().sum(0), res.double().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+    assert (ssq[:, M:] == 0).all()
+    y = r * torch.rsqrt(r.pow(2).mean(-1, keepdim=True) + eps) * nw.double()
+    full = y @ w2.double().T
+    torch.testing.assert_close(plain.double(), full + bias.double(), rtol=1e-2, atol=1.5e-2 * math.sqrt(H / 96))
+    torch.testing.assert_close(gated.double(), torch.nn.functional.silu(full[:, :I]) * full[:, I:],
+                               rtol=2e-2, atol=2e-2 * math.sqrt(H / 96))
+
+
+def test_gemm_rows_refuses_other_sizes(native):
+    assert not native.gemm_rows_supports(17, 64, 64, 64)
+    assert not native.gemm_rows_supports(4, 64, 96, 96)      # K no multiple of 64
+    assert not native.gemm_rows_supports(4, 64, 64, 100)     # leading dimension no multiple of 8
+    assert not native.gemm_rows_supports(4, 64, 32, 32)
+
+
 # ----------------------------------------------------------------------------- both sides of every launch choice
 
 
