@@ -13,6 +13,7 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
 from ..parts import registry
 from ..parts.base import Part, Runtime
+from ..parts.linear import resolve
 from ..parts.spec import CacheNeed, ModelSpec, PartSpec
 
 
@@ -103,6 +104,9 @@ class Model:
         residual = self.embedding.forward(step.token_ids, step.num_tokens)
         delta = None
         for e in self.spec.run_order:
-            delta = self.blocks[e.layer].run(residual, delta, step, caches.get(e.cache), e.writes_cache)
-        y = self.final_norm.add_norm(residual, delta, "norm.final", step.logits_rows, step.num_logits_rows)
+            block = self.blocks[e.layer]
+            if not getattr(block, "takes_pending", False):
+                delta = resolve(delta)      # (a block may hand its last product on unrun)
+            delta = block.run(residual, delta, step, caches.get(e.cache), e.writes_cache)
+        y = self.final_norm.add_norm(residual, resolve(delta), "norm.final", step.logits_rows, step.num_logits_rows)
         return self.lm_head.forward(y, step.logits_out)

@@ -16,11 +16,13 @@
 //
 // Warps: one streams W into the ring and never waits for the kernels before this one (W is written by
 // nobody), so the first ring of weights arrives while they finish; one brings the X columns of a stage
-// once the kernels before have completed; sixteen consume (one mma.sync warp per scheduler keeps the
-// tensor cores busy for a fraction of the time only, and with a handful of stages per CTA the
-// consumers' time per stage is on the critical path): 8 along k (one 64-k chunk each) times 2 over the
-// 16-row tiles.  At a sub-slab's end the warps' sums meet in shared memory and each of the 512
-// consumer threads settles one output (a single epilogue warp took 2-5 us for it).
+// once the kernels before have completed; one turns the sums of squares into the rows' factors beside
+// the stream (inside the X producer it held the stages' X back by 1-2 us); sixteen consume (one
+// mma.sync warp per scheduler keeps the tensor cores busy for a fraction of the time only, and with a
+// handful of stages per CTA the consumers' time per stage is on the critical path): 8 along k (one
+// 64-k chunk each) times 2 over the 16-row tiles.  At a sub-slab's end the warps' sums meet in shared
+// memory and each of the 512 consumer threads settles one output (a single epilogue warp took 2-5 us
+// for it).
 //
 // The norm between two products needs no pass of its own:
 //     RMSNorm(r) W^T = rstd(r) * ((r . w) W^T)
@@ -39,7 +41,7 @@ namespace rows {
 using namespace atom::smallm;
 
 constexpr int KG = 8, TG = 2, NCW = KG * TG;      // consumer warps: k groups times tile groups
-constexpr int CTHREADS = (NCW + 2) * 32;          // consumers, W producer, X producer
+constexpr int CTHREADS = (NCW + 3) * 32;          // consumers, W producer, X producer, the rows' factors
 constexpr int KC_MAX = 8;                         // chunks of 64 k in a stage, at most
 constexpr int RLD = 65;                           // stride of the buffer of sums [k group][token][row]
 
@@ -186,16 +188,11 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) prefetch_map(&map_x);
     atom::pdl_wait();
     const uint32_t x_bytes = (uint32_t)(KC * MP * 128);
-    bool need_scale = p.ssq_in != nullptr;
     int s = 0, u = 0;
     long long it = 0;
     for (int sl = 0; sl < p.S; ++sl) {
       if (R0 + sl * h >= R1) break;
       for (int kt = 0; kt < p.num_kt; ++kt, ++it) {
-        if (need_scale && it == NS) {       // the first stages' X is on its way: now the rows' factors
-          need_scale = false;
-          row_factors(p, row_scale, scale_bar, lane);
-        }
         if (it >= NS) mbar_wait(&empty[s], (u & 1) ^ 1, &aborted, p.error);
         unsigned char* stage = ring + (size_t)s * STAGE;
         if (lane == 0) {
@@ -208,7 +205,15 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
       }
     }
-    if (need_scale) row_factors(p, row_scale, scale_bar, lane);
+    return;
+  }
+
+  if (warp == NCW + 2) {
+    // ---------------------------------------------------------------- the rows' factors, beside the stream
+    if (p.ssq_in != nullptr) {
+      atom::pdl_wait();
+      row_factors(p, row_scale, scale_bar, lane);
+    }
     return;
   }
 

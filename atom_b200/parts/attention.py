@@ -18,13 +18,16 @@ import torch
 from .. import native
 from . import registry
 from .base import Mixer, PositionEncoding
-from .linear import linear
+from .linear import PendingProduct, linear, may_defer
 from .registry import register
 from .spec import CacheNeed, ParamSpec, PartSpec
 
 
 @register("mixer", "paged_attention")
 class PagedAttention(Mixer):
+    takes_scaled_rows = True      # x may be ScaledRows: the qkv product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the output projection on unrun
+
     @property
     def graph_safe(self) -> bool:      # its own launches are; the position encoding answers for itself
         return self.position.graph_safe
@@ -66,7 +69,7 @@ class PagedAttention(Mixer):
         if self.hd > 512:
             raise ValueError(f"paged_attention: head_dim {self.hd} is beyond what the kernels take (512)")
 
-    def forward(self, x, step, cache, writes_cache):
+    def forward(self, x, step, cache, writes_cache, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
         nh, nkv, hd = self.nh, self.nkv, self.hd
@@ -93,7 +96,10 @@ class PagedAttention(Mixer):
                                            step.seq_of_token, bt, cache.page_size, kp, vp, step.status)
         o = ws.get("attn.o", (T, nh * hd), dt)
         self.attend(o, qkv, step, cache, bt)
-        return linear(o, self.w_o_weight, None, ws.get("attn.out", (T, self.hidden_size), dt))
+        out = ws.get("attn.out", (T, self.hidden_size), dt)
+        if defer and may_defer(o, self.w_o_weight):
+            return PendingProduct(o, self.w_o_weight, None, out)
+        return linear(o, self.w_o_weight, None, out)
 
     def launch_plan(self, step):
         """The attention kernels' plan for this step: tile counts and the number of splits along the

@@ -109,8 +109,20 @@ class Part:
         process_weights_after_loading, atom/model_loader/loader.py:354-360.)"""
 
 
+# What a mixer or a feed-forward may say about itself, beside its interface (both default to False; the
+# arrangement asks before it uses either, so a part that says nothing gets and gives plain tensors):
+#   takes_scaled_rows  x may come as parts.linear.ScaledRows (rows whose RMSNorm the part's first product
+#                      finishes; ``linear`` and ``gated_linear`` take them as they take a tensor);
+#   defers_output      ``forward`` takes the keyword ``defer``; with defer=True it may return its last
+#                      product unrun, as a parts.linear.PendingProduct.
+# A norm that says ``fuses_products`` takes a PendingProduct as delta and the keyword ``scaled_ok``
+# (the receiver of its rows takes ScaledRows).
+
+
 class Norm(Part):
     """``add_norm``: residual (+= delta), returns the normalised rows in the compute type."""
+
+    fuses_products = False
 
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], tag: str,
                  rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
@@ -148,6 +160,9 @@ class Mixer(Part):
     token: the storage clears the slot at admission, also for a preempted request that is computed
     again.  Pages are not cleared; a mixer reads only positions its request has written."""
 
+    takes_scaled_rows = False
+    defers_output = False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
@@ -158,5 +173,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_scaled_rows = False
+    defers_output = False
+
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         raise NotImplementedError

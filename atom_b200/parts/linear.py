@@ -16,8 +16,59 @@ import torch
 from .. import native
 
 
+class PendingProduct:
+    """A product out = x W^T (+ bias) of a step with few rows that has been described but not launched.
+    A part hands it on in place of its output where the receiver may fold it into a kernel of its
+    own (the norm that follows adds it to the residual stream in the product's epilogue); whoever
+    cannot use it calls ``run()`` and has the tensor."""
+    __slots__ = ("x", "weight", "bias", "out")
+
+    def __init__(self, x, weight, bias, out):
+        self.x, self.weight, self.bias, self.out = x, weight, bias, out
+
+    def run(self) -> torch.Tensor:
+        return linear(self.x, self.weight, self.bias, self.out)
+
+
+class ScaledRows:
+    """Rows x = bf16(r * w) of a residual stream r whose RMSNorm the next product finishes:
+    RMSNorm(r; w) W^T = rstd(r) * (x W^T), with rstd from the sums of squares ``ssq`` [parts, 16] of r's
+    ``size`` columns.  ``linear`` and ``gated_linear`` take it as their x."""
+    __slots__ = ("x", "ssq", "size", "eps")
+
+    def __init__(self, x, ssq, size, eps):
+        self.x, self.ssq, self.size, self.eps = x, ssq, size, eps
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+
+def resolve(delta):
+    """The tensor of a part's output, whether it came as one or as a product still to run."""
+    return delta.run() if isinstance(delta, PendingProduct) else delta
+
+
+def may_defer(x, weight) -> bool:
+    """Whether out = x W^T is a product that a residual epilogue can take (few rows of bf16, sizes the
+    row-sharing kernel takes)."""
+    if not FOLD_NORMS or isinstance(x, ScaledRows) or x.dtype != torch.bfloat16 or x.shape[0] > native.ROWS_M:
+        return False
+    return native.gemm_rows_supports(x.shape[0], weight.shape[0], x.shape[1], x.stride(0))
+
+
+FOLD_NORMS = True     # False: every norm runs as a kernel of its own (for measurements and tests)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias).  ``out`` may be float32 for bf16 operands."""
+    if isinstance(x, ScaledRows):
+        native.gemm_rows(x.x, weight, out, bias, ssq_in=x.ssq, norm_size=x.size, norm_eps=x.eps)
+        return out
     if x.dtype == torch.float32:
         b = bias
         if b is not None and b.dtype != torch.float32:
@@ -42,6 +93,9 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scrat
     ``scratch(M, 2I)`` and the activation kernel."""
     M, K = x.shape
     I = weight.shape[0] // 2
+    if isinstance(x, ScaledRows):
+        native.gemm_rows(x.x, weight, out, gated=True, ssq_in=x.ssq, norm_size=x.size, norm_eps=x.eps)
+        return out
     if x.dtype == torch.bfloat16 and M <= native.ROWS_M and native.gemm_rows_supports(M, I, K, x.stride(0)):
         native.gemm_rows(x, weight, out, gated=True)
         return out

@@ -5,7 +5,7 @@ from __future__ import annotations
 from typing import Dict
 
 from .base import FeedForward
-from .linear import gated_linear, linear
+from .linear import PendingProduct, gated_linear, linear, may_defer
 from .registry import register
 from .spec import ParamSpec
 
@@ -13,6 +13,8 @@ from .spec import ParamSpec
 @register("ffn", "gated_silu")
 class GatedSiluMLP(FeedForward):
     graph_safe = True
+    takes_scaled_rows = True      # x may be ScaledRows: the first product finishes the norm
+    defers_output = True          # forward(..., defer=True) may hand the last product on unrun
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -24,9 +26,12 @@ class GatedSiluMLP(FeedForward):
             "down.weight": ParamSpec((H, I)),
         }
 
-    def forward(self, x, step):
+    def forward(self, x, step, defer=False):
         T = x.shape[0]
         ws, dt = self.rt.workspace, self.rt.dtype
         f = gated_linear(x, self.w_gate_up_weight, ws.get("ffn.act", (T, self.intermediate_size), dt),
                          lambda m, n: ws.get("ffn.gate_up", (m, n), dt))
-        return linear(f, self.w_down_weight, None, ws.get("ffn.out", (T, self.hidden_size), dt))
+        out = ws.get("ffn.out", (T, self.hidden_size), dt)
+        if defer and may_defer(f, self.w_down_weight):
+            return PendingProduct(f, self.w_down_weight, None, out)
+        return linear(f, self.w_down_weight, None, out)
