@@ -61,13 +61,13 @@ def bench_gemm(args) -> None:
             line = f"{name:8s} rows={M:3d}"
             t = _time_graph([(lambda w=w: native.gemm_bf16(o1, x, w)) for w in ws])
             line += f"  library {t:7.1f} us ({gb / t * 1e6:6.0f} GB/s)"
-            if native.gemm_smallm_supports(M, N, K, K):
-                t = _time_graph([(lambda w=w: native.gemm_smallm(o1, x, w)) for w in ws])
+            if M <= 16 and native.gemm_rows_supports(M, N, K, K):
+                t = _time_graph([(lambda w=w: native.gemm_rows(x, w, o1)) for w in ws])
                 line += f"  streaming {t:7.1f} us ({gb / t * 1e6:6.0f} GB/s)"
                 if name == "gate_up":
                     o2 = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
-                    t = _time_graph([(lambda w=w: native.gemm_smallm(o2, x, w, None, True)) for w in ws])
-                    line += f"  streaming+silu*mul {t:7.1f} us ({gb / t * 1e6:6.0f} GB/s)"
+                    t = _time_graph([(lambda w=w: native.gemm_rows(x, w, o2, gated=True)) for w in ws])
+                    line += f"  +silu*mul {t:7.1f} us ({gb / t * 1e6:6.0f} GB/s)"
             print(line, flush=True)
     native.check_error_flags()
 

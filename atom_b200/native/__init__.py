@@ -69,9 +69,6 @@ _SIGNATURES = {
     "atom_gemm_f32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _vp],
     "atom_gemm_bf16": [_vp, _i, _vp, _vp, _i, _i, _i, _i64, _vp, _sz, _vp],
     "atom_add_bias": [_vp, _i, _vp, _i, _i, _i, _vp],
-    "atom_gemm_smallm": [_vp, _i, _i64, _vp, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i64, _vp],
-    "atom_gemm_smallm_scratch_bytes": [_i],
-    "atom_gemm_smallm_supports": [_i, _i, _i, _i64],
     "atom_gemm_rows": [_vp, _i, _vp, _vp],
     "atom_gemm_rows_grid": [],
     "atom_gemm_rows_supports": [_i, _i, _i, _i64],
@@ -101,7 +98,7 @@ def declare(name: str, args) -> None:
 # Choices the launch code otherwise makes by itself (csrc/common.cuh, ATOM_OPT_*): for measurements
 # and for tests of both sides of a choice.  They hold for launches made after the call; a captured
 # graph keeps what it was recorded with.
-OPTIONS = {"pdl": 0, "decode_tma": 1, "decode_ktw": 2, "gemm_row_tile": 3, "gemm_cut": 4}
+OPTIONS = {"pdl": 0, "decode_tma": 1, "decode_ktw": 2}
 _option_values = {}
 
 
@@ -116,7 +113,7 @@ def set_option(name: str, value: int) -> None:
 
 
 def reset_options() -> None:
-    for name, default in (("pdl", 1), ("decode_tma", 1), ("decode_ktw", 0), ("gemm_row_tile", 0), ("gemm_cut", -1)):
+    for name, default in (("pdl", 1), ("decode_tma", 1), ("decode_ktw", 0)):
         set_option(name, default)
     _option_values.clear()
 
@@ -360,45 +357,6 @@ def check_error_flags() -> None:
             raise NativeError(f"a bounded wait of the attention kernels (head size {hd}) ran out")
 
 
-SMALL_M = 8     # rows up to which the weight-streaming product beats the library's (measured)
-
-
-def gemm_smallm_supports(M: int, N: int, K: int, lda: int) -> bool:
-    return bool(lib().atom_gemm_smallm_supports(M, N, K, lda))
-
-
-_smallm_scratch = {}
-
-
-def _smallm_scratch_for(device: torch.device, n_rows: int) -> torch.Tensor:
-    """Zeroed device memory for the partial sums of W slabs that several CTAs share: one buffer
-    per device, grown (outside graph capture only) when a taller matrix comes."""
-    need = int(lib().atom_gemm_smallm_scratch_bytes(n_rows))
-    buf = _smallm_scratch.get(device)
-    if buf is None or buf.numel() < need:
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("gemm_smallm: first call for this size inside a graph capture; run the step once before")
-        buf = _smallm_scratch[device] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
-    return buf
-
-
-def gemm_smallm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                gated: bool = False) -> None:
-    """out[M,N] (bf16 or f32) = a[M,K] @ w[N,K]^T (+ bias) for M <= 16: the weight-streaming
-    kernel.  gated: w is [2N, K] = [gate ; up] and out = silu(a gate^T) * (a up^T)."""
-    _cuda(out, a, w, bias)
-    M, K = a.shape
-    N = out.shape[1]
-    assert a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous()
-    assert w.shape[0] == (2 * N if gated else N) and out.shape[0] == M
-    assert a.stride(1) == 1 and out.stride(1) == 1
-    scratch = _smallm_scratch_for(out.device, w.shape[0])
-    _check(lib().atom_gemm_smallm(
-        out.data_ptr(), dtype_code(out.dtype), out.stride(0), a.data_ptr(), a.stride(0), w.data_ptr(),
-        _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, M, N, K, int(gated),
-        error_flag(out.device).data_ptr(), scratch.data_ptr(), scratch.numel(), _stream()), "gemm_smallm")
-
-
 class _RowsOpC(ctypes.Structure):
     """csrc/gemm_rows.h: AtomRowsOp."""
     _fields_ = [("X", _vp), ("lda", _i64), ("W", _vp), ("out", _vp), ("out_dtype", _i), ("ldc", _i64),
@@ -407,7 +365,7 @@ class _RowsOpC(ctypes.Structure):
                 ("residual", _vp), ("norm_w", _vp), ("norm_w_dtype", _i), ("xout", _vp), ("ssq_out", _vp)]
 
 
-ROWS_M = 8      # rows up to which the row-sharing product is used (it takes 16)
+ROWS_M = 8      # rows up to which the weight-streaming product beats the library's (measured; it takes 16)
 
 
 def gemm_rows_grid() -> int:

@@ -1065,6 +1065,18 @@ ATOM_EXPORT int atom_flash_has_tc() {
 // Head size this library was compiled for.
 ATOM_EXPORT int atom_flash_head_dim() { return atom::flash::HD; }
 
+namespace atom {
+namespace flash {
+// A kernel's shared-memory attribute belongs to a device: one flag per (device, kind of kernel).
+static bool& attr_done(int kind) {
+  static bool done[64][4] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  return done[dev][kind];
+}
+}  // namespace flash
+}  // namespace atom
+
 // Bytes of scratch that `num_splits` splits need for T tokens.
 ATOM_EXPORT int64_t atom_flash_scratch_bytes(int T, int nh, int num_splits) {
   return num_splits <= 1 ? 0 : (int64_t)T * nh * num_splits * (atom::flash::HD + 2) * (int64_t)sizeof(float);
@@ -1119,7 +1131,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   p.part_o = (float*)scratch;
   p.part_ml = p.part_o ? p.part_o + (int64_t)T * nh * num_splits * HD : nullptr;
 
-  static bool attr_set = false;
+  bool& attr_set = attr_done(0);
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)prefill_smem_bytes()) != cudaSuccess ||
@@ -1149,7 +1161,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
                 atom::tma::make_map_raw(&maps.q, q, 3, d3, s3, b3);
     }
     if (use_tma) {
-      static bool tc2_attr = false;
+      bool& tc2_attr = attr_done(1);
       if (!tc2_attr) {
         if (cudaFuncSetAttribute(tc2::flash_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)tc2::smem_bytes2()) != cudaSuccess)
@@ -1160,7 +1172,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
       atom::launch_pdl(tc2::flash_prefill_tc2_kernel, dim3(nkv, long_tiles), dim3(tc2::NTHREADS2), tc2::smem_bytes2(),
                        stream, p, long_rows, maps);
     } else {
-      static bool tc_attr = false;
+      bool& tc_attr = attr_done(2);
       if (!tc_attr) {
         if (cudaFuncSetAttribute(tc::flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)tc::smem_bytes()) != cudaSuccess)
@@ -1199,7 +1211,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
       CUtensorMap kmap, vmap;
       if (atom::tma::cached_map(&kmap, k_pages, page_rows, HD, HD, box_rows, HD / 64) &&
           atom::tma::cached_map(&vmap, v_pages, page_rows, HD, HD, box_rows, HD / 64)) {
-        static bool tma_attr = false;
+        bool& tma_attr = attr_done(3);
         if (!tma_attr) {
           if (cudaFuncSetAttribute(flash_decode_tma_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)decode_tma_smem_bytes(16)) != cudaSuccess)

@@ -38,7 +38,37 @@
 extern "C" {
 #endif
 
-// Same arguments and meaning as atom_flash_attention, without the scratch pointer.
+// Causal attention of T query tokens (of num_seqs requests, a request's tokens in a row) over the keys
+// and values of their own requests in a paged cache, bf16 in and out, sums in 32-bit.  Only the
+// cp.async / mma.sync kernels run on this path (no TMA, no tensor memory), for any page size.
+//
+//   out            [T, nh * hd] bf16.  A row that no launched tile covers is NOT written: see prefill_tiles.
+//   q, q_stride    queries: token t's head h at q + t * q_stride + h * hd (bf16 elements; q_stride a
+//                  multiple of 8).  The queries may be the first columns of a wider [q | k | v] array.
+//   k_pages, v_pages   [pages, nkv, page_size, hd] bf16 each.
+//   block_table    [num_seqs, max_pages] int32: the page of request s that holds its tokens
+//                  [i * page_size, (i + 1) * page_size).
+//   cu_q           [num_seqs + 1] int32: request s owns the query tokens cu_q[s] .. cu_q[s + 1] - 1.
+//   ctx_len        [num_seqs] int32: tokens of request s in the cache, its query tokens of this call
+//                  included (they are its last ones; their keys must be in the pages already).
+//   seq_of_token   [T] int32: the request of every query token (-1: a padding row, skipped).
+//   nh, nkv, hd    query heads, key/value heads (nh a multiple of nkv), head size.  hd must be the one
+//                  this library was compiled for (atom_flash_head_dim()).
+//   scale          multiplies the scores before the softmax (> 0; usually hd^-0.5).
+//   window         > 0: a token sees only the last `window` keys up to itself; 0: all of them.
+//   A request's "packed rows" are its query tokens times nh / nkv (the query heads that share a kv head are
+//   rows of one tile).  The caller says which kernels are needed:
+//   prefill_tiles  the sum, over the requests with MORE than 16 packed rows, of ceil(packed rows / 64)
+//                  (requests of 128 rows and more too: the tensor-memory kernel is off on this path);
+//                  0 if there is none.  A count that is too small leaves rows of `out` unwritten; one that
+//                  is too large costs CTAs that leave at once.
+//   has_short      1 if some request has at most 16 packed rows (decoded tokens), else 0.
+//   num_splits     >= 1: the key ranges of the short requests are cut into this many pieces that run as
+//                  CTAs of their own and are merged afterwards; with 1 nothing is merged and no scratch
+//                  is used.  At most 65535, and within the scratch limit above.
+//   stream         the CUDA stream of every launch.
+// Returns 0, or ATOM_ERR_ARG (1) for sizes the kernels do not take, ATOM_ERR_SCRATCH, ATOM_ERR_SETUP, or
+// the launch error code of common.cuh.
 int atom_flash_attention_static(void* out, const void* q, int64_t q_stride, const void* k_pages,
                                 const void* v_pages, const int* block_table, int max_pages,
                                 int page_size, const int* cu_q, const int* ctx_len,

@@ -100,11 +100,9 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 #define ATOM_OPT_PDL 0            // 1 (default): programmatic dependent launch; 0: plain launches
 #define ATOM_OPT_DECODE_TMA 1     // 1 (default): decode attention through TMA where it applies; 0: cp.async kernel
 #define ATOM_OPT_DECODE_KTW 2     // 0 (default): warp tile of the TMA decode kernel by occupancy; 16 or 32: forced
-#define ATOM_OPT_GEMM_ROW_TILE 3  // 0 (default): row tile of the streaming product by shape; 1, 2, 4: forced
-#define ATOM_OPT_GEMM_CUT 4       // -1 (default): ranges cut inside slabs where a CTA streams much; 0 never; 1 always
-#define ATOM_OPT_COUNT 5
+#define ATOM_OPT_COUNT 3
 struct Options {
-  int v[ATOM_OPT_COUNT] = {1, 1, 0, 0, -1};
+  int v[ATOM_OPT_COUNT] = {1, 1, 0};
 };
 inline Options& options() {
   static Options o;

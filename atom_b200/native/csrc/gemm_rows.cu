@@ -33,12 +33,26 @@
 //     bias or activation; the parts are added in their order, so the factor does not depend on timing.
 // Every wait is bounded; one that runs out raises the device error flag and the kernel finishes.
 #include "gemm_rows.h"
-#include "gemm_smallm.cuh"
+
+#include "common.cuh"
+#include "tma.cuh"
 
 namespace atom {
 namespace rows {
 
-using namespace atom::smallm;
+using namespace atom::tma;
+
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 
 constexpr int KG = 8, TG = 2, NCW = KG * TG;      // consumer warps: k groups times tile groups
 constexpr int CTHREADS = (NCW + 3) * 32;          // consumers, W producer, X producer, the rows' factors

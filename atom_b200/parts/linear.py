@@ -1,11 +1,9 @@
 """Matrix product y = x W^T (+ b) with weights [out, in], as atom/model_ops/linear.py:946-965.
 
 bfloat16: for many rows the GEMM library, as the reference does (tgemm.mm, linear.py:960); for
-few rows (decode) the framework's weight-streaming kernels: the one that shares out rows of W
-among the CTAs (``native.gemm_rows``, up to ``native.ROWS_M`` rows, K a multiple of 64), else
-the one that shares out slabs and k ranges (``native.gemm_smallm``, up to ``native.SMALL_M``
-rows).  All accumulate in 32-bit.  float32: the framework's own FMA kernel, never a
-reduced-precision mode.
+few rows (decode: up to ``native.ROWS_M``, K a multiple of 64) the framework's weight-streaming
+kernel, which shares out rows of W among the CTAs (``native.gemm_rows``).  Both accumulate in
+32-bit.  float32: the framework's own FMA kernel, never a reduced-precision mode.
 """
 from __future__ import annotations
 
@@ -77,9 +75,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     elif x.shape[0] <= native.ROWS_M and native.gemm_rows_supports(
             x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
         native.gemm_rows(x, weight, out, bias)            # few rows: the product is a read of W
-    elif x.shape[0] <= native.SMALL_M and native.gemm_smallm_supports(
-            x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
-        native.gemm_smallm(out, x, weight, bias)
     else:
         native.gemm_bf16(out, x, weight)
         if bias is not None:
@@ -98,10 +93,6 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scrat
         return out
     if x.dtype == torch.bfloat16 and M <= native.ROWS_M and native.gemm_rows_supports(M, I, K, x.stride(0)):
         native.gemm_rows(x, weight, out, gated=True)
-        return out
-    if (x.dtype == torch.bfloat16 and M <= native.SMALL_M
-            and native.gemm_smallm_supports(M, I, K, x.stride(0))):
-        native.gemm_smallm(out, x, weight, None, gated=True)
         return out
     gu = linear(x, weight, None, scratch(M, 2 * I))
     native.silu_mul(out, gu)

@@ -1,5 +1,5 @@
-"""The plain implementation against outputs of the reference's own code (the two functions of
-its model code that run on a CPU; made by tests/golden/make_golden.py)."""
+"""The plain implementation against outputs of the reference's own code (the functions of its
+model code that run on a CPU; made by tests/golden/make_golden.py)."""
 import json
 import os
 
@@ -21,4 +21,10 @@ def test_rope_matches_reference_function():
 def test_silu_and_mul_matches_reference_function():
     g = json.load(open(GOLDEN))["silu_and_mul"]
     got = plain.silu_and_mul(torch.tensor(g["x"], dtype=torch.float32))
+    assert torch.allclose(got, torch.tensor(g["out"]), rtol=1e-6, atol=1e-6)
+
+
+def test_rms_norm_matches_reference_function():
+    g = json.load(open(GOLDEN))["rms_norm"]
+    got = plain.rms_norm(torch.tensor(g["x"], dtype=torch.float32), torch.tensor(g["weight"]), g["eps"])
     assert torch.allclose(got, torch.tensor(g["out"]), rtol=1e-6, atol=1e-6)

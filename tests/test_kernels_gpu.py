@@ -497,83 +497,7 @@ def test_sampler_greedy_and_distribution():
     assert a == b[::-1]
 
 
-# ----------------------------------------------------------------------------- few-row matrix product
-
-
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K", [(1, 389, 64), (3, 130, 320), (8, 4096, 4096), (9, 1000, 576), (16, 77, 1024),
-                                   (7, 301, 192), (4, 200, 448), (13, 640, 2112), (2, 2500, 512), (5, 151, 12288)])
-def test_gemm_smallm(native, out_dtype, M, N, K):
-    a, w = _rand((M, K), torch.bfloat16, 30), _rand((N, K), torch.bfloat16, 31)
-    bias = _rand((N,), torch.bfloat16, 32) if N % 2 else None
-    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    assert native.gemm_smallm_supports(M, N, K, K)
-    native.gemm_smallm(out, a, w, bias)
-    native.check_error_flags()
-    want = a.float() @ w.float().T + (bias.float() if bias is not None else 0)
-    torch.testing.assert_close(out.float(), want.to(out_dtype).float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
-
-
-@pytest.mark.parametrize("M,I,K", [(1, 160, 128), (7, 1001, 320), (8, 12288, 4096), (12, 112, 64), (16, 333, 1024)])
-def test_gemm_smallm_gated(native, M, I, K):
-    a, w = _rand((M, K), torch.bfloat16, 33), _rand((2 * I, K), torch.bfloat16, 34, 0.3)
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    native.gemm_smallm(out, a, w, None, gated=True)
-    native.check_error_flags()
-    gu = a.float() @ w.float().T
-    g, u = gu[:, :I], gu[:, I:]
-    want = g * torch.sigmoid(g) * u
-    torch.testing.assert_close(out.float(), want.bfloat16().float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
-
-
-def test_gemm_smallm_rows_do_not_depend_on_the_batch(native):
-    """A row's result does not depend on the rows beside it: bit-equal within one tile shape
-    (up to 8 rows), and equal up to the order of 32-bit sums across tile shapes."""
-    N, K = 520, 1088
-    a, w = _rand((16, K), torch.bfloat16, 35), _rand((N, K), torch.bfloat16, 36)
-    outs = {}
-    for m in (1, 5, 8, 9, 16):
-        outs[m] = torch.empty((m, N), dtype=torch.float32, device=DEV)
-        native.gemm_smallm(outs[m], a[:m], w)
-    assert torch.equal(outs[1], outs[8][:1]) and torch.equal(outs[5], outs[8][:5])
-    assert torch.equal(outs[9], outs[16][:9])
-    torch.testing.assert_close(outs[8], outs[16][:8], rtol=1e-5, atol=1e-4)
-
-
-@pytest.mark.parametrize("M,N,K,gated", [(8, 4096, 12288, False), (3, 6144, 4096, False), (8, 2048, 1024, True),
-                                         (5, 48, 8192, False), (8, 1000, 320, False)])
-def test_gemm_smallm_shared_slabs_repeat_bit_equal(native, M, N, K, gated):
-    """CTAs' ranges of work are cut inside slabs of W rows; the partial sums of a shared slab are added
-    in the order of the ranges by whoever arrives last.  The result is the same bits every time, also
-    with other products in between (the arrival counters are left clean), and it is right."""
-    a = _rand((M, K), torch.bfloat16, 40)
-    w = _rand((2 * N if gated else N, K), torch.bfloat16, 41)
-    other_a, other_w = _rand((2, 704), torch.bfloat16, 42), _rand((333, 704), torch.bfloat16, 43)
-    other = torch.empty((2, 333), dtype=torch.float32, device=DEV)
-    outs = []
-    for i in range(6):
-        out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
-        native.gemm_smallm(out, a, w, None, gated=gated)
-        native.gemm_smallm(other, other_a, other_w)
-        outs.append(out)
-    native.check_error_flags()
-    assert all(torch.equal(outs[0], o) for o in outs[1:])
-    if gated:
-        g, u = a.float() @ w[:N].float().T, a.float() @ w[N:].float().T
-        want = torch.nn.functional.silu(g) * u
-    else:
-        want = a.float() @ w.float().T
-    torch.testing.assert_close(outs[0], want, rtol=2e-3, atol=2e-3 * math.sqrt(K / 96))
-    torch.testing.assert_close(other, other_a.float() @ other_w.float().T, rtol=2e-3, atol=5e-3)
-
-
-def test_gemm_smallm_refuses_other_sizes(native):
-    assert not native.gemm_smallm_supports(17, 64, 64, 64)
-    assert not native.gemm_smallm_supports(4, 64, 96, 96)      # K no multiple of 64
-    assert not native.gemm_smallm_supports(4, 64, 64, 100)     # leading dimension no multiple of 8
-
-
-# ----------------------------------------------------------------------------- few-row product that shares out rows of W
+# ----------------------------------------------------------------------------- few-row matrix product (rows of W shared out)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -676,12 +600,10 @@ def test_gemm_rows_refuses_other_sizes(native):
 # ----------------------------------------------------------------------------- both sides of every launch choice
 
 
-@pytest.mark.parametrize("name,value", [("pdl", 0), ("decode_tma", 0), ("decode_ktw", 16), ("decode_ktw", 32),
-                                        ("gemm_row_tile", 1), ("gemm_row_tile", 2), ("gemm_row_tile", 4),
-                                        ("gemm_cut", 0), ("gemm_cut", 1)])
+@pytest.mark.parametrize("name,value", [("pdl", 0), ("decode_tma", 0), ("decode_ktw", 16), ("decode_ktw", 32)])
 def test_forced_launch_choices_give_the_same_results(native, name, value):
     """The launch code chooses between kernels and tilings by itself (dependent launch, the TMA decode kernel
-    and its warp tile, the streaming product's row tile, ranges cut inside slabs); ``set_option`` forces a
+    and its warp tile); ``set_option`` forces a
     side.  Each forced side is checked against the dense references, so no path runs only at sizes the
     default happens to send there."""
     try:
@@ -694,15 +616,13 @@ def test_forced_launch_choices_give_the_same_results(native, name, value):
         got = _run_attention(native, "flash", q, kp, vp, bt, q_lens, ctx_lens, nh, nkv, hd, hd ** -0.5, 0,
                              force_splits=3)
         assert (got - want).abs().max().item() <= 2e-2
-        # the streaming product: plain with bias, and gated; sizes with whole and with shared slabs
+        # the streaming product under the same launch mode: plain with bias, and gated
         for M, N, K, gated in ((8, 4096, 12288, False), (3, 1000, 576, False), (5, 2048, 1024, True)):
-            if name == "gemm_row_tile" and gated and value % 2:
-                continue                     # (a gated slab holds gate and up rows: an even row tile)
             a = _rand((M, K), torch.bfloat16, 92)
             w = _rand(((2 if gated else 1) * N, K), torch.bfloat16, 93, 0.3)
             bias = None if gated else _rand((N,), torch.bfloat16, 94)
             out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
-            native.gemm_smallm(out, a, w, bias, gated=gated)
+            native.gemm_rows(a, w, out, bias, gated=gated)
             acc = a.double() @ w.double().T
             ref = torch.nn.functional.silu(acc[:, :N]) * acc[:, N:] if gated else acc + bias.double()
             torch.testing.assert_close(out.double(), ref, rtol=1e-2, atol=2e-2 * math.sqrt(K / 96))

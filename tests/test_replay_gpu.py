@@ -110,11 +110,10 @@ def test_request_freed_and_fed_again_matches_plain(model_dirs, runners, name, dt
 
 @pytest.mark.parametrize("name", ["A", "D"])
 @pytest.mark.parametrize("side", ["norms folded into the products", "norms as kernels of their own",
-                                  "slabs of W shared out", "the library's product"])
+                                  "the library's product"])
 def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
-    """Steps of few rows choose between products by themselves: the kernel that shares out rows of W with
-    the norms folded into its epilogues, the same with the norm kernels, the kernel that shares out slabs,
-    the library.  Each side, forced, gives the plain implementation's logits when the last 32 tokens are
+    """Steps of few rows choose between products by themselves: the weight-streaming kernel with the norms
+    folded into its epilogues, the same with the norm kernels, the library.  Each side, forced, gives the plain implementation's logits when the last 32 tokens are
     decoded one by one and when portions are mixed with decoded tokens (A and D have widths that every
     side takes); with the norms folded, fewer kernels are launched."""
     from atom_b200 import native
@@ -122,13 +121,11 @@ def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
 
     seqs = _seqs(name)
     ref = plain_logits(model_dirs[name], seqs)
-    saved = (linear.FOLD_NORMS, native.ROWS_M, native.SMALL_M)
+    saved = (linear.FOLD_NORMS, native.ROWS_M)
     try:
         linear.FOLD_NORMS = side == "norms folded into the products"
-        if side in ("slabs of W shared out", "the library's product"):
-            native.ROWS_M = 0
         if side == "the library's product":
-            native.SMALL_M = 0
+            native.ROWS_M = 0
         runner = make_runner(model_dirs[name], "bfloat16", 512, PAGE[name])
         before = native.launches
         for steps in (traces.tail_by_token(seqs, 32), traces.mixed(seqs, max_live=4, budget_tokens=512)[0]):
@@ -143,7 +140,7 @@ def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
         _launches[(name, side)] = native.launches - before
         assert all(g.pool.num_used == 0 for g in runner.cache.groups)
     finally:
-        linear.FOLD_NORMS, native.ROWS_M, native.SMALL_M = saved
+        linear.FOLD_NORMS, native.ROWS_M = saved
     a, b = _launches.get((name, "norms folded into the products")), _launches.get((name, "norms as kernels of their own"))
     if a is not None and b is not None:
         assert a < b, "folding the norms saved no launch"
