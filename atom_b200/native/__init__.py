@@ -431,7 +431,10 @@ def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
 _flash_libs = {}
 _FLASH_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _i,
               _i, _vp, _vp]
+_FLASH_ROT_SIG = [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp,
+                  _vp, _vp, _i, _i, _vp, _vp, _i, _f, _i, _vp, _vp]
 LONG_ROWS = 128    # packed rows from which a request runs on the tcgen05 attention kernel
+ROTATE_IN_DECODE = True    # decode steps leave q/k norm, rotation and cache write to the attention kernel where it takes them
 
 
 def flash_supports(hd: int, dtype: torch.dtype) -> bool:
@@ -452,6 +455,10 @@ def flash_lib(hd: int):
                 l.atom_flash_attention.restype = ctypes.c_int
                 l.atom_flash_scratch_bytes.argtypes = [_i, _i, _i]
                 l.atom_flash_scratch_bytes.restype = ctypes.c_int64
+                l.atom_flash_attention_rotating.argtypes = _FLASH_ROT_SIG
+                l.atom_flash_attention_rotating.restype = ctypes.c_int
+                l.atom_flash_rotating_supports.argtypes = [_i, _i64, _i, _i, _i]
+                l.atom_flash_rotating_supports.restype = ctypes.c_int
                 l.atom_flash_take_error.restype = ctypes.c_int
                 l.atom_flash_has_tc.restype = ctypes.c_int
                 if l.atom_flash_head_dim() != hd:
@@ -559,6 +566,50 @@ def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: 
         block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
         seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(long_tiles),
         LONG_ROWS, int(tiles), int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")
+
+
+def flash_rotating_supports(hd: int, page_size: int, num_pages: int, nh: int, nkv: int, rotary_dim: int) -> bool:
+    """A decode step of these sizes can leave the heads' norm, the rotation and the cache write of its new
+    tokens to the decode attention kernel (``flash_attention_rotating``)."""
+    return ROTATE_IN_DECODE and flash_supports(hd, torch.bfloat16) and bool(
+        flash_lib(hd).atom_flash_rotating_supports(page_size, num_pages, nh, nkv, rotary_dim))
+
+
+def flash_attention_rotating(out: torch.Tensor, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                             block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
+                             seq_of_token: torch.Tensor, T: int, num_seqs: int, nh: int, nkv: int, hd: int,
+                             scale: float, window: int, splits: int, scratch: Optional[torch.Tensor],
+                             table: torch.Tensor, rotary_dim: int, rows: torch.Tensor,
+                             q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                             write_cache: bool, status: torch.Tensor) -> None:
+    """Decode attention of a step in which every request brings one token, over the raw projection
+    qkv[T, (nh + 2 nkv) * hd]: the kernel normalises each query and key head (weights or None), rotates it
+    by row rows[t] of ``table`` [positions, rotary_dim] (cos, then sin), stores the new key and value in the
+    token's page (``write_cache``; a token without a page sets ``status``) and attends.  out[T, nh*hd]."""
+    _cuda(out, qkv, k_pages, v_pages, block_table, cu_q, ctx_len, seq_of_token, scratch, table, rows, q_weight,
+          k_weight, status)
+    page_size = k_pages.shape[2]
+    assert out.dtype == qkv.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16 and T == num_seqs
+    assert out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous() and qkv.stride(1) == 1
+    assert qkv.shape[1] == (nh + 2 * nkv) * hd
+    assert tuple(k_pages.shape[1:]) == (nkv, page_size, hd) and v_pages.shape == k_pages.shape
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous()
+    assert cu_q.dtype == ctx_len.dtype == seq_of_token.dtype == rows.dtype == status.dtype == torch.int32
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] == rotary_dim
+    w = q_weight if q_weight is not None else k_weight
+    if w is not None:
+        assert all(x is None or (x.dtype == w.dtype and x.numel() == hd and x.is_contiguous()) for x in (q_weight, k_weight))
+    if splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32
+        assert scratch.numel() >= flash_scratch_elems(T, nh, hd, splits)
+    l = flash_lib(hd)
+    _check(l.atom_flash_attention_rotating(
+        out.data_ptr(), qkv.data_ptr(), qkv.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+        block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
+        seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(splits), _ptr(scratch),
+        table.data_ptr(), rows.data_ptr(), int(rotary_dim), table.shape[0], _ptr(q_weight), _ptr(k_weight),
+        dtype_code(w.dtype) if w is not None else F32, float(eps), int(write_cache), status.data_ptr(), _stream()),
+        "flash_attention_rotating")
 
 
 def flash_scratch_elems(T: int, nh: int, hd: int, splits: int) -> int:

@@ -63,6 +63,19 @@ struct Params {
   float* part_ml;              // [T, nh, num_splits, 2]
   int* error;                  // device flag raised when a bounded wait ran out
   int long_rows;               // requests with at least this many packed rows go to the tcgen05 kernel
+  // A decode step (one new token per request) may leave the per-head norm, the rotation and the cache write
+  // of its new tokens to the TMA decode kernel: q then points at the raw projection [q | k | v] of a token.
+  const float* rot_table;      // [max_pos, rotary_dim] cos of every pair's angle, then sin; null: q and the cache are ready
+  const int* rot_rows;         // [T] table row of every token
+  int rotary_dim, rot_max_pos;
+  const void* q_norm_w;        // [HD] or null
+  const void* k_norm_w;
+  int norm_w_dtype;
+  float norm_eps;
+  __nv_bfloat16* k_write;      // the pages again, to be written (null: this call writes no cache)
+  __nv_bfloat16* v_write;
+  int64_t num_pages;
+  int* status;                 // set when a new token has no page
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -752,6 +765,67 @@ __device__ __forceinline__ void warp_tile_t(AccT<NQ>& acc, const uint32_t (*qf)[
   }
 }
 
+// One head row of a new token, normalised over the head (if a weight is given) and rotated over its first
+// rotary_dim elements in the half-split pairing (j, j + rotary_dim / 2), by one warp: lane l holds the
+// EPL = HD / 32 consecutive elements from l * EPL, so an element's partner lies in the same slot of the lane
+// rotary_dim / 2 / EPL further on (rotary_dim a multiple of 2 EPL).  32-bit throughout, rounded once.
+// What does not depend on the kernels before this one (the token's angles, the norm weights) is read first.
+constexpr int EPL = HD / 32 > 0 ? HD / 32 : 1;
+struct Rotation {
+  float c[EPL], s[EPL];      // cos and sin of this lane's elements' pairs (1, 0 beyond the rotary part)
+  int src;                   // the lane that holds the partners
+  bool first, second;        // this lane's elements are the first / the second of their pairs
+  __device__ __forceinline__ void init(const float* table_row, int rotary_dim) {
+    const int lane = threadIdx.x & 31;
+    const int half = rotary_dim >> 1, D = half / EPL;
+    first = lane < D;
+    second = !first && lane < 2 * D;
+    src = first ? lane + D : (second ? lane - D : lane);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      c[e] = 1.f;
+      s[e] = 0.f;
+      if (first || second) {
+        const int j = (first ? lane : lane - D) * EPL + e;
+        c[e] = table_row[j];
+        s[e] = table_row[half + j];
+      }
+    }
+  }
+};
+__device__ __forceinline__ void load_norm_weight(const void* nw, int w_dtype, float (&w)[EPL]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) w[e] = nw != nullptr ? atom::load_as_float(nw, w_dtype, lane * EPL + e) : 1.f;
+}
+__device__ __forceinline__ void load_row(const __nv_bfloat16* x, __nv_bfloat16 (&raw)[EPL]) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) raw[e] = x[lane * EPL + e];
+}
+__device__ __forceinline__ void rotated_row(const __nv_bfloat16 (&raw)[EPL], bool normed, const float (&w)[EPL], float eps,
+                                            const Rotation& r, float (&out)[EPL]) {
+  float v[EPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    v[e] = __bfloat162float(raw[e]);
+    ss += v[e] * v[e];
+  }
+  if (normed) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = v[e] * rstd * w[e];
+  }
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const float other = __shfl_sync(0xffffffffu, v[e], r.src);
+    out[e] = r.first ? v[e] * r.c[e] - other * r.s[e] : (r.second ? v[e] * r.c[e] + other * r.s[e] : v[e]);
+  }
+}
+
 // The work of one warp of a short-request CTA over KTW-key tiles [tile_begin, tile_end) of the
 // request.  ring / full: this warp's stages and their barriers.
 template <int NQ, int KTW>
@@ -795,6 +869,22 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
   // once: the kernel before this one (which may still be running) writes the step's new keys and
   // nothing else of the cache, and the step's arrays were filled before it began.  The others, and Q,
   // follow once that kernel has completed.
+  // Where this kernel rotates the step's new tokens itself: the token's angles and the norm weights, and
+  // which warp will meet the new token's tile, before the wait for the kernels in front of it.
+  const bool rotating = p.rot_table != nullptr;
+  Rotation rot;
+  float qw[EPL], kw[EPL];
+  bool will_patch = false;
+  __nv_bfloat16 new_k[EPL], new_v[EPL];    // the new token's key (normalised, rotated) and value, held by the warp that will meet their tile
+  if (rotating) {
+    const int row_of = min(p.rot_rows[w.q_begin], p.rot_max_pos - 1);
+    rot.init(p.rot_table + (int64_t)row_of * p.rotary_dim, p.rotary_dim);
+    load_norm_weight(p.q_norm_w, p.norm_w_dtype, qw);
+    const int t_new = (w.ctx - 1) / KTW;
+    will_patch = p.k_write != nullptr && w.ctx >= 1 && t_new >= tile_begin && t_new < tile_end &&
+                 ((t_new - tile_begin) & 3) == warp;
+    if (will_patch) load_norm_weight(p.k_norm_w, p.norm_w_dtype, kw);
+  }
   int row_next;
   {
     int rows[RING + 1];
@@ -804,7 +894,8 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
 #pragma unroll
     for (int i = 0; i < RING; ++i) {
       const int t = tile_begin + warp + 4 * i;
-      early[i] = t < tile_end && (t + 1) * KTW <= w.q_start;
+      // (where this kernel writes the new token's key and value itself, no kernel of the step writes the cache)
+      early[i] = t < tile_end && ((t + 1) * KTW <= w.q_start || p.k_write != nullptr);
       if (early[i]) issue(i, rows[i]);
     }
     atom::pdl_wait();      // inputs written by the kernels before this one are visible from here on
@@ -814,9 +905,39 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
     row_next = rows[RING];
   }
   if (tile_begin < tile_end) {
-    load_q_tile<16>(p, w, sQ);
-    cp_async_commit();
-    cp_async_wait<0>();
+    if (rotating) {
+      // the raw projection's query rows of this kv head, normalised and rotated on their way into sQ; what
+      // the warp needs from the projection (its query rows, the new key and value) is asked for at once
+      const __nv_bfloat16* raw = p.q + (int64_t)w.q_begin * p.q_stride;
+      __nv_bfloat16 xq[4][EPL];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (warp + 4 * i < w.rows_total) load_row(raw + (int64_t)(w.kvh * p.group + warp + 4 * i) * HD, xq[i]);
+      if (will_patch) {
+        load_row(raw + (int64_t)(p.nh + w.kvh) * HD, new_k);
+        load_row(raw + (int64_t)(p.nh + p.nkv + w.kvh) * HD, new_v);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int R = warp + 4 * i;
+        float qv[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) qv[e] = 0.f;
+        if (R < w.rows_total) rotated_row(xq[i], p.q_norm_w != nullptr, qw, p.norm_eps, rot, qv);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) sQ[R * LDS + lane * EPL + e] = __float2bfloat16_rn(qv[e]);
+      }
+      if (will_patch) {
+        float kv[EPL];
+        rotated_row(new_k, p.k_norm_w != nullptr, kw, p.norm_eps, rot, kv);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) new_k[e] = __float2bfloat16_rn(kv[e]);
+      }
+    } else {
+      load_q_tile<16>(p, w, sQ);
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
   }
   __syncthreads();
 
@@ -848,8 +969,31 @@ __device__ __forceinline__ void decode_tma_body(const Params& p, const Work& w, 
     const int refill = t + 4 * RING;
     const int row_after = box_row(refill + 4);   // in flight during the tile's arithmetic
     atom::tma::mbar_wait(&full[st], phase, aborted, p.error);
-    const unsigned char* sK = ring + st * TMA_STAGE_BYTES;
+    unsigned char* sK = ring + st * TMA_STAGE_BYTES;
     const int key0 = t * KTW;
+    if (will_patch && w.ctx - 1 >= key0 && w.ctx - 1 < key0 + KTW) {
+      // The tile of the request's new token: its key and value replace what the page held at that place
+      // in this stage, and go to the page.
+      const int newpos = w.ctx - 1, kr = newpos - key0;
+      const int page = w.bt[newpos >> p.page_shift];
+      const bool has_page = page >= 0 && page < p.num_pages;
+      if (!has_page && lane == 0) atomicExch(p.status, 1);     // a position without a page: recorded, not written
+      const int64_t at = (((int64_t)(has_page ? page : 0) * p.nkv + w.kvh) * p.page_size + (newpos & (p.page_size - 1))) * HD;
+      const int half_stride = 128 << box_shift;
+      const int rbase = (((kr >> box_shift) * HD) << (box_shift + 1)) + (kr & ((1 << box_shift) - 1)) * 128;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const int d = lane * EPL + e;
+        const int off = rbase + (d >> 6) * half_stride + ((((d & 63) >> 3) ^ (kr & 7)) << 4) + (d & 7) * 2;
+        *reinterpret_cast<__nv_bfloat16*>(sK + off) = new_k[e];
+        *reinterpret_cast<__nv_bfloat16*>(sK + KTW * HD * 2 + off) = new_v[e];
+        if (has_page) {
+          p.k_write[at + d] = new_k[e];
+          p.v_write[at + d] = new_v[e];
+        }
+      }
+      __syncwarp();
+    }
     bool mask = key0 + KTW - 1 > w.q_start;
     if (p.window > 0) mask = mask || (key0 <= w.ctx - 1 - p.window);
     warp_tile_t<NQ, KTW>(acc, qf, sQ, sK, sK + KTW * HD * 2, key0, pos, p.window, p.scale_log2, mask, box_shift);
@@ -1082,19 +1226,51 @@ ATOM_EXPORT int64_t atom_flash_scratch_bytes(int T, int nh, int num_splits) {
   return num_splits <= 1 ? 0 : (int64_t)T * nh * num_splits * (atom::flash::HD + 2) * (int64_t)sizeof(float);
 }
 
-// num_pages: pages of k_pages / v_pages (used to bound the TMA maps; 0: unknown, no TMA loading).
-// long_tiles > 0: requests with at least long_rows packed rows run on the tcgen05 kernel
-// (long_tiles = sum over them of ceil(rows / 128); needs atom_flash_has_tc() and window <= 0).
-// prefill_tiles: sum over the other requests with more than 16 packed rows of ceil(rows / 64); 0: none.
-// has_short: some request has at most 16 packed rows.  scratch: atom_flash_scratch_bytes bytes
-// when num_splits > 1.
-ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride, const void* k_pages,
+// What a decode step hands over when the kernel is to normalise, rotate and store its new tokens itself
+// (atom_flash_attention_rotating): see Params.
+struct AtomFlashRotation {
+  const float* table;
+  const int* rows;
+  int rotary_dim, max_pos;
+  const void* q_norm_w;
+  const void* k_norm_w;
+  int norm_w_dtype;
+  float norm_eps;
+  int write_cache;
+  int* status;
+};
+
+namespace atom {
+namespace flash {
+static bool decode_tma_usable(int page_size, int64_t num_pages, int nkv) {
+#if ATOM_HD % 64 == 0
+  const bool pow2 = page_size >= 8 && (page_size & (page_size - 1)) == 0;
+  return pow2 && atom::options().v[ATOM_OPT_DECODE_TMA] != 0 && num_pages > 0 &&
+         (uint64_t)num_pages * nkv * page_size < 0x7fffffffull && atom::tma::encode_fn() != nullptr;
+#else
+  return false;
+#endif
+}
+}  // namespace flash
+}  // namespace atom
+
+// 1 if a decode step of these sizes can leave norm, rotation and cache write to the decode kernel.
+ATOM_EXPORT int atom_flash_rotating_supports(int page_size, int64_t num_pages, int nh, int nkv, int rotary_dim) {
+#if ATOM_HD % 64 == 0
+  return nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && rotary_dim > 0 && rotary_dim <= atom::flash::HD &&
+         rotary_dim % (2 * atom::flash::EPL) == 0 && atom::flash::decode_tma_usable(page_size, num_pages, nkv);
+#else
+  return 0;
+#endif
+}
+
+static int flash_run(void* out, const void* q, int64_t q_stride, const void* k_pages,
                                      const void* v_pages, int64_t num_pages, const int* block_table, int max_pages,
                                      int page_size, const int* cu_q, const int* ctx_len,
                                      const int* seq_of_token, int T, int num_seqs, int nh, int nkv,
                                      int hd, float scale, int window, int long_tiles, int long_rows,
                                      int prefill_tiles, int has_short, int num_splits, void* scratch,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, const AtomFlashRotation* rot) {
   using namespace atom::flash;
   if (T <= 0 || num_seqs <= 0) return ATOM_OK;
   if (hd != HD || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || num_splits < 1 ||
@@ -1130,6 +1306,36 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
   if (long_tiles > 0 && (!atom_flash_has_tc() || window > 0 || long_rows < 17 || p.error == nullptr)) return ATOM_ERR_ARG;
   p.part_o = (float*)scratch;
   p.part_ml = p.part_o ? p.part_o + (int64_t)T * nh * num_splits * HD : nullptr;
+  p.rot_table = nullptr;
+  p.rot_rows = nullptr;
+  p.rotary_dim = p.rot_max_pos = 0;
+  p.q_norm_w = p.k_norm_w = nullptr;
+  p.norm_w_dtype = ATOM_F32;
+  p.norm_eps = 0.f;
+  p.k_write = p.v_write = nullptr;
+  p.num_pages = num_pages;
+  p.status = nullptr;
+  if (rot != nullptr) {
+    // one new token per request, all of them short, on the TMA decode kernel
+    if (!atom_flash_rotating_supports(page_size, num_pages, nh, nkv, rot->rotary_dim) || T != num_seqs ||
+        long_tiles > 0 || prefill_tiles > 0 || !has_short || rot->table == nullptr || rot->rows == nullptr ||
+        rot->max_pos <= 0 || rot->status == nullptr || p.error == nullptr ||
+        (rot->norm_w_dtype != ATOM_F32 && rot->norm_w_dtype != ATOM_BF16))
+      return ATOM_ERR_ARG;
+    p.rot_table = rot->table;
+    p.rot_rows = rot->rows;
+    p.rotary_dim = rot->rotary_dim;
+    p.rot_max_pos = rot->max_pos;
+    p.q_norm_w = rot->q_norm_w;
+    p.k_norm_w = rot->k_norm_w;
+    p.norm_w_dtype = rot->norm_w_dtype;
+    p.norm_eps = rot->norm_eps;
+    if (rot->write_cache) {
+      p.k_write = (__nv_bfloat16*)const_cast<void*>(k_pages);
+      p.v_write = (__nv_bfloat16*)const_cast<void*>(v_pages);
+    }
+    p.status = rot->status;
+  }
 
   bool& attr_set = attr_done(0);
   if (!attr_set) {
@@ -1232,6 +1438,7 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
       }
     }
 #endif
+    if (!tma_done && rot != nullptr) return ATOM_ERR_LIB;      // (the tensor maps were refused)
     if (!tma_done) atom::launch_pdl(flash_decode_kernel, dim3(grid), dim3(NT), decode_smem_bytes(), stream, p);
     if (num_splits > 1) {
       const int warps = T * nh;
@@ -1239,6 +1446,45 @@ ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride,
     }
   }
   return atom::check_launch();
+}
+
+// num_pages: pages of k_pages / v_pages (used to bound the TMA maps; 0: unknown, no TMA loading).
+// long_tiles > 0: requests with at least long_rows packed rows run on the tcgen05 kernel
+// (long_tiles = sum over them of ceil(rows / 128); needs atom_flash_has_tc() and window <= 0).
+// prefill_tiles: sum over the other requests with more than 16 packed rows of ceil(rows / 64); 0: none.
+// has_short: some request has at most 16 packed rows.  scratch: atom_flash_scratch_bytes bytes
+// when num_splits > 1.
+ATOM_EXPORT int atom_flash_attention(void* out, const void* q, int64_t q_stride, const void* k_pages,
+                                     const void* v_pages, int64_t num_pages, const int* block_table, int max_pages,
+                                     int page_size, const int* cu_q, const int* ctx_len,
+                                     const int* seq_of_token, int T, int num_seqs, int nh, int nkv,
+                                     int hd, float scale, int window, int long_tiles, int long_rows,
+                                     int prefill_tiles, int has_short, int num_splits, void* scratch,
+                                     cudaStream_t stream) {
+  return flash_run(out, q, q_stride, k_pages, v_pages, num_pages, block_table, max_pages, page_size, cu_q, ctx_len,
+                   seq_of_token, T, num_seqs, nh, nkv, hd, scale, window, long_tiles, long_rows, prefill_tiles,
+                   has_short, num_splits, scratch, stream, nullptr);
+}
+
+// A decode step (T == num_seqs: one new token per request; requests of a fixed-size batch without one
+// have ctx_len 0) whose tokens' queries and keys are still raw: q points at the projection's rows
+// [q heads | k heads | v heads] of width hd each.  The decode kernel normalises every query and key head
+// (weights of hd elements, or null), rotates it by the table row rows[t], writes the key and the value to
+// the token's page (write_cache; a token without a page sets *status) and attends over the pages and the
+// new token.  Needs atom_flash_rotating_supports.
+ATOM_EXPORT int atom_flash_attention_rotating(void* out, const void* qkv, int64_t q_stride, void* k_pages,
+                                              void* v_pages, int64_t num_pages, const int* block_table,
+                                              int max_pages, int page_size, const int* cu_q, const int* ctx_len,
+                                              const int* seq_of_token, int T, int num_seqs, int nh, int nkv, int hd,
+                                              float scale, int window, int num_splits, void* scratch,
+                                              const float* table, const int* rows, int rotary_dim, int max_pos,
+                                              const void* q_norm_w, const void* k_norm_w, int norm_w_dtype,
+                                              float norm_eps, int write_cache, int* status, cudaStream_t stream) {
+  AtomFlashRotation rot = {table, rows, rotary_dim, max_pos, q_norm_w, k_norm_w, norm_w_dtype, norm_eps, write_cache,
+                           status};
+  return flash_run(out, qkv, q_stride, k_pages, v_pages, num_pages, block_table, max_pages, page_size, cu_q, ctx_len,
+                   seq_of_token, T, num_seqs, nh, nkv, hd, scale, window, 0, 0, 0, 1, num_splits, scratch, stream,
+                   &rot);
 }
 
 // ------------------------------------------------------------------ allocation-free entry point

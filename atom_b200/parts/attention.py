@@ -80,6 +80,19 @@ class PagedAttention(Mixer):
         kw = self.w_k_norm_weight if self.qk_norm else None
         kp = cache.k_pages if writes_cache else None
         vp = cache.v_pages if writes_cache else None
+        o = ws.get("attn.o", (T, nh * hd), dt)
+        if self._rotates_in_decode(step, cache):
+            # a decode step: norm, rotation and cache write are the attention kernel's own prologue
+            plan = self.launch_plan(step)
+            scratch = None
+            if plan[2] > 1:
+                scratch = ws.get("attn.splits", (native.flash_scratch_elems(T, nh, hd, plan[2]),), torch.float32)
+            native.flash_attention_rotating(
+                o, qkv, cache.k_pages, cache.v_pages, bt, step.cu_q, step.ctx_len, step.seq_of_token, T,
+                step.num_seqs, nh, nkv, hd, self.scale, self.window if self.window else 0, plan[2], scratch,
+                self._table, self.position.rotary_dim, self.position.rows_of(step), qw, kw, self.norm_eps,
+                writes_cache, step.status)
+            return self._project_out(o, T, defer)
         if self._table is not None or type(self.position).apply is PositionEncoding.apply:
             # one kernel: norm, rotation by the table's rows, cache write
             native.qknorm_rope_kvwrite(
@@ -94,12 +107,24 @@ class PagedAttention(Mixer):
             if kp is not None:
                 native.qknorm_rope_kvwrite(qkv, nh, nkv, hd, None, None, 0.0, None, 0, step.positions,
                                            step.seq_of_token, bt, cache.page_size, kp, vp, step.status)
-        o = ws.get("attn.o", (T, nh * hd), dt)
         self.attend(o, qkv, step, cache, bt)
-        out = ws.get("attn.out", (T, self.hidden_size), dt)
+        return self._project_out(o, T, defer)
+
+    def _project_out(self, o, T, defer):
+        out = self.rt.workspace.get("attn.out", (T, self.hidden_size), self.rt.dtype)
         if defer and may_defer(o, self.w_o_weight):
             return PendingProduct(o, self.w_o_weight, None, out)
         return linear(o, self.w_o_weight, None, out)
+
+    def _rotates_in_decode(self, step, cache) -> bool:
+        """Every request of the step brings one token, the position encoding is a table of angles, and
+        the decode attention kernel takes these sizes with norm, rotation and cache write inside."""
+        if step.max_q_len != 1 or step.num_tokens != step.num_seqs or self._table is None or step.plan_for_any_batch:
+            return False
+        if self.rt.dtype != torch.bfloat16 or not native.flash_supports(self.hd, self.rt.dtype):
+            return False
+        return native.flash_rotating_supports(self.hd, cache.page_size, cache.k_pages.shape[0], self.nh, self.nkv,
+                                              self.position.rotary_dim)
 
     def launch_plan(self, step):
         """The attention kernels' plan for this step: tile counts and the number of splits along the

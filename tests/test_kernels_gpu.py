@@ -394,6 +394,104 @@ def test_flash_decode_tma_one_far_key_decides(native, far, splits):
     assert (got - want).abs().max().item() <= 3e-2
 
 
+ROTATING_CASES = [
+    # nh, nkv, hd, rotary_dim, page, window, use_norm, ctx_lens (the new token is each request's last)
+    (32, 8, 128, 128, 16, 0, True, [700, 1, 129, 16, 4097, 33]),
+    (8, 1, 128, 64, 8, 0, False, [50, 300, 9]),
+    (4, 2, 64, 64, 32, 24, True, [77, 120, 31, 2]),
+    (16, 2, 256, 256, 16, 0, True, [97, 35]),
+    (6, 2, 192, 96, 16, 0, True, [260, 17]),
+]
+
+
+@pytest.mark.parametrize("case", ROTATING_CASES, ids=lambda c: f"nh{c[0]}kv{c[1]}hd{c[2]}rd{c[3]}pg{c[4]}w{c[5]}")
+@pytest.mark.parametrize("splits", [1, 3])
+def test_decode_attention_that_rotates_and_stores_its_new_tokens(native, case, splits):
+    """A decode step hands the raw projection [q | k | v] to the attention kernel, which normalises and
+    rotates the heads, stores the new key and value in the token's page and attends over the pages and the new
+    token.  The output is the float64 attention over the dense keys with the rotated new key at the end,
+    the page holds the rotated key and the value, no other place of the cache changes, and the result agrees
+    with the two kernels it replaces.  New tokens at a page's first and last place, a request of one token."""
+    nh, nkv, hd, rd, page, window, use_norm, ctx_lens = case
+    S = len(ctx_lens)
+    q_lens = [1] * S
+    eps, theta, scale = 1e-5, 10000.0, hd ** -0.5
+    _, kp, vp, bt, dense = _paged_case(q_lens, ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=hd + page + splits)
+    assert native.flash_rotating_supports(hd, page, kp.shape[0], nh, nkv, rd)
+    table = _rope_table(max(ctx_lens) + 1, rd, theta)
+    pos = torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32, device=DEV)
+    qkv = _rand((S, (nh + 2 * nkv) * hd), torch.bfloat16, 77)
+    wdt = torch.bfloat16 if hd == 128 else torch.float32                     # (norm weights of either type)
+    qw = (_rand((hd,), torch.float32, 14) * 0.1 + 1).to(wdt) if use_norm else None
+    kw = (_rand((hd,), torch.float32, 15) * 0.1 + 1).to(wdt) if use_norm else None
+    rq, rk, rv = _ref_qknorm_rope(qkv, nh, nkv, hd, qw, kw, eps, table, rd, pos)
+    rq, rk, rv = rq.bfloat16().cpu(), rk.bfloat16().cpu(), rv.bfloat16().cpu()
+    # the reference sees the rotated new key and the value at each request's last position
+    dense_new = []
+    for s, (k, v) in enumerate(dense):
+        k, v = k.clone(), v.clone()
+        k[-1], v[-1] = rk[s], rv[s]
+        dense_new.append((k, v))
+    want = _ref_attention(rq.view(S, nh, hd), dense_new, q_lens, ctx_lens, nh, nkv, scale, window)
+    kpd, vpd, btd = kp.to(DEV), vp.to(DEV), bt.contiguous().to(DEV)
+    kp0, vp0 = kpd.clone(), vpd.clone()
+    cu = torch.arange(S + 1, dtype=torch.int32, device=DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    sot = torch.arange(S, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((S, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty(max(1, native.flash_scratch_elems(S, nh, hd, splits)), dtype=torch.float32, device=DEV)
+    raw = qkv.clone()
+    native.flash_attention_rotating(out, qkv, kpd, vpd, btd, cu, ctx, sot, S, S, nh, nkv, hd, scale, window, splits,
+                                    scratch, table, rd, pos, qw, kw, eps, True, status)
+    native.check_error_flags()
+    assert int(status.item()) == 0 and torch.equal(qkv, raw)          # (the projection is left as it was)
+    got = out.float().cpu().view(S, nh, hd)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() <= 2e-2
+    touched = torch.zeros(kpd.shape[0], page, dtype=torch.bool)
+    for s, c in enumerate(ctx_lens):
+        pg, slot = int(bt[s, (c - 1) // page]), (c - 1) % page
+        touched[pg, slot] = True
+        torch.testing.assert_close(kpd[pg, :, slot].float().cpu(), rk[s].float(), rtol=1.6e-2, atol=1.6e-2)
+        assert torch.equal(vpd[pg, :, slot].cpu(), rv[s])
+    same = ~touched.to(DEV)[:, None, :, None].expand_as(kpd)
+    assert torch.equal(kpd[same], kp0[same]) and torch.equal(vpd[same], vp0[same])
+    # the two kernels it replaces, from the same raw projection and the old cache
+    q2, k2, v2 = raw.clone(), kp0.clone(), vp0.clone()
+    native.qknorm_rope_kvwrite(q2, nh, nkv, hd, qw, kw, eps, table, rd, pos, sot, btd, page, k2, v2, status)
+    plan = (0, True, splits)
+    out2 = torch.empty_like(out)
+    native.flash_attention(out2, q2, q2.shape[1], k2, v2, btd, cu, ctx, sot, S, S, nh, nkv, hd, scale, window, plan,
+                           scratch)
+    assert (out2.float() - out.float()).abs().max().item() <= 1e-2
+    assert (k2.float() - kpd.float()).abs().max().item() <= 1.6e-2 and torch.equal(v2, vpd)
+
+
+def test_decode_attention_that_rotates_reports_a_token_without_a_page(native):
+    """The new token's position has no page in the block table: nothing is stored, the status word is set."""
+    nh, nkv, hd, page = 8, 2, 128, 16
+    ctx_lens = [40, 17]
+    _, kp, vp, bt, _ = _paged_case([1, 1], ctx_lens, nh, nkv, hd, page, torch.bfloat16, seed=5)
+    bt[1, 1] = -1
+    kpd, vpd, btd = kp.to(DEV), vp.to(DEV), bt.contiguous().to(DEV)
+    kp0 = kpd.clone()
+    table = _rope_table(64, hd, 10000.0)
+    qkv = _rand((2, (nh + 2 * nkv) * hd), torch.bfloat16, 78)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty((2, nh * hd), dtype=torch.bfloat16, device=DEV)
+    native.flash_attention_rotating(out, qkv, kpd, vpd, btd, torch.arange(3, dtype=torch.int32, device=DEV),
+                                    torch.tensor(ctx_lens, dtype=torch.int32, device=DEV),
+                                    torch.arange(2, dtype=torch.int32, device=DEV), 2, 2, nh, nkv, hd, hd ** -0.5, 0, 1,
+                                    None, table, hd, torch.tensor([39, 16], dtype=torch.int32, device=DEV), None, None,
+                                    0.0, True, status)
+    native.check_error_flags()
+    assert int(status.item()) == 1
+    pg0 = int(bt[0, 2])
+    changed = (kpd != kp0).flatten(1).any(1).nonzero().flatten().tolist()
+    assert changed == [pg0]
+
+
 @pytest.mark.parametrize("splits", [2, 3, 7])
 def test_flash_decode_splits_agree(native, splits):
     nh, nkv, hd, page = 8, 2, 64, 16

@@ -110,10 +110,11 @@ def test_request_freed_and_fed_again_matches_plain(model_dirs, runners, name, dt
 
 @pytest.mark.parametrize("name", ["A", "D"])
 @pytest.mark.parametrize("side", ["norms folded into the products", "norms as kernels of their own",
-                                  "the library's product"])
+                                  "the library's product", "rotation as a kernel of its own"])
 def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
     """Steps of few rows choose between products by themselves: the weight-streaming kernel with the norms
-    folded into its epilogues, the same with the norm kernels, the library.  Each side, forced, gives the plain implementation's logits when the last 32 tokens are
+    folded into its epilogues, the same with the norm kernels, the library; and decode steps leave the heads'
+    norm, the rotation and the cache write to the attention kernel where it takes them (D), or not.  Each side, forced, gives the plain implementation's logits when the last 32 tokens are
     decoded one by one and when portions are mixed with decoded tokens (A and D have widths that every
     side takes); with the norms folded, fewer kernels are launched."""
     from atom_b200 import native
@@ -121,9 +122,10 @@ def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
 
     seqs = _seqs(name)
     ref = plain_logits(model_dirs[name], seqs)
-    saved = (linear.FOLD_NORMS, native.ROWS_M)
+    saved = (linear.FOLD_NORMS, native.ROWS_M, native.ROTATE_IN_DECODE)
     try:
-        linear.FOLD_NORMS = side == "norms folded into the products"
+        linear.FOLD_NORMS = side in ("norms folded into the products", "rotation as a kernel of its own")
+        native.ROTATE_IN_DECODE = side != "rotation as a kernel of its own"
         if side == "the library's product":
             native.ROWS_M = 0
         runner = make_runner(model_dirs[name], "bfloat16", 512, PAGE[name])
@@ -140,10 +142,13 @@ def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
         _launches[(name, side)] = native.launches - before
         assert all(g.pool.num_used == 0 for g in runner.cache.groups)
     finally:
-        linear.FOLD_NORMS, native.ROWS_M = saved
+        linear.FOLD_NORMS, native.ROWS_M, native.ROTATE_IN_DECODE = saved
     a, b = _launches.get((name, "norms folded into the products")), _launches.get((name, "norms as kernels of their own"))
     if a is not None and b is not None:
         assert a < b, "folding the norms saved no launch"
+    c = _launches.get((name, "rotation as a kernel of its own"))
+    if name == "D" and a is not None and c is not None:
+        assert a < c, "the decode steps of D did not rotate inside the attention kernel"
 
 
 _launches = {}
