@@ -95,6 +95,7 @@ class LLMEngine:
         os.makedirs(self.config.torch_profiler_dir, exist_ok=True)
         self._profiler = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA])
         self._profiler.__enter__()
+        self.runner.profiling = True       # every step becomes a labelled range (runner.step_label)
 
     def stop_profile(self) -> Optional[str]:
         """Stops the profiler and writes ``<model name>_ts_<time>.pt.trace.json.gz``; returns its path."""
@@ -104,6 +105,7 @@ class LLMEngine:
         import shutil
 
         prof, self._profiler = self._profiler, None
+        self.runner.profiling = False
         torch.cuda.synchronize(self.runner.device)
         prof.__exit__(None, None, None)
         name = os.path.basename(self.config.model.rstrip("/")) or "trace"

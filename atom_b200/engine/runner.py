@@ -9,6 +9,8 @@ which takes either prompt portions or decoded tokens, never both.)
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -46,6 +48,49 @@ _MIXED_TOKENS = (16, 32, 48, 64, 80, 96, 128, 160, 192, 224, 256, 320, 384, 448,
 _MIXED_SEQS = (8, 32, 64)
 
 
+def step_label(q_lens: Sequence[int], ctx_lens: Sequence[int], graph_batch: Optional[int] = None,
+               graph_shape=None) -> str:
+    """The name of a step's range in a profiler trace, after the reference's labels
+    (atom/model_engine/run_labels.py:38-110): the kind, then ``key=value`` fields in brackets.
+
+      decode[bs=3/4 tok=3 d=3]            single-token requests replayed from the graph of batch 4
+      mixed[bs=5 tok=77/128 p=2 d=3]      portions beside decoded tokens, replayed from the graph of 128 tokens
+      prefill[bs=2 tok=900 p=2 ctx=[600, 300]]   a step with portions that runs eagerly
+      eager_decode[bs=3 tok=3 d=3 ctx=[41, 7, 100]]
+
+    bs: requests (``/n``: the captured batch it is padded to); tok: tokens of the step; p / d: requests with a
+    portion of several tokens / with one token; ctx: the requests' lengths after the step (the first three and a
+    count when there are more than five)."""
+    bs, tok = len(q_lens), sum(q_lens)
+    p = sum(1 for n in q_lens if n > 1)
+    d = bs - p
+    fields = []
+    if graph_batch:
+        kind = "decode"
+        fields.append(f"bs={bs}/{graph_batch}" if graph_batch > bs else f"bs={bs}")
+        fields.append(f"tok={tok}")
+    elif graph_shape:
+        kind = "mixed"
+        fields.append(f"bs={bs}/{graph_shape[1]}" if graph_shape[1] > bs else f"bs={bs}")
+        fields.append(f"tok={tok}/{graph_shape[0]}" if graph_shape[0] > tok else f"tok={tok}")
+    else:
+        kind = "prefill" if p else "eager_decode"
+        fields += [f"bs={bs}", f"tok={tok}"]
+    if p:
+        fields.append(f"p={p}")
+    if d:
+        fields.append(f"d={d}")
+    if not graph_batch and not graph_shape:
+        ctx = [int(c) for c in ctx_lens]
+        if len(ctx) == 1:
+            fields.append(f"ctx={ctx[0]}")
+        elif len(ctx) <= 5:
+            fields.append(f"ctx={ctx}")
+        else:
+            fields.append(f"ctx={ctx[:3]}...+{len(ctx) - 3}")
+    return f"{kind}[{' '.join(fields)}]"
+
+
 class ModelRunner:
     def __init__(self, engine_config: EngineConfig, model_config: Optional[ModelConfig] = None,
                  device: str = "cuda:0"):
@@ -80,6 +125,7 @@ class ModelRunner:
         self._mixed_tokens = tuple(t for t in _MIXED_TOKENS if t <= limit) or _MIXED_TOKENS[:1]
         self._table_width = max(1, -(-self.max_model_len // self.page_size))
         self.graph_replays = 0
+        self.profiling = False     # set by whoever starts a profiler: steps then carry labels in the trace
         # All graphs share one workspace and one logits buffer: steps run one after another.
         self._graph_ws = Workspace(self.device, keep_outgrown=True)
         self._graph_logits: Optional[torch.Tensor] = None
@@ -242,19 +288,28 @@ class ModelRunner:
                 raise StepError("device_tokens needs a captured decode step and one int32 token per entry")
         targets = self._reserve(entries)
         shape = None if size or device_tokens is not None else self._mixed_shape(entries)
-        if device_tokens is not None:
-            logits = self._step_graph(entries, targets, size, device_tokens, rows)
-        elif size:
-            logits = self._step_graph(entries, targets, size)
-        elif shape:
-            logits = self._step_mixed_graph(entries, targets, shape)
-        else:
-            ctx = self.builder.build(entries, targets)
-            logits = self.model.forward(ctx, self.storage)
+        with self._labelled(entries, targets, size, shape):
+            if device_tokens is not None:
+                logits = self._step_graph(entries, targets, size, device_tokens, rows)
+            elif size:
+                logits = self._step_graph(entries, targets, size)
+            elif shape:
+                logits = self._step_mixed_graph(entries, targets, shape)
+            else:
+                ctx = self.builder.build(entries, targets)
+                logits = self.model.forward(ctx, self.storage)
         for e, t in zip(entries, targets):
             self.cache.commit(e.rid, t)
         self.steps_run += 1
         return logits
+
+    def _labelled(self, entries, targets, size, shape):
+        """While a profiler records (``profiling``), every step is a range of its own in the trace, named by
+        ``step_label``; otherwise nothing."""
+        if not self.profiling:
+            return contextlib.nullcontext()
+        return torch.profiler.record_function(step_label(
+            [len(e.tokens) for e in entries], targets, graph_batch=size or None, graph_shape=shape))
 
     @property
     def h2d_bytes(self) -> int:

@@ -233,8 +233,13 @@ def test_profiler_hook_writes_a_trace(model_dirs, tmp_path):
     path = eng.stop_profile()
     assert path and path.endswith(".pt.trace.json.gz")
     with gzip.open(path) as f:
-        names = [e["name"] for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+        events = json.load(f)["traceEvents"]
+    names = [e["name"] for e in events if e.get("cat") == "kernel"]
     assert any("rmsnorm" in n for n in names) and any("embedding" in n for n in names)
+    # every step is a labelled range: the prompt as a step with a portion, then decode steps
+    labels = [e["name"] for e in events if e.get("cat") in ("user_annotation", "cpu_op") and "[bs=" in e.get("name", "")]
+    assert any(l.startswith("prefill[bs=1 tok=5 p=1 ctx=5]") or l.startswith("mixed[bs=1") for l in labels), labels
+    assert sum(l.startswith(("decode[bs=1", "eager_decode[bs=1")) for l in labels) >= 3, labels
     assert eng.stop_profile() is None            # nothing running any more
 
 

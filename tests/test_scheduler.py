@@ -299,3 +299,15 @@ def test_portions_off_recomputes_a_preempted_request_whole():
         run(s, cache, st)
     e = next(e for e in st.entries if e.seq is b)
     assert (e.start, e.num_tokens) == (0, n)        # what it had, prompt and generated tokens, in one step
+
+
+def test_step_labels_for_profiler_traces():
+    """The names steps carry in a trace (after atom/model_engine/run_labels.py): kind, requests, tokens,
+    portions and single tokens, padding of a captured shape, contexts of eager steps."""
+    from atom_b200.engine.runner import step_label
+    assert step_label([1, 1, 1], [41, 7, 100], graph_batch=4) == "decode[bs=3/4 tok=3 d=3]"
+    assert step_label([1] * 8, [9] * 8, graph_batch=8) == "decode[bs=8 tok=8 d=8]"
+    assert step_label([70, 1, 1, 5, 1], [70, 9, 9, 30, 2], graph_shape=(128, 8)) == "mixed[bs=5/8 tok=78/128 p=2 d=3]"
+    assert step_label([600, 300], [600, 300]) == "prefill[bs=2 tok=900 p=2 ctx=[600, 300]]"
+    assert step_label([1], [12]) == "eager_decode[bs=1 tok=1 d=1 ctx=12]"
+    assert step_label([2, 1, 1, 1, 1, 1, 1], [5, 6, 7, 8, 9, 10, 11]) == "prefill[bs=7 tok=8 p=1 d=6 ctx=[5, 6, 7]...+4]"
