@@ -172,6 +172,9 @@ def main() -> int:
     ap.add_argument("--num-kvcache-blocks", type=int, default=-1,
                     help="cache pages (default -1: sized by the engine from the memory that is left)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only-measured-graphs", action="store_true",
+                    help="capture only the decode graphs of the measured batch sizes and none for small mixed steps "
+                         "(a short start-up, for runs under a profiler)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -217,7 +220,9 @@ def main() -> int:
     eng = LLMEngine("", model_config=mcfg, dtype="bfloat16", load_dummy="random", seed=weight_seed,
                     kv_cache_block_size=PAGE, num_kvcache_blocks=args.num_kvcache_blocks,
                     max_num_seqs=max(64, max_b), max_num_batched_tokens=max([8192] + sweep_prefill),
-                    max_model_len=max_model_len)
+                    max_model_len=max_model_len,
+                    **(dict(cudagraph_capture_sizes=sorted(batches), cudagraph_mixed_steps=False)
+                       if args.only_measured_graphs else {}))
     runner = eng.runner
     rng = np.random.default_rng(8)
     sp_greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
