@@ -33,7 +33,7 @@ def _tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("V,H,T", [(389, 96, 7), (1000, 200, 33), (151, 4104, 3)])
+@pytest.mark.parametrize("V,H,T", [(389, 96, 7), (1000, 200, 33), (151, 4104, 3), (77, 100, 5), (301, 4096, 9), (64, 12288, 2)])
 def test_embedding(native, dtype, V, H, T):
     table = _rand((V, H), dtype, 1)
     ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2)).to(torch.int32).to(DEV)
