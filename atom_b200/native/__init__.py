@@ -365,7 +365,7 @@ class _RowsOpC(ctypes.Structure):
                 ("residual", _vp), ("norm_w", _vp), ("norm_w_dtype", _i), ("xout", _vp), ("ssq_out", _vp)]
 
 
-ROWS_M = 8      # rows up to which the weight-streaming product beats the library's (measured; it takes 16)
+ROWS_M = 16     # rows up to which the weight-streaming product is used (parts/linear.py: streams)
 
 
 def gemm_rows_grid() -> int:

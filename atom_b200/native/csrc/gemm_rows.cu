@@ -265,15 +265,19 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_wait(&full[s], u & 1, &aborted, p.error);
       const uint32_t wbase = smem_u32(ring + (size_t)s * STAGE);
       const unsigned char* xreg = ring + (size_t)s * STAGE + W_MAX;
-      for (int ck = kg; ck < KC; ck += KG) {
+      // a k group takes half chunks (two 16-k steps): kg, kg + 8, ... of the stage's 2 KC, so that all eight
+      // groups work on a stage of four chunks too (the stages of [gate ; up])
+      for (int un = kg; un < 2 * KC; un += KG) {
+        const int ck = un >> 1, ks0 = (un & 1) * 2;
         const unsigned char* xbox = xreg + ck * (MP * 128);
         const uint32_t crow = (uint32_t)(ck * h) + lrow;
-        uint32_t xb[MT][4][2];
+        uint32_t xb[MT][2][2];
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) ldsm_x2(xb[nt][ks], swizzled(xbox, nt * 8 + r8, ks * 2 + ((lane >> 3) & 1)));
-        uint32_t a[2][4][4];
+          for (int k2 = 0; k2 < 2; ++k2)
+            ldsm_x2(xb[nt][k2], swizzled(xbox, nt * 8 + r8, (ks0 + k2) * 2 + ((lane >> 3) & 1)));
+        uint32_t a[2][2][4];
         bool valid[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -285,19 +289,19 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const uint32_t off = (crow + (uint32_t)(tt * 16)) * 128u + (up ? up_off : 0u);
             const uint32_t rowaddr = wbase + off, sw = (off >> 7) & 7u;
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
+            for (int k2 = 0; k2 < 2; ++k2)
               asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                           : "=r"(a[j][ks][0]), "=r"(a[j][ks][1]), "=r"(a[j][ks][2]), "=r"(a[j][ks][3])
-                           : "r"(rowaddr + ((((uint32_t)(ks * 2) + lcol) ^ sw) << 4)));
+                           : "=r"(a[j][k2][0]), "=r"(a[j][k2][1]), "=r"(a[j][k2][2]), "=r"(a[j][k2][3])
+                           : "r"(rowaddr + ((((uint32_t)((ks0 + k2) * 2) + lcol) ^ sw) << 4)));
           }
         }
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
+        for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
           for (int j = 0; j < 2; ++j)
             if (valid[j]) {
 #pragma unroll
-              for (int nt = 0; nt < MT; ++nt) mma16816(acc[nt][j][ks & 1], a[j][ks], xb[nt][ks][0], xb[nt][ks][1]);
+              for (int nt = 0; nt < MT; ++nt) mma16816(acc[nt][j][k2], a[j][k2], xb[nt][k2][0], xb[nt][k2][1]);
             }
       }
       __syncwarp();

@@ -1,7 +1,7 @@
 """Matrix product y = x W^T (+ b) with weights [out, in], as atom/model_ops/linear.py:946-965.
 
 bfloat16: for many rows the GEMM library, as the reference does (tgemm.mm, linear.py:960); for
-few rows (decode: up to ``native.ROWS_M``, K a multiple of 64) the framework's weight-streaming
+few rows (decode: up to ``native.ROWS_M`` = 16, K a multiple of 64) the framework's weight-streaming
 kernel, which shares out rows of W among the CTAs (``native.gemm_rows``).  Both accumulate in
 32-bit.  float32: the framework's own FMA kernel, never a reduced-precision mode.
 """
@@ -54,12 +54,25 @@ def resolve(delta):
 def may_defer(x, weight) -> bool:
     """Whether out = x W^T is a product that a residual epilogue can take (few rows of bf16, sizes the
     row-sharing kernel takes)."""
-    if not FOLD_NORMS or isinstance(x, ScaledRows) or x.dtype != torch.bfloat16 or x.shape[0] > native.ROWS_M:
+    if not FOLD_NORMS or isinstance(x, ScaledRows) or x.dtype != torch.bfloat16:
         return False
-    return native.gemm_rows_supports(x.shape[0], weight.shape[0], x.shape[1], x.stride(0))
+    return streams(x.shape[0], weight.shape[0], x.shape[1], x.stride(0))
 
 
 FOLD_NORMS = True     # False: every norm runs as a kernel of its own (for measurements and tests)
+
+
+def streams(M: int, N: int, K: int, lda: int, gated: bool = False) -> bool:
+    """Whether x[M, K] W[N, K]^T (W of 2N rows if gated) runs on the weight-streaming kernel: up to
+    ``native.ROWS_M`` rows of sizes it takes.  From 9 rows on only where a CTA's rows make at most eight
+    sub-slabs: every sub-slab reads X again, and with the second token tile's shallower ring the library
+    wins on a matrix as tall as the head's (measured: 223 against 195 us at 16 rows)."""
+    if M > native.ROWS_M or not native.gemm_rows_supports(M, N, K, lda):
+        return False
+    if M > 8:
+        per_cta = -(-N // native.gemm_rows_grid())
+        return per_cta <= 8 * (32 if gated else 64)
+    return True
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
@@ -72,8 +85,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         if b is not None and b.dtype != torch.float32:
             b = b.float()
         native.gemm_f32(out, x, weight, b)
-    elif x.shape[0] <= native.ROWS_M and native.gemm_rows_supports(
-            x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
+    elif streams(x.shape[0], weight.shape[0], x.shape[1], x.stride(0)):
         native.gemm_rows(x, weight, out, bias)            # few rows: the product is a read of W
     else:
         native.gemm_bf16(out, x, weight)
@@ -91,7 +103,7 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scrat
     if isinstance(x, ScaledRows):
         native.gemm_rows(x.x, weight, out, gated=True, ssq_in=x.ssq, norm_size=x.size, norm_eps=x.eps)
         return out
-    if x.dtype == torch.bfloat16 and M <= native.ROWS_M and native.gemm_rows_supports(M, I, K, x.stride(0)):
+    if x.dtype == torch.bfloat16 and streams(M, I, K, x.stride(0), gated=True):
         native.gemm_rows(x, weight, out, gated=True)
         return out
     gu = linear(x, weight, None, scratch(M, 2 * I))

@@ -54,4 +54,4 @@ class RMSNorm(Norm):
         return (_linear.FOLD_NORMS and p.bias is None and self.rt.dtype == torch.bfloat16
                 and residual.dtype == torch.float32 and residual.is_contiguous()
                 and p.weight.shape[0] == self.size and _linear.may_defer(p.x, p.weight)
-                and native.gemm_rows_supports(M, 1, self.size, self.size))
+                and M <= native.ROWS_M and native.gemm_rows_supports(M, 1, self.size, self.size))

@@ -151,6 +151,37 @@ def test_both_sides_of_the_decode_products_match_plain(model_dirs, name, side):
         assert a < c, "the decode steps of D did not rotate inside the attention kernel"
 
 
+@pytest.mark.parametrize("name", ["A", "D"])
+@pytest.mark.parametrize("live", [9, 13, 16])
+def test_nine_to_sixteen_requests_decode_side_by_side(model_dirs, name, live):
+    """Steps of 9 to 16 single tokens take the streaming product's second token tile (with the norms in its
+    epilogues) where the widths allow it: every request's prompt in one step, then all of them decoded token
+    by token in the same steps, against the plain implementation."""
+    lengths = [20 + 3 * i for i in range(live)]
+    ps = tiny.prompts(name, lengths, seed=11)
+    seqs = {f"q{i}": p for i, p in enumerate(ps)}
+    ref = plain_logits(model_dirs[name], seqs)
+    tail = 6
+    steps = []
+    for rid, toks in seqs.items():
+        n = len(toks) - tail
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": list(toks[:n]), "want": list(range(n))}], "end": []})
+    for k in range(tail):
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": [toks[len(toks) - tail + k]], "want": [0]} for rid, toks in seqs.items()]})
+    steps[-1]["end"] = list(seqs)
+    runner = make_runner(model_dirs[name], "bfloat16", 64 * live, PAGE[name], max_num_seqs=16)
+    got = traces.collect(steps, replay(runner, steps))
+    err, rid, pos = max_err(got, ref)
+    tol = _tol("bfloat16", ref)
+    assert err <= tol, f"{name}/{live}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    for r in ref:
+        rms = float(np.sqrt(((got[r] - ref[r]) ** 2).mean()))
+        assert rms <= RMS_TOL_BF16 * scale, f"{name}/{live}: rms error {rms:.3e} in {r}"
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
 _launches = {}
 
 
