@@ -204,14 +204,14 @@ def _build_locked(nvcc: str, bdir: str, verbose: bool, defines: Dict[str, str], 
 
 
 def _prune(bdir: str, srcs: Sequence[str], tag: str, keep: set) -> None:
-    """Removes the objects of older versions of these sources in this variant, and objects
-    named in an older scheme (<source>.<hash>.o) whatever they belonged to."""
-    stems = {os.path.splitext(x)[0] for x in srcs}
+    """Removes the objects of this variant that the library just linked does not hold (older versions of
+    its sources, and sources that are gone), and objects named in an older scheme (<source>.<hash>.o)
+    whatever they belonged to."""
     for f in os.listdir(bdir):
         if not f.endswith(".o") or f in keep:
             continue
         parts = f.split(".")
-        stale = (len(parts) == 4 and parts[0] in stems and parts[1] == tag) or len(parts) == 3
+        stale = (len(parts) == 4 and parts[1] == tag) or len(parts) == 3
         if stale:
             try:
                 os.remove(os.path.join(bdir, f))
