@@ -19,8 +19,9 @@
 // once the kernels before have completed; one turns the sums of squares into the rows' factors beside
 // the stream (inside the X producer it held the stages' X back by 1-2 us); sixteen consume (one
 // mma.sync warp per scheduler keeps the tensor cores busy for a fraction of the time only, and with a
-// handful of stages per CTA the consumers' time per stage is on the critical path): 8 along k (one
-// 64-k chunk each) times 2 over the 16-row tiles.  At a sub-slab's end the warps' sums meet in shared
+// handful of stages per CTA the consumers' time per stage is on the critical path): 8 along k (half
+// chunks of two 16-k steps each, so that all work on a stage of four chunks too) times 2 over the 16-row
+// tiles, each warp with one or two 8-token tiles (up to 8 or 16 rows of X; with 16 the ring has 4 stages).  At a sub-slab's end the warps' sums meet in shared
 // memory and each of the 512 consumer threads settles one output (a single epilogue warp took 2-5 us
 // for it).
 //
