@@ -91,15 +91,26 @@ def bench_attention(args) -> None:
         plan = native.flash_plan(q_lens, nh // nkv, nkv, ctx, long_rows=long_rows)
         scratch = torch.empty(max(1, native.flash_scratch_elems(T, nh, hd, plan[2])), dtype=torch.float32, device=DEV)
 
+        rotate = args.mode == "decode" and args.rotate and native.flash_rotating_supports(hd, page, S * P, nh, nkv, hd)
+        if rotate:      # as the engine's decode steps run it: norm, rotation and cache write inside the kernel
+            table = torch.randn(ctx + 1, hd, device=DEV)
+            rows = torch.full((T,), ctx - 1, dtype=torch.int32, device=DEV)
+            nw = torch.ones(hd, device=DEV, dtype=torch.bfloat16)
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
         def run(k, v):
-            native.flash_attention(out, q, q.shape[1], k, v, bt, cu, cl, sot, T, S, nh, nkv, hd, hd ** -0.5, 0,
-                                   plan, scratch)
+            if rotate:
+                native.flash_attention_rotating(out, q, k, v, bt, cu, cl, sot, T, S, nh, nkv, hd, hd ** -0.5, 0, plan[2],
+                                                scratch, table, hd, rows, nw, nw, 1e-6, True, status)
+            else:
+                native.flash_attention(out, q, q.shape[1], k, v, bt, cu, cl, sot, T, S, nh, nkv, hd, hd ** -0.5, 0,
+                                       plan, scratch)
 
         t = _time_graph([(lambda kv=kv: run(*kv)) for kv in caches] * (1 if copies > 1 else 4))
         if args.mode == "decode":
             gb = B * ctx * nkv * hd * 2 * 2 / 1e9
-            print(f"decode  batch={B:3d} context={ctx} splits={plan[2]:2d}: {t:8.1f} us  {gb / t * 1e6:7.0f} GB/s of cache",
-                  flush=True)
+            print(f"decode  batch={B:3d} context={ctx} splits={plan[2]:2d}{' rotating' if rotate else ''}: {t:8.1f} us  "
+                  f"{gb / t * 1e6:7.0f} GB/s of cache", flush=True)
         else:
             fl = 4.0 * nh * hd * ctx * (ctx + 1) / 2 * B
             kind = "tcgen05" if len(plan) > 3 and plan[3] else "mma.sync"
@@ -163,6 +174,8 @@ def main(argv=None) -> int:
             p.add_argument("--context", type=int, default=4096)
             p.add_argument("--page", type=int, default=16)
             p.add_argument("--tc", type=int, default=1, help="0: keep long portions off the tcgen05 kernel")
+            p.add_argument("--rotate", type=int, default=1,
+                           help="decode: 1 (default) the kernel normalises, rotates and stores the new tokens itself; 0: it finds them ready")
     args = ap.parse_args(argv)
     native.lib()
     {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.what](args)
