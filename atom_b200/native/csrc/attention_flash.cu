@@ -1111,6 +1111,21 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
   if (s < 0 || rows > 16) return;   // beyond the batch, a padding row of a fixed-size batch, or not a short request
   const float* ml = p.part_ml + (int64_t)warp * p.num_splits * 2;
   const float* po = p.part_o + (int64_t)warp * p.num_splits * HD;
+  constexpr int VEC = HD / 32 > 0 ? HD / 32 : 1;   // (head sizes of 128, 256: a lane holds VEC consecutive elements)
+  constexpr bool WIDE = HD % 128 == 0;
+  constexpr int BATCH = 8;              // splits whose partial sums are asked for together
+  constexpr int NV = VEC / 4 > 0 ? VEC / 4 : 1;      // 16-byte pieces of a lane's elements
+  float4 first[WIDE ? BATCH * NV : 1];
+  if constexpr (WIDE) {
+    // the first splits' partial sums are asked for before the weights are known: one round trip, not two
+#pragma unroll
+    for (int k = 0; k < BATCH; ++k)
+#pragma unroll
+      for (int v = 0; v < VEC / 4; ++v)
+        first[k * (VEC / 4) + v] = k < p.num_splits
+                                       ? __ldcg(reinterpret_cast<const float4*>(po + (int64_t)k * HD + lane * VEC) + v)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const int k0 = lane, k1 = lane + 32;
   const float m0 = k0 < p.num_splits ? ml[2 * k0] : -INFINITY;
   const float m1 = k1 < p.num_splits ? ml[2 * k1] : -INFINITY;
@@ -1127,6 +1142,42 @@ __global__ void flash_merge_kernel(const Params p, const int* __restrict__ seq_o
   const float inv = 1.f / L;
   w0 *= inv;
   w1 *= inv;
+  if constexpr (WIDE) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int kb = 0; kb < p.num_splits; kb += BATCH) {
+      float4 part[BATCH * NV];
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k)
+#pragma unroll
+        for (int v = 0; v < VEC / 4; ++v) {
+          if (kb == 0)
+            part[k * (VEC / 4) + v] = first[k * (VEC / 4) + v];
+          else
+            part[k * (VEC / 4) + v] = kb + k < p.num_splits
+                                          ? __ldcg(reinterpret_cast<const float4*>(po + (int64_t)(kb + k) * HD + lane * VEC) + v)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+      for (int k = 0; k < BATCH; ++k) {
+        const int kk = kb + k;
+        const float wk = __shfl_sync(0xffffffffu, kk < 32 ? w0 : w1, kk & 31);     // (0 beyond the last split)
+#pragma unroll
+        for (int v = 0; v < VEC / 4; ++v) {
+          const float4 x = part[k * (VEC / 4) + v];
+          acc[4 * v] += x.x * wk;
+          acc[4 * v + 1] += x.y * wk;
+          acc[4 * v + 2] += x.z * wk;
+          acc[4 * v + 3] += x.w * wk;
+        }
+      }
+    }
+    __nv_bfloat16* o = p.out + (int64_t)warp * HD + lane * VEC;
+#pragma unroll
+    for (int e = 0; e < VEC; e += 2) *reinterpret_cast<__nv_bfloat162*>(o + e) = __floats2bfloat162_rn(acc[e], acc[e + 1]);
+    return;
+  }
   float acc[(HD + 31) / 32];
 #pragma unroll
   for (int i = 0; i < (HD + 31) / 32; ++i) acc[i] = 0.f;
