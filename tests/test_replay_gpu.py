@@ -182,6 +182,22 @@ def test_nine_to_sixteen_requests_decode_side_by_side(model_dirs, name, live):
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
 
 
+@pytest.mark.parametrize("page", [8, 32, 128])
+def test_other_page_sizes_on_the_tma_kernels(model_dirs, page):
+    """Head size 128 with pages of 8, 32 and 128 tokens (boxes of a page, or pieces of a larger one): the last
+    32 tokens one by one (rotation and cache write inside the decode kernel) and mixed steps, in bfloat16."""
+    name = "D"
+    seqs = _seqs(name)
+    ref = plain_logits(model_dirs[name], seqs)
+    runner = make_runner(model_dirs[name], "bfloat16", 2048, page)
+    for steps in (traces.tail_by_token(seqs, 32), traces.mixed(seqs, max_live=4, budget_tokens=2048, page=page)[0]):
+        got = traces.collect(steps, replay(runner, steps))
+        err, rid, pos = max_err(got, ref)
+        tol = _tol("bfloat16", ref)
+        assert err <= tol, f"page {page}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+    assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
 _launches = {}
 
 
