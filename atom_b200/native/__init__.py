@@ -566,6 +566,8 @@ def flash_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_pages: 
         block_table.data_ptr(), block_table.shape[1], page_size, cu_q.data_ptr(), ctx_len.data_ptr(),
         seq_of_token.data_ptr(), T, num_seqs, nh, nkv, hd, float(scale), int(window), int(long_tiles),
         LONG_ROWS, int(tiles), int(has_short), int(splits), _ptr(scratch), _stream()), "flash_attention")
+    # (one kernel for the long portions, one for the others, one for the short requests, one that merges their splits)
+    add_launches(int(long_tiles > 0) + int(tiles > 0) + int(bool(has_short)) + int(bool(has_short) and splits > 1) - 1)
 
 
 def flash_rotating_supports(hd: int, page_size: int, num_pages: int, nh: int, nkv: int, rotary_dim: int) -> bool:
@@ -610,6 +612,7 @@ def flash_attention_rotating(out: torch.Tensor, qkv: torch.Tensor, k_pages: torc
         table.data_ptr(), rows.data_ptr(), int(rotary_dim), table.shape[0], _ptr(q_weight), _ptr(k_weight),
         dtype_code(w.dtype) if w is not None else F32, float(eps), int(write_cache), status.data_ptr(), _stream()),
         "flash_attention_rotating")
+    add_launches(int(splits > 1))      # (the kernel that merges the splits)
 
 
 def flash_scratch_elems(T: int, nh: int, hd: int, splits: int) -> int:

@@ -72,6 +72,7 @@ class Sampler:
                 out.data_ptr(), logits.data_ptr(), dev[0].data_ptr(), dev[1].data_ptr(), dev[2].data_ptr(),
                 self._part.data_ptr(), chunks, R, V, torch.cuda.current_stream().cuda_stream)
             native._check(code, "sample_simple")
+            native.add_launches(1)          # (the chunks' kernel and the one that picks among them)
             return out
         probs = None
         if any_filter:
