@@ -68,6 +68,23 @@ def bench_gemm(args) -> None:
                     o2 = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
                     t = _time_graph([(lambda w=w: native.gemm_rows(x, w, o2, gated=True)) for w in ws])
                     line += f"  +silu*mul {t:7.1f} us ({gb / t * 1e6:6.0f} GB/s)"
+            if M > 16 and native.gemm_pairs_supports(M, N, K, K, N):
+                # many rows: the tcgen05 kernel against the library, turn and turn about (a B200 under its power
+                # cap slows down within a second of work, so the two sides share the warm and the cold moments)
+                gated = name == "gate_up"
+                o2 = torch.empty(M, N // 2 if gated else N, device=DEV, dtype=torch.bfloat16)
+                own = [(lambda w=w: native.gemm_pairs(x, w, o2, gated=gated)) for w in ws]
+                lib_ = [(lambda w=w: native.gemm_bf16(o1, x, w)) for w in ws]
+                if gated:
+                    lib_ = [f for w in ws for f in ((lambda w=w: native.gemm_bf16(o1, x, w)), (lambda: native.silu_mul(o2, o1)))]
+                to, tl = [], []
+                for _ in range(3):
+                    to.append(_time_graph(own, reps=2))
+                    tl.append(_time_graph(lib_, reps=2) * (2 if gated else 1))
+                fl = 2.0 * M * N * K
+                line = (f"{name:8s} rows={M:5d}  library{' + silu*mul' if gated else ''} {np.median(tl):7.1f} us  "
+                        f"two CTAs to a tile{' with silu*mul' if gated else ''} {np.median(to):7.1f} us "
+                        f"({fl / np.median(to) / 1e6:5.0f} TFLOP/s)  fill {native.gemm_pairs_waves(M, N // 2 if gated else N, gated):.2f}")
             print(line, flush=True)
     native.check_error_flags()
 

@@ -72,6 +72,9 @@ _SIGNATURES = {
     "atom_gemm_rows": [_vp, _i, _vp, _vp],
     "atom_gemm_rows_grid": [],
     "atom_gemm_rows_supports": [_i, _i, _i, _i64],
+    "atom_gemm_pairs": [_vp, _i64, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp],
+    "atom_gemm_pairs_resident": [],
+    "atom_gemm_pairs_supports": [_i, _i, _i, _i64, _i64],
     "atom_set_option": [_i, _i],
     "atom_copy_rows_h2d": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
 }
@@ -416,6 +419,46 @@ def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     c.norm_w_dtype = dtype_code(norm_w.dtype) if norm_w is not None else F32
     c.xout, c.ssq_out = _ptr(xout), _ptr(ssq_out)
     _check(lib().atom_gemm_rows(ctypes.byref(c), M, error_flag(x.device).data_ptr(), _stream()), "gemm_rows")
+
+
+def gemm_pairs_supports(M: int, N: int, K: int, lda: int, ldc: int) -> bool:
+    return bool(lib().atom_gemm_pairs_supports(M, N, K, lda, ldc)) and gemm_pairs_resident() > 0
+
+
+_pairs_resident = None
+
+
+def gemm_pairs_resident() -> int:
+    """Pairs of CTAs of a ``gemm_pairs`` launch: as many as the device holds at once."""
+    global _pairs_resident
+    if _pairs_resident is None:
+        _pairs_resident = int(lib().atom_gemm_pairs_resident())
+    return _pairs_resident
+
+
+def gemm_pairs_waves(M: int, N: int, gated: bool) -> float:
+    """How well the tiles of a ``gemm_pairs`` product fill the device: tiles / (waves x pairs), where the
+    last, ragged wave counts 0.72 when it is handed out in halves (csrc/gemm_pairs.cu: plan_items; a half
+    tile runs at about 0.72 of a whole one's time)."""
+    pairs = gemm_pairs_resident()
+    if pairs < 1:
+        return 0.0
+    tiles = -(-M // 256) * (-(-N // 256) if gated else -(-N // 512))
+    full, rem = divmod(tiles, pairs)
+    waves = full + (0.0 if rem == 0 else (0.72 if full > 0 and 2 * rem <= pairs else 1.0))
+    return tiles / (waves * pairs)
+
+
+def gemm_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] w[N, K]^T in bf16 on tcgen05 with two CTAs to a tile; ``gated``: w = [gate ; up]
+    of 2N rows, out = silu(x gate^T) * (x up^T) (csrc/gemm_pairs.cu)."""
+    M, K = x.shape
+    N = out.shape[1]
+    _cuda(x, w, out)
+    assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and w.shape[1] == K and w.is_contiguous()
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M and w.shape[0] == (2 * N if gated else N)
+    _check(lib().atom_gemm_pairs(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), M, N, K,
+                                 int(gated), error_flag(x.device).data_ptr(), _stream()), "gemm_pairs")
 
 
 def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

@@ -2,8 +2,10 @@
 
 bfloat16: for many rows the GEMM library, as the reference does (tgemm.mm, linear.py:960); for
 few rows (decode: up to ``native.ROWS_M`` = 16, K a multiple of 64) the framework's weight-streaming
-kernel, which shares out rows of W among the CTAs (``native.gemm_rows``).  Both accumulate in
-32-bit.  float32: the framework's own FMA kernel, never a reduced-precision mode.
+kernel, which shares out rows of W among the CTAs (``native.gemm_rows``); the gated product of a
+long prompt portion on the framework's tcgen05 kernel with the activation in its epilogue
+(``native.gemm_pairs``).  All accumulate in 32-bit.  float32: the framework's own FMA kernel, never
+a reduced-precision mode.
 """
 from __future__ import annotations
 
@@ -75,6 +77,19 @@ def streams(M: int, N: int, K: int, lda: int, gated: bool = False) -> bool:
     return True
 
 
+PAIRS_MIN_ROWS = 1024     # the gated product runs on native.gemm_pairs from this many rows on (0: never)
+PAIRS_MIN_FILL = 0.85     # ... where its tiles fill the device's waves at least this well
+
+
+def pairs_pay(M: int, N: int, K: int, lda: int, ldc: int) -> bool:
+    """Whether silu(x gate^T) * (x up^T) of M rows, N outputs runs on the tcgen05 kernel with the activation
+    in its epilogue: measured against the library's product plus the activation kernel it wins from about a
+    thousand rows on, where the tiles (256 rows x 256 outputs, one pair of CTAs each) fill whole waves."""
+    if PAIRS_MIN_ROWS <= 0 or M < PAIRS_MIN_ROWS or not native.gemm_pairs_supports(M, N, K, lda, ldc):
+        return False
+    return native.gemm_pairs_waves(M, N, True) >= PAIRS_MIN_FILL
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias).  ``out`` may be float32 for bf16 operands."""
     if isinstance(x, ScaledRows):
@@ -95,9 +110,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
 
 
 def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scratch) -> torch.Tensor:
-    """out[M, I] = silu(x W_gate^T) * (x W_up^T) for weight [2I, K] = [gate ; up].  Few rows:
-    one kernel, the activation fused into the product.  Else the product into
-    ``scratch(M, 2I)`` and the activation kernel."""
+    """out[M, I] = silu(x W_gate^T) * (x W_up^T) for weight [2I, K] = [gate ; up].  Few rows, and
+    long portions in bf16 (``pairs_pay``): one kernel, the activation fused into the product.  Else
+    the product into ``scratch(M, 2I)`` and the activation kernel."""
     M, K = x.shape
     I = weight.shape[0] // 2
     if isinstance(x, ScaledRows):
@@ -105,6 +120,9 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, scrat
         return out
     if x.dtype == torch.bfloat16 and streams(M, I, K, x.stride(0), gated=True):
         native.gemm_rows(x, weight, out, gated=True)
+        return out
+    if x.dtype == torch.bfloat16 and pairs_pay(M, I, K, x.stride(0), out.stride(0)):
+        native.gemm_pairs(x, weight, out, gated=True)
         return out
     gu = linear(x, weight, None, scratch(M, 2 * I))
     native.silu_mul(out, gu)

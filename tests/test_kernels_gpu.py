@@ -653,6 +653,63 @@ def test_gemm_rows_do_not_depend_on_the_batch(native):
     torch.testing.assert_close(outs[16], a.float() @ w.float().T, rtol=2e-3, atol=5e-3)
 
 
+# ----------------------------------------------------------------------------- many-row product on pairs of CTAs (tcgen05)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (1, 8, 8), (300, 544, 448), (129, 1000, 200), (2048, 4096, 4096),
+                                   (777, 5000, 72), (4100, 520, 1024), (5000, 20000, 64)])
+def test_gemm_pairs(native, M, N, K):
+    """One tile and less than one, rows and columns that end inside a tile, a k that ends inside a block of 64,
+    more tiles than the device holds pairs of CTAs (several rounds, the last in halves)."""
+    a, w = _rand((M, K), torch.bfloat16, 60), _rand((N, K), torch.bfloat16, 61)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert native.gemm_pairs_supports(M, N, K, K, N)
+    native.gemm_pairs(a, w, out)
+    native.check_error_flags()
+    want = a.float() @ w.float().T
+    torch.testing.assert_close(out.float(), want.bfloat16().float(), rtol=1e-2, atol=1e-2 * math.sqrt(K / 96))
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 256, 128), (5, 112, 64), (1030, 1001 * 8, 320), (2048, 12288, 4096),
+                                   (333, 160, 192), (3000, 9728, 2560)])
+def test_gemm_pairs_gated(native, M, I, K):
+    """The activation in the epilogue: gate and up sums of an output lie in the same half of a tile."""
+    a, w = _rand((M, K), torch.bfloat16, 62), _rand((2 * I, K), torch.bfloat16, 63, 0.3)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    native.gemm_pairs(a, w, out, gated=True)
+    native.check_error_flags()
+    gu = a.double() @ w.double().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    torch.testing.assert_close(out.double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K / 96))
+
+
+def test_gemm_pairs_strided_and_batch_independent(native):
+    """X and the output may be column ranges of wider arrays, nothing beside the output is written, and a
+    row's result does not depend on the rows beside it."""
+    M, N, K = 700, 392, 256
+    big_a = _rand((M, K + 64), torch.bfloat16, 64)
+    w = _rand((N, K), torch.bfloat16, 65)
+    big_out = torch.full((M, N + 24), float("nan"), dtype=torch.bfloat16, device=DEV)
+    native.gemm_pairs(big_a[:, 64:], w, big_out[:, 8:8 + N])
+    native.check_error_flags()
+    want = (big_a[:, 64:].float() @ w.float().T).bfloat16().float()
+    torch.testing.assert_close(big_out[:, 8:8 + N].float(), want, rtol=1e-2, atol=2e-2)
+    assert torch.isnan(big_out[:, :8]).all() and torch.isnan(big_out[:, 8 + N:]).all()
+    part = torch.empty((130, N), dtype=torch.bfloat16, device=DEV)
+    native.gemm_pairs(big_a[300:430, 64:], w, part)
+    native.check_error_flags()
+    assert torch.equal(part, big_out[300:430, 8:8 + N])
+
+
+def test_gemm_pairs_refuses_what_it_cannot_take(native):
+    assert not native.gemm_pairs_supports(64, 100, 64, 64, 100)      # columns: a multiple of 8
+    assert not native.gemm_pairs_supports(64, 96, 60, 60, 96)        # k: a multiple of 8
+    assert not native.gemm_pairs_supports(64, 96, 64, 68, 96)        # rows of x 16 bytes apart
+    a, w = _rand((64, 60), torch.bfloat16, 66), _rand((96, 60), torch.bfloat16, 67)
+    with pytest.raises(RuntimeError):
+        native.gemm_pairs(a, w, torch.empty((64, 96), dtype=torch.bfloat16, device=DEV))
+
+
 @pytest.mark.parametrize("M,H,I,wdtype", [(8, 4096, 12288, torch.bfloat16), (3, 320, 960, torch.float32),
                                           (1, 64, 192, torch.float32), (11, 1088, 2112, torch.bfloat16)])
 def test_gemm_rows_norm_without_a_pass_of_its_own(native, M, H, I, wdtype):

@@ -108,6 +108,45 @@ def test_request_freed_and_fed_again_matches_plain(model_dirs, runners, name, dt
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_gated_product_of_portions_on_the_tcgen05_kernel_matches_plain(model_dirs, name):
+    """Long portions run their gated product on the kernel with two CTAs to a tile (from a thousand rows on by
+    itself).  Forced for every portion of more than 16 rows, whole prompts, portions of changing size and the
+    mixed trace give the plain implementation's logits on every configuration (widths that end inside a block
+    of 64, outputs that end inside a tile), and the kernel did run."""
+    from atom_b200 import native
+    from atom_b200.parts import linear
+
+    seqs = _seqs(name)
+    ref = plain_logits(model_dirs[name], seqs)
+    saved = (linear.PAIRS_MIN_ROWS, linear.PAIRS_MIN_FILL)
+    calls = [0]
+    real = native.gemm_pairs
+
+    def counted(*args, **kwargs):
+        calls[0] += 1
+        return real(*args, **kwargs)
+
+    try:
+        linear.PAIRS_MIN_ROWS, linear.PAIRS_MIN_FILL = 17, 0.0
+        native.gemm_pairs = counted
+        runner = make_runner(model_dirs[name], "bfloat16", 512, PAGE[name])
+        for steps in (traces.whole(seqs), traces.ragged(seqs), traces.mixed(seqs, max_live=4, budget_tokens=512)[0]):
+            got = traces.collect(steps, replay(runner, steps))
+            err, rid, pos = max_err(got, ref)
+            tol = _tol("bfloat16", ref)
+            assert err <= tol, f"{name}: max abs error {err:.3e} at {rid}[{pos}] > {tol:.3e}"
+            scale = max(float(np.abs(r).max()) for r in ref.values())
+            for r in ref:
+                rms = float(np.sqrt(((got[r] - ref[r]) ** 2).mean()))
+                assert rms <= RMS_TOL_BF16 * scale, f"{name}: rms error {rms:.3e} in {r}"
+        assert calls[0] > 0, "no portion ran on the kernel"
+        assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+    finally:
+        native.gemm_pairs = real
+        linear.PAIRS_MIN_ROWS, linear.PAIRS_MIN_FILL = saved
+
+
 @pytest.mark.parametrize("name", ["A", "D"])
 @pytest.mark.parametrize("side", ["norms folded into the products", "norms as kernels of their own",
                                   "the library's product", "rotation as a kernel of its own"])
