@@ -21,7 +21,8 @@
 // tensor memory's lanes that its index selects), apply the epilogue and write blocks of 128 rows x 64
 // columns to shared memory, from where TMA stores take them (rows and columns beyond the matrix are cut
 // off by the store, rows and columns beyond X and W are read as zeros).  The tensor memory is full with
-// one tile, so the MMAs of a tile wait for the epilogue of the one before; the loads do not.
+// one tile, so the MMAs of a tile wait until the epilogue of the one before has read the sums (a gated
+// tile's outputs fit in registers as bf16, so its stores come after that); the loads do not wait.
 // All waits are bounded (tma.cuh); tensor memory is freed on every path.
 #include "tma.cuh"
 #include <cuda_bf16.h>
@@ -49,7 +50,6 @@ constexpr size_t SMEM = 1024 + BARS_OFF + 256;
 
 struct Params {
   int M, N, K;        // N: columns of C (gated: W has 2 N rows)
-  int gated;
   int mt, nt;         // tiles of 256 rows, tiles of 512 columns of sums
   int full_items;     // work items [0, full_items) are whole tiles, the others halves of the tiles that follow
   int items;
@@ -188,6 +188,7 @@ __device__ __forceinline__ Item item_of(const Params& p, int i) {
   return w;
 }
 
+template <bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
 gemm_pairs_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW,
                   const __grid_constant__ CUtensorMap mapC, const Params p) {
@@ -235,7 +236,7 @@ gemm_pairs_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constan
         const uint32_t bytes = 2 * BLK * (1 + (int)w.h0 + (int)w.h1);
         int row;
         if (which == 0) row = m0 + 128 * (int)rank;
-        else if (p.gated) row = (int)rank * p.N + nti * 256 + (which - 1) * 128;
+        else if (GATED) row = (int)rank * p.N + nti * 256 + (which - 1) * 128;
         else row = nti * 512 + (which - 1) * 256 + 128 * (int)rank;
         for (int kt = 0; kt < KT; ++kt, ++it) {
           if (!mine) continue;
@@ -283,63 +284,95 @@ gemm_pairs_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constan
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue: 8 warps, a block of 64 columns at a time
+    // ------------------------------------------------------------------ epilogue: 8 warps, blocks of 64 output columns
     const int q = warp & 3;                       // the quarter of the tensor memory's lanes this warp may read
     const int ch = (warp - EPI_WARP0) >> 2;       // which 32 of a block's 64 columns this warp writes
     const int r = 32 * q + lane;                  // row of the CTA's 128
     const bool issuer = threadIdx.x == EPI_WARP0 * 32;
     const uint32_t empty0[2] = {map_to_rank(smem_u32(&bars->acc_empty[0]), 0), map_to_rank(smem_u32(&bars->acc_empty[1]), 0)};
     const uint32_t tbase = tmem + ((uint32_t)(32 * q) << 16);
-    const int nblk = p.gated ? 2 : 4;             // blocks of 64 output columns in a half
     int used[2] = {0, 0};
     int blocks = 0;                               // output blocks written so far (they alternate between two buffers)
+    // 32 values of this thread's row (16 registers of bf16 pairs) into the block buffer, and the block on its way.
+    auto put_block = [&](const uint32_t* v, int x, int y) {
+      if (issuer && blocks >= 2) stores_read_but_one();   // the store that read this buffer two blocks ago is through with it
+      epi_sync();
+      const uint32_t buf = sbase + OUT_OFF + (blocks & 1) * BLK;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t dst = buf + r * 128 + (((ch * 4 + c) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(v[4 * c]), "r"(v[4 * c + 1]), "r"(v[4 * c + 2]),
+                     "r"(v[4 * c + 3])
+                     : "memory");
+      }
+      fence_async_smem();
+      epi_sync();
+      if (issuer) {
+        if (y < p.M && x < p.N) store_box(&mapC, x, y, buf);
+        store_commit();      // (an empty group where nothing of the block lies inside C, so that the count of groups holds)
+      }
+      ++blocks;
+    };
+    auto pack = [](const float* v, uint32_t* o) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+    };
     for (int i = pair; i < p.items; i += n_pairs) {
       const Item w = item_of(p, i);
       const int m0 = (w.tile % p.mt) * 256, nti = w.tile / p.mt;
+      const int y = m0 + 128 * (int)rank;
+      if (GATED) {
+        // First everything out of the tensor memory (a tile's 256 outputs of this thread's row and column half
+        // fit in 64 registers as bf16), so that the next tile's MMAs wait for the reads only; then the stores.
+        uint32_t o[2][2][16];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (!(h == 0 ? w.h0 : w.h1)) continue;
-        mbar_wait(&bars->acc_full[h], used[h] & 1, aborted, p.error);
-        ++used[h];
-        tc_fence_after();
-        for (int b = 0; b < nblk; ++b, ++blocks) {
-          float v[32];
-          if (p.gated) {
-            float g[32];
+        for (int h = 0; h < 2; ++h) {
+          if (!(h == 0 ? w.h0 : w.h1)) continue;
+          mbar_wait(&bars->acc_full[h], used[h] & 1, aborted, p.error);
+          ++used[h];
+          tc_fence_after();
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            float g[32], u[32];
             tmem_ld32(tbase + h * 256 + b * 64 + ch * 32, g);
-            tmem_ld32(tbase + h * 256 + 128 + b * 64 + ch * 32, v);
+            tmem_ld32(tbase + h * 256 + 128 + b * 64 + ch * 32, u);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu(g[j]) * v[j];
-          } else {
+            for (int j = 0; j < 32; ++j) g[j] = silu(g[j]) * u[j];
+            pack(g, o[h][b]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) arrive_at(empty0[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!(h == 0 ? w.h0 : w.h1)) continue;
+#pragma unroll
+          for (int b = 0; b < 2; ++b) put_block(o[h][b], nti * 256 + h * 128 + b * 64, y);
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!(h == 0 ? w.h0 : w.h1)) continue;
+          mbar_wait(&bars->acc_full[h], used[h] & 1, aborted, p.error);
+          ++used[h];
+          tc_fence_after();
+          for (int b = 0; b < 4; ++b) {
+            float v[32];
+            uint32_t o[16];
             tmem_ld32(tbase + h * 256 + b * 64 + ch * 32, v);
             tmem_wait_ld();
-          }
-          if (b == nblk - 1) {       // the sums of this half are in registers: the next tile may overwrite them
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) arrive_at(empty0[h]);
-          }
-          if (issuer && blocks >= 2) stores_read_but_one();   // the store that read this buffer two blocks ago is through with it
-          epi_sync();
-          const uint32_t buf = sbase + OUT_OFF + (blocks & 1) * BLK;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            __nv_bfloat162 hh[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) hh[j] = __floats2bfloat162_rn(v[c * 8 + 2 * j], v[c * 8 + 2 * j + 1]);
-            const uint4 val = *reinterpret_cast<uint4*>(hh);
-            const uint32_t dst = buf + r * 128 + (((ch * 4 + c) ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
-                         : "memory");
-          }
-          fence_async_smem();
-          epi_sync();
-          if (issuer) {
-            const int x = p.gated ? nti * 256 + h * 128 + b * 64 : nti * 512 + h * 256 + b * 64;
-            const int y = m0 + 128 * (int)rank;
-            if (y < p.M && x < p.N) store_box(&mapC, x, y, buf);
-            store_commit();      // (an empty group where nothing of the block lies inside C, so that the count of groups holds)
+            if (b == 3) {       // the sums of this half are in registers: the next tile may overwrite them
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) arrive_at(empty0[h]);
+            }
+            pack(v, o);
+            put_block(o, nti * 512 + h * 256 + b * 64, y);
           }
         }
       }
@@ -356,7 +389,8 @@ gemm_pairs_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constan
 static int resident_pairs() {
   static int pairs = 0;
   if (pairs == 0) {
-    if (cudaFuncSetAttribute(gemm_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(gemm_pairs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
       return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2, 1, 1);
@@ -370,7 +404,7 @@ static int resident_pairs() {
     cfg.attrs = at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_pairs_kernel, &cfg) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pairs_kernel<true>, &cfg) != cudaSuccess || n < 1) {
       (void)cudaGetLastError();
       return 0;
     }
@@ -419,13 +453,13 @@ ATOM_EXPORT int atom_gemm_pairs(const void* X, int64_t lda, const void* W, void*
   p.M = M;
   p.N = N;
   p.K = K;
-  p.gated = gated ? 1 : 0;
   p.mt = (M + 255) / 256;
   p.nt = gated ? (N + 255) / 256 : (N + 511) / 512;
   p.error = error;
   const int tiles = p.mt * p.nt;
   if (pairs > tiles) pairs = tiles;
   p.items = plan_items(tiles, pairs, &p.full_items);
-  atom::launch_pdl(gemm_pairs_kernel, dim3(2 * pairs), dim3(NTHREADS), SMEM, stream, mx, mw, mc, p);
+  if (gated) atom::launch_pdl(gemm_pairs_kernel<true>, dim3(2 * pairs), dim3(NTHREADS), SMEM, stream, mx, mw, mc, p);
+  else atom::launch_pdl(gemm_pairs_kernel<false>, dim3(2 * pairs), dim3(NTHREADS), SMEM, stream, mx, mw, mc, p);
   return atom::check_launch();
 }
