@@ -77,14 +77,15 @@ def streams(M: int, N: int, K: int, lda: int, gated: bool = False) -> bool:
     return True
 
 
-PAIRS_MIN_ROWS = 1024     # the gated product runs on native.gemm_pairs from this many rows on (0: never)
-PAIRS_MIN_FILL = 0.85     # ... where its tiles fill the device's waves at least this well
+PAIRS_MIN_ROWS = 600      # the gated product runs on native.gemm_pairs from this many rows on (0: never)
+PAIRS_MIN_FILL = 0.76     # ... where its tiles fill the device's waves at least this well
 
 
 def pairs_pay(M: int, N: int, K: int, lda: int, ldc: int) -> bool:
     """Whether silu(x gate^T) * (x up^T) of M rows, N outputs runs on the tcgen05 kernel with the activation
-    in its epilogue: measured against the library's product plus the activation kernel it wins from about a
-    thousand rows on, where the tiles (256 rows x 256 outputs, one pair of CTAs each) fill whole waves."""
+    in its epilogue: measured against the library's product plus the activation kernel it wins from 640 rows
+    on (not at 512) wherever the tiles (256 rows x 256 outputs, one pair of CTAs each) fill three quarters of
+    the device's waves."""
     if PAIRS_MIN_ROWS <= 0 or M < PAIRS_MIN_ROWS or not native.gemm_pairs_supports(M, N, K, lda, ldc):
         return False
     return native.gemm_pairs_waves(M, N, True) >= PAIRS_MIN_FILL
