@@ -1418,6 +1418,17 @@ static int flash_run(void* out, const void* q, int64_t q_stride, const void* k_p
                 atom::tma::make_map_raw(&maps.q, q, 3, d3, s3, b3);
     }
     if (use_tma) {
+      // The two-tile kernel trades registers between its warpgroups (setmaxnreg), which waits without a bound
+      // if the CTA's pool is smaller than the kernel assumes: it runs only if it was compiled to the register
+      // count its numbers are made for.
+      static int tc2_regs = -1;
+      if (tc2_regs < 0) {
+        cudaFuncAttributes fa;
+        tc2_regs = cudaFuncGetAttributes(&fa, tc2::flash_prefill_tc2_kernel) == cudaSuccess ? fa.numRegs : 0;
+      }
+      if (tc2_regs != tc2::LAUNCH_REGS) use_tma = false;
+    }
+    if (use_tma) {
       bool& tc2_attr = attr_done(1);
       if (!tc2_attr) {
         if (cudaFuncSetAttribute(tc2::flash_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

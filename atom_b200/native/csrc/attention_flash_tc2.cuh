@@ -7,19 +7,23 @@
 // head) as two tiles A and B of 128 rows, and walks over the request's keys in tiles of 128:
 //     S_X = Q_X K^T     tcgen05.mma, operands from shared memory, S_X (128 x 128, 32-bit) in
 //                       tensor memory, one buffer per query tile
-//     P_X = softmax     one warpgroup per query tile, one row per thread (tcgen05.ld of the
-//                       row, running maximum and sum in 32-bit); P_X goes back into the first
-//                       64 columns of S_X as bf16 pairs
+//     P_X = softmax     two warpgroups per query tile, two threads per row (each takes 64 of the
+//                       128 keys: tcgen05.ld of its half row, the two halves' maxima exchanged
+//                       through shared memory, running maximum and sums in 32-bit); P_X goes
+//                       back into the first 64 columns of S_X as bf16 pairs
 //     O_X += P_X V      tcgen05.mma with A from tensor memory, V as it lies in the pages
 // The single MMA-issuing thread alternates between the tiles, S_A(0) S_B(0) | PV_A(0) S_A(1)
 // | PV_B(0) S_B(1) | PV_A(1) ..., so while one warpgroup computes exponentials the tensor
 // cores work for the other tile, and every K and V tile that comes into shared memory is used
 // for twice the rows.  Tensor memory: S_A, S_B, O_A, O_B = 512 columns.  Shared memory: Q 64 KB,
 // two stages of K and of V, 32 KB each.
-// Warps 0-3 softmax and epilogue of tile A, 4-7 of tile B (warp w owns TMEM lanes
-// 32 (w mod 4) ...; a thread holds its whole row of S in registers, which the third warpgroup
-// cedes to these two with setmaxnreg), warp 8 issues the TMA boxes, warp 9 allocates tensor
-// memory and issues every MMA from one thread, warps 10 and 11 only fill the third warpgroup.
+// Warps 0-7 softmax and epilogue of tile A (0-3 the keys 0..63 of a key tile, 4-7 the keys 64..127),
+// warps 8-15 of tile B (warp w owns TMEM lanes 32 (w mod 4) ...; a thread holds its half row of S in
+// registers; the fifth warpgroup cedes registers to these four with setmaxnreg), warp 16 issues the TMA
+// boxes, warp 17 allocates tensor memory and issues every MMA from one thread, warps 18 and 19 only fill
+// the fifth warpgroup.  A tile's exponentials (one special-function operation per score, the unit
+// does 16 a clock) thus run on all four schedulers at once, which halves the time a tile's chain
+// softmax -> PV -> next S spends in its softmax.
 // All waits are bounded; tensor memory is freed on every path.
 #pragma once
 #include "attention_flash_tc.cuh"
@@ -31,20 +35,26 @@ namespace tc2 {
 using namespace atom::flash::tc;
 
 constexpr int ROWS2 = 2 * TM;                 // packed query rows per CTA
-constexpr int NTHREADS2 = 384;                // two softmax warpgroups and a third with the loader warp and the MMA warp
-constexpr int SOFTMAX_REGS = 224, OTHER_REGS = 56;   // registers per thread after the warpgroups have traded them
-constexpr int LOAD_WARP = 8, MMA_WARP2 = 9;
+constexpr int NTHREADS2 = 640;                // four softmax warpgroups and a fifth with the loader warp and the MMA warp
+// Registers per thread after the warpgroups have traded them.  setmaxnreg.inc waits, without a bound, until the
+// CTA's own pool (threads x registers per thread at launch) has that many to give, so the sum must fit the pool:
+// 512 x 104 + 128 x 64 = 640 x 96; the launch code checks the compiled kernel's register count against it.
+constexpr int SOFTMAX_REGS = 104, OTHER_REGS = 64, LAUNCH_REGS = 96;
+static_assert(16 * 32 * SOFTMAX_REGS + 4 * 32 * OTHER_REGS <= 640 * LAUNCH_REGS, "the warpgroups' registers exceed the CTA's pool");
+constexpr int SOFTMAX_WARPS = 16, LOAD_WARP = 16, MMA_WARP2 = 17;
+constexpr int HALF = TN / 2;                  // keys of a thread per key tile
 constexpr int KV_STAGES = 2;
 constexpr uint32_t SA_COL = 0, SB_COL = 128, OA_COL = 256, OB_COL = 384;
 // shared memory: Q_A, Q_B (2 blocks each), K stages (2 blocks each), V stages (2 blocks each)
 constexpr int S2_Q = 0, S2_K = 4 * BLOCK, S2_V = S2_K + KV_STAGES * 2 * BLOCK, S2_DATA = S2_V + KV_STAGES * 2 * BLOCK;
-constexpr size_t smem_bytes2() { return 1024 + S2_DATA + 256; }
+constexpr size_t smem_bytes2() { return 1024 + S2_DATA + 256 + 2 * 2 * 2 * TM * 4; }
 
 struct Bars2 {
   uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES], v_empty[KV_STAGES];
   uint64_t s_full[2], p_full[2], o_full[2];   // [0] tile A, [1] tile B
   uint32_t tmem_base;
   int aborted;
+  float xch[2][2][2][TM];                     // [step parity][query tile][half][row]: the halves' row maxima (at the end: sums)
 };
 
 __global__ void __launch_bounds__(NTHREADS2, 1)
@@ -105,7 +115,7 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&bars->s_full[x], 1);
-      mbar_init(&bars->p_full[x], 128);
+      mbar_init(&bars->p_full[x], 256);
       mbar_init(&bars->o_full[x], 1);
     }
     bars->aborted = 0;
@@ -119,7 +129,7 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
   volatile int* aborted = &bars->aborted;
   // The softmax threads hold a whole row of S (128 values) in registers: the third warpgroup gives
   // up registers it does not need and the softmax warpgroups take them.
-  if (warp >= 8) {
+  if (warp >= SOFTMAX_WARPS) {
    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(OTHER_REGS));
    if (warp == LOAD_WARP) {
     // ------------------------------------------------------------------ loader: TMA boxes
@@ -231,48 +241,55 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
     }
    }
   } else {
-    // ------------------------------------------------------------------ softmax and epilogue of tile x
+    // ------------------------------------------------------------------ softmax and epilogue of tile x, keys / columns of half c
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(SOFTMAX_REGS));
-    const int x = warp >> 2;
-    const int r = threadIdx.x & 127;                 // row of the tile = TMEM lane
+    const int x = warp >> 3, c2 = (warp >> 2) & 1;
+    const int r = (warp & 3) * 32 + lane;            // row of the tile = TMEM lane
     const int R = w.row0 + x * TM + r;
     const int pos = R < w.rows_total ? w.q_start + R / p.group : -1;
     const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
     const uint32_t scol = tmem + lane_base + (x ? SB_COL : SA_COL);
-    const uint32_t ocol = tmem + lane_base + (x ? OB_COL : OA_COL);
+    const uint32_t ocol = tmem + lane_base + (x ? OB_COL : OA_COL) + c2 * (HD / 2);
+    const int pair_bar = 1 + x * 4 + (warp & 3);     // named barrier of the two warps that share these 32 rows
     const float c = p.scale_log2;
     const int n_mine = n_of[x];
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;                    // l: the sum over this thread's keys only
     for (int j = 0; j < n_mine; ++j) {
-      if (r == 0) TC_TRACE(x * 4 + 0, j);
+      if (r == 0 && c2 == 0) TC_TRACE(x * 4 + 0, j);
       mbar_wait(&bars->s_full[x], j & 1, aborted, p.error);
       tc_fence_after();
-      if (r == 0) TC_TRACE(x * 4 + 1, j);
-      const int key0 = j * TN;
-      const bool diag = key0 + TN - 1 > pos;   // the diagonal crosses this tile for this row (or the row does not exist)
-      // the whole row in registers: one round trip to tensor memory per tile
-      float s[TN];
+      if (r == 0 && c2 == 0) TC_TRACE(x * 4 + 1, j);
+      const int key0 = j * TN + c2 * HALF;
+      const bool diag = key0 + HALF - 1 > pos;   // the diagonal crosses this half tile for this row (or the row does not exist)
+      // the half row in registers: one round trip to tensor memory per tile
+      float s[HALF];
 #pragma unroll
-      for (int q = 0; q < TN / 32; ++q) tmem_ld32(scol + q * 32, s + q * 32);
+      for (int q = 0; q < HALF / 32; ++q) tmem_ld32(scol + c2 * HALF + q * 32, s + q * 32);
       tmem_wait_ld();
       if (diag) {
 #pragma unroll
-        for (int i = 0; i < TN; ++i)
+        for (int i = 0; i < HALF; ++i)
           if (key0 + i > pos) s[i] = -INFINITY;
       }
       float mx8[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) mx8[e] = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < TN; i += 8) {
+      for (int i = 0; i < HALF; i += 8) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
       }
-      const float mt = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mt = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                       fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      // The row's maximum over both halves.  After this barrier both threads of the row have read their
+      // scores, so the first 64 columns of S may take P.
+      bars->xch[j & 1][x][c2][r] = mt;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+      mt = fmaxf(mt, bars->xch[j & 1][x][c2 ^ 1][r]);
       // The exponent's offset m follows the row maximum lazily: it moves (and O and l are rescaled)
       // only when the maximum has outgrown it by more than 2^8, so P stays below 256 and most tiles
-      // need no pass over O.  The quotient O / l does not depend on the offset.
+      // need no pass over O.  The quotient O / l does not depend on the offset.  Both threads of a row
+      // see the same maxima and decide alike.
       const bool grow = (mt - m) * c > 8.f || (m == -INFINITY && mt != -INFINITY);
       const bool rescale = __any_sync(0xffffffffu, grow);
       const float mx = rescale ? fmaxf(m, mt) : m;
@@ -281,22 +298,35 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
       const float mc = m_use * c;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < TN; i += 4) {
+      for (int i = 0; i < HALF; i += 4) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           s[i + e] = ex2(fmaf(s[i + e], c, -mc));
           sum4[e] += s[i + e];
         }
       }
-      if (r == 0) TC_TRACE(x * 4 + 2, j);
+      if (r == 0 && c2 == 0) TC_TRACE(x * 4 + 2, j);
+      m = mx;
+      // P as bf16 pairs into the first 64 columns of the same buffer: this thread's 64 keys are 32 columns
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(s[q * 32 + 2 * e], s[q * 32 + 2 * e + 1]);
+          pk[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        tmem_st16(scol + c2 * 32 + q * 16, pk);
+      }
       // O of the tile before: its MMA was issued before this tile's S, so it is complete by now; the
-      // wait only makes that visible to this thread.
+      // wait only makes that visible to this thread.  (After P has left the registers, before the word
+      // that lets the next product add to O.)
       if (j > 0) {
         mbar_wait(&bars->o_full[x], (j - 1) & 1, aborted, p.error);
         tc_fence_after();
-        if (rescale) {      // some row of this warp moves its offset: rescale O
+        if (rescale) {      // some row of this warp moves its offset: rescale this thread's half of O
 #pragma unroll
-          for (int q = 0; q < HD / 32; ++q) {
+          for (int q = 0; q < HD / 64; ++q) {
             float o[32];
             tmem_ld32(ocol + q * 32, o);
             tmem_wait_ld();
@@ -304,39 +334,29 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
             for (int i = 0; i < 32; ++i) o[i] *= alpha;
             tmem_st32(ocol + q * 32, o);
           }
-          tmem_wait_st();
         }
-      }
-      m = mx;
-      // P as bf16 pairs into the first 64 columns of the same buffer (the row has been read whole)
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        float pk[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(s[q * 64 + 2 * e], s[q * 64 + 2 * e + 1]);
-          pk[e] = __uint_as_float(*reinterpret_cast<uint32_t*>(&h));
-        }
-        tmem_st32(scol + q * 32, pk);
       }
       l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&bars->p_full[x]);
-      if (r == 0) TC_TRACE(x * 4 + 3, j);
+      if (r == 0 && c2 == 0) TC_TRACE(x * 4 + 3, j);
     }
-    // epilogue: O / l -> bf16 -> global
+    // epilogue: O / l -> bf16 -> global, this thread's 64 columns of the row
     if (n_mine > 0) {
+      bars->xch[n_mine & 1][x][c2][r] = l;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+      l += bars->xch[n_mine & 1][x][c2 ^ 1][r];
       mbar_wait(&bars->o_full[x], (n_mine - 1) & 1, aborted, p.error);
       tc_fence_after();
       const float inv = 1.f / l;
       __nv_bfloat16* orow = nullptr;
       if (R < w.rows_total) {
         const int tok = R / p.group, hig = R - tok * p.group;
-        orow = p.out + ((int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig)) * HD;
+        orow = p.out + ((int64_t)(w.q_begin + tok) * p.nh + (w.kvh * p.group + hig)) * HD + c2 * (HD / 2);
       }
 #pragma unroll
-      for (int q = 0; q < HD / 32; ++q) {
+      for (int q = 0; q < HD / 64; ++q) {
         float o[32];
         tmem_ld32(ocol + q * 32, o);
         tmem_wait_ld();
