@@ -50,3 +50,28 @@ def test_a_plan_for_any_batch_of_a_shape_covers_every_batch_of_it():
                 assert plan[0] <= bound[0], (group, long_rows, tokens, seqs, lens, plan, bound)
                 if long_rows:
                     assert plan[3] <= bound[3], (group, long_rows, tokens, seqs, lens, plan, bound)
+
+
+def test_where_the_gated_product_of_a_portion_runs_on_the_kernel_with_two_ctas_to_a_tile(monkeypatch):
+    """How well a product's tiles (256 rows x 256 outputs, one pair of CTAs each) fill the rounds of 74 pairs,
+    the ragged last round counting 0.72 where it is handed out in halves, and the rule built on it."""
+    from atom_b200.parts import linear
+
+    monkeypatch.setattr(native, "_pairs_resident", 74)
+    monkeypatch.setattr(native, "gemm_pairs_supports", lambda M, N, K, lda, ldc: K % 8 == 0 and N % 8 == 0)
+    # 2,048 rows x 12,288 outputs: 8 x 48 = 384 tiles = 5 rounds and 14 tiles, those in halves
+    assert abs(native.gemm_pairs_waves(2048, 12288, True) - 384 / (5.72 * 74)) < 1e-9
+    # 512 rows: 96 tiles = one round and 22 tiles in halves; 640 rows: 144 tiles = two rounds but four tiles
+    assert abs(native.gemm_pairs_waves(512, 12288, True) - 96 / (1.72 * 74)) < 1e-9
+    assert abs(native.gemm_pairs_waves(640, 12288, True) - 144 / (2 * 74)) < 1e-9
+    # fewer tiles than pairs: one round, however few
+    assert abs(native.gemm_pairs_waves(64, 4096, False) - 8 / 74) < 1e-9
+    assert linear.pairs_pay(2048, 12288, 4096, 4096, 12288)
+    assert linear.pairs_pay(640, 12288, 4096, 4096, 12288)
+    assert not linear.pairs_pay(512, 12288, 4096, 4096, 12288)       # fills too little
+    assert not linear.pairs_pay(64, 12288, 4096, 4096, 12288)        # too few rows
+    assert not linear.pairs_pay(2048, 12288, 4100, 4100, 12288)      # a width the kernel refuses
+    monkeypatch.setattr(linear, "PAIRS_MIN_ROWS", 0)
+    assert not linear.pairs_pay(2048, 12288, 4096, 4096, 12288)      # switched off
+    monkeypatch.setattr(native, "_pairs_resident", 0)                # the kernel cannot run on this device
+    assert native.gemm_pairs_waves(2048, 12288, True) == 0.0
