@@ -133,6 +133,22 @@ __device__ __forceinline__ uint32_t instr_desc(int m, int n, bool b_mn_major) {
          ((uint32_t)(m >> 4) << 24);
 }
 
+// The largest of three in one instruction.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Two 32-bit lanes in one instruction: (x0, x1) = (x0, x1) * c + d, and (s0, s1) += (x0, x1).
+__device__ __forceinline__ void fma2(float& x0, float& x1, float c, float d) {
+  asm("{\n.reg .b64 a, b, cc, r;\nmov.b64 a, {%0, %1};\nmov.b64 b, {%2, %2};\nmov.b64 cc, {%3, %3};\n"
+      "fma.rn.f32x2 r, a, b, cc;\nmov.b64 {%0, %1}, r;\n}\n"
+      : "+f"(x0), "+f"(x1) : "f"(c), "f"(d));
+}
+__device__ __forceinline__ void add2(float& s0, float& s1, float x0, float x1) {
+  asm("{\n.reg .b64 a, b, r;\nmov.b64 a, {%0, %1};\nmov.b64 b, {%2, %3};\nadd.rn.f32x2 r, a, b;\nmov.b64 {%0, %1}, r;\n}\n"
+      : "+f"(s0), "+f"(s1) : "f"(x0), "f"(x1));
+}
 // 2^x, one instruction of the special-function unit (2^-inf = 0).
 __device__ __forceinline__ float ex2(float x) {
   float y;

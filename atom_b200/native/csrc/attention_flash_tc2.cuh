@@ -275,12 +275,11 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
 #pragma unroll
       for (int e = 0; e < 8; ++e) mx8[e] = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < HALF; i += 8) {
+      for (int i = 0; i < HALF; i += 16) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], s[i + e]);
+        for (int e = 0; e < 8; ++e) mx8[e] = max3(mx8[e], s[i + e], s[i + 8 + e]);
       }
-      float mt = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                       fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mt = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
       // The row's maximum over both halves.  After this barrier both threads of the row have read their
       // scores, so the first 64 columns of S may take P.
       bars->xch[j & 1][x][c2][r] = mt;
@@ -298,12 +297,13 @@ flash_prefill_tc2_kernel(const Params p, int min_rows, const __grid_constant__ M
       const float mc = m_use * c;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < HALF; i += 4) {
+      for (int i = 0; i < HALF; i += 4) {      // (the softmax warps are bound by the instructions they issue: two lanes per FMA and per add)
+        fma2(s[i], s[i + 1], c, -mc);
+        fma2(s[i + 2], s[i + 3], c, -mc);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          s[i + e] = ex2(fmaf(s[i + e], c, -mc));
-          sum4[e] += s[i + e];
-        }
+        for (int e = 0; e < 4; ++e) s[i + e] = ex2(s[i + e]);
+        add2(sum4[0], sum4[1], s[i], s[i + 1]);
+        add2(sum4[2], sum4[3], s[i + 2], s[i + 3]);
       }
       if (r == 0 && c2 == 0) TC_TRACE(x * 4 + 2, j);
       m = mx;
