@@ -76,3 +76,43 @@ def test_prompts_whole_then_decoded_together(big_model, dtype):
     for i in range(4):
         runner.finish(i)
     assert all(g.pool.num_used == 0 for g in runner.cache.groups)
+
+
+def test_a_portion_long_enough_for_the_gated_product_on_two_ctas_to_a_tile(big_model):
+    """From 600 rows on the feed-forward's gated product of a portion runs, by the engine's own rule, on the
+    tcgen05 kernel with two CTAs to a tile and the activation in its epilogue: a prompt of 700 tokens in one
+    step gives the plain implementation's logits, and the kernel did run."""
+    from atom_b200 import native
+    from atom_b200.config import EngineConfig
+    from atom_b200.engine.batch import StepEntry
+    from atom_b200.engine.runner import ModelRunner
+
+    d, _, _ = big_model
+    n = 700
+    seq = np.random.default_rng(13).integers(0, CONFIG["vocab_size"], n).tolist()
+    cfg, w = plain.read_config(d), plain.read_tensors(d)
+    r = plain.forward(cfg, w, seq).numpy()
+    calls = [0]
+    real = native.gemm_pairs
+
+    def counted(*args, **kwargs):
+        calls[0] += 1
+        return real(*args, **kwargs)
+
+    native.gemm_pairs = counted
+    try:
+        runner = ModelRunner(EngineConfig(model=d, dtype="bfloat16", kv_cache_block_size=16, num_kvcache_blocks=64,
+                                          max_num_seqs=2, max_num_batched_tokens=1024, enforce_eager=True))
+        g = runner.step([StepEntry(0, seq, list(range(n)))]).cpu().numpy()
+        runner.check_status()
+    finally:
+        native.gemm_pairs = real
+    assert calls[0] == CONFIG["num_hidden_layers"], "the portion's gated products did not run on the kernel"
+    scale = float(np.abs(r).max())
+    err, rms = float(np.abs(g - r).max()), float(np.sqrt(np.mean((g - r) ** 2)))
+    assert err <= 0.08 * scale and rms <= 0.01 * scale, f"max {err:.3f}, rms {rms:.4f}, scale {scale:.2f}"
+    top2 = np.sort(r, axis=-1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 0.1 * scale
+    assert (g.argmax(-1)[clear] == r.argmax(-1)[clear]).all()
+    runner.finish(0)
+    assert all(grp.pool.num_used == 0 for grp in runner.cache.groups)
