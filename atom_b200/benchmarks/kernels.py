@@ -4,6 +4,8 @@
     python -m atom_b200.benchmarks.kernels attention [--mode decode|prefill] [--batch 1,8,64] [--context 4096]
     python -m atom_b200.benchmarks.kernels elementwise [--tokens 8,2048]
 
+With up to 16 rows the gemm mode times the library beside the weight-streaming product, with more rows
+(--rows 2048) beside the tcgen05 product with two CTAs to a tile, the two sides in turn.
 Sizes default to Qwen3-8B's (hidden 4096, 32 heads, 8 kv heads, head size 128, feed-forward
 12288, vocabulary 151936).  Every timing replays a CUDA graph of several launches over
 different copies of the operands (together larger than L2), so neither host launch
